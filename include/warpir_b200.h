@@ -1,0 +1,118 @@
+/*
+ * C ABI of libwarpir_b200.so: the sm_100a launcher for WarpIR's hot path
+ * (bf16 GEMM and attention forward).
+ *
+ * Each entry point replaces a run-time interface of the reference, which has no
+ * library of its own: it JIT-builds a pybind module per generated kernel with
+ * torch's load_inline and calls `launch_gemm(A, B, C)` / `launch_attention(Q, K, V, O)`
+ * on torch tensors.  The citations below name the reference wrapper each entry
+ * point stands in for.
+ *
+ * Conventions
+ *  - plain pointers and sizes only; every pointer is DEVICE memory on `device`;
+ *  - the caller owns every buffer, outputs included (as in the reference, which
+ *    passes a pre-allocated C / O: tests/test_gemm_baseline.py:80);
+ *  - calls enqueue work on `cuda_stream` (a cudaStream_t, NULL = legacy default
+ *    stream, which is what the reference's wrappers launch on) and return without
+ *    synchronising; results are ready when the stream reaches that point;
+ *  - return value: 0 on success, a negative WARPIR_E* code otherwise; nothing is
+ *    thrown across the boundary and the process is never terminated;
+ *  - arguments are validated BEFORE anything is launched; a rejected call has no
+ *    side effect;
+ *  - the library keeps a few hundred bytes of state per device (status words) and,
+ *    only when a GEMM is split along K, a scratch buffer it grows on demand;
+ *  - thread-safe: calls may come from several host threads, for one or several
+ *    devices.
+ */
+#ifndef WARPIR_B200_H_
+#define WARPIR_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define WARPIR_ABI_VERSION 1
+
+enum {
+  WARPIR_OK = 0,
+  WARPIR_EINVAL = -1,      /* NULL pointer, negative size, bad enum value            */
+  WARPIR_EALIGN = -2,      /* a pointer or a row pitch is not 16-byte aligned        */
+  WARPIR_ESHAPE = -3,      /* a size the kernels do not cover (see each function)    */
+  WARPIR_ECUDA = -4,       /* a CUDA runtime call failed; see warpir_last_error()    */
+  WARPIR_EDRIVER = -5,     /* cuTensorMapEncodeTiled missing or failed               */
+  WARPIR_EKERNEL = -6,     /* a kernel reported an error in its status words         */
+  WARPIR_EDEVICE = -7,     /* pointer does not live on `device`, or bad device index */
+  WARPIR_ENOMEM = -8       /* scratch allocation failed                              */
+};
+
+/* ABI version of the loaded library (== WARPIR_ABI_VERSION it was built with). */
+int warpir_abi_version(void);
+
+/* Static, human-readable text for a WARPIR_E* code. */
+const char* warpir_strerror(int code);
+
+/* Text of the most recent failure on the calling thread (CUDA error string,
+ * the argument that was rejected ...).  Valid until the thread's next call. */
+const char* warpir_last_error(void);
+
+/*
+ * C[M,N] = A[M,K] * B, bf16 inputs, fp32 accumulation, bf16 output, all row-major
+ * and densely packed.
+ *   b_layout 0: B is stored [K,N] (the layout of the reference's GEMM tile program,
+ *               tests/gemm_baseline_v2.py:78-79);
+ *   b_layout 1: B is stored [N,K], i.e. C = A * B_stored^T ("K-major").
+ * Replaces `launch_gemm(A, B, C)` (reference: tests/test_gemm_baseline.py:20-31,
+ * tests/test_modal_gpu.py:24-50), which takes square N x N tensors only and requires
+ * N to be a multiple of 64.  Here M, N, K are free, except that the row pitches TMA
+ * reads must be multiples of 16 bytes: K % 8 == 0, and N % 8 == 0 for b_layout 0.
+ * M, N or K equal to 0 is a valid no-op (K == 0 zero-fills C).
+ */
+int warpir_gemm_bf16(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K,
+                     int b_layout, int device, void* cuda_stream);
+
+/*
+ * Same as warpir_gemm_bf16 with the two launch parameters the scheduling pass may
+ * choose made explicit: the tile width `block_n` (64, 128 or 256; 0 = choose) and
+ * the number of K-splits per output tile `splits` (>= 1; 0 = choose).  With
+ * splits > 1 the partial sums go through an fp32 scratch buffer owned by the
+ * library and are reduced in a fixed order, so results do not depend on timing.
+ * No counterpart in the reference, whose tile shape is a constant of the tile
+ * program (tests/gemm_baseline_v2.py:32).
+ */
+int warpir_gemm_bf16_ex(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K,
+                        int b_layout, int block_n, int splits, int device, void* cuda_stream);
+
+/*
+ * Attention forward: O[b,h] = softmax(softmax_scale * Q[b,h] K[b,hk]^T (+ causal mask)) V[b,hk],
+ * LSE[b,h,i] = log sum_j exp(softmax_scale * q_i . k_j) (natural log), hk = h / (Hq / Hkv).
+ *   Q, O: [B, Hq, S, D] bf16, contiguous;  K, V: [B, Hkv, S, D] bf16, contiguous;
+ *   LSE: [B, Hq, S] fp32, or NULL to skip it;  D is 64 or 128;  Hq % Hkv == 0;
+ *   causal != 0: key j is visible to query i iff j <= i.
+ * Replaces `launch_attention(Q, K, V, O)` (reference: tests/test_modal_attention.py:25-39:
+ * one head, [N, 64], non-causal, scale 1/8 fixed, N a multiple of 64, no LSE) and the
+ * host wrapper `attention_forward` of the reference's hand-written target
+ * (kernel_examples/attention/mha_h100.cu:651-797: 4-D, D in {64,128}, causal flag,
+ * grouped KV heads, an L vector).  S is free (any S >= 1).
+ */
+int warpir_attn_fwd_bf16(const void* Q, const void* K, const void* V, void* O, float* LSE,
+                         int64_t B, int64_t Hq, int64_t Hkv, int64_t S, int64_t D,
+                         float softmax_scale, int causal, int device, void* cuda_stream);
+
+/*
+ * Waits for `cuda_stream`, then reports and clears the device's status words:
+ * *code is 0 when every kernel launched so far on this device ran to completion,
+ * otherwise the kernel-side error (1 = a bounded wait ran out); *detail packs
+ * (role << 16 | tag).  Returns WARPIR_OK when *code == 0, WARPIR_EKERNEL otherwise.
+ * Every wait inside the kernels is bounded, so a protocol failure surfaces here
+ * rather than as a hung GPU.  The reference checks nothing after a launch
+ * (tests/test_gemm_baseline.py:21-30).
+ */
+int warpir_read_status(int device, void* cuda_stream, int* code, int* detail);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* WARPIR_B200_H_ */

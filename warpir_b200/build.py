@@ -1,0 +1,74 @@
+"""Builds ``libwarpir_b200.so`` (sm_100a only) in-tree with nvcc.
+
+    python -m warpir_b200.build [--force]
+
+The library lands in ``warpir_b200/lib/``; it is what ``warpir_b200.runtime``
+loads through ``ctypes``.  nvcc cross-compiles, so no GPU is needed to build.
+"""
+from __future__ import annotations
+
+import hashlib
+import os
+import shutil
+import subprocess
+import sys
+from pathlib import Path
+
+PKG = Path(__file__).resolve().parent
+CSRC = PKG / "csrc"
+LIB_DIR = PKG / "lib"
+LIB_PATH = LIB_DIR / "libwarpir_b200.so"
+INCLUDE = PKG.parent / "include"
+
+NVCC_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a",
+    "-lineinfo", "-O3", "-std=c++17",
+    "-shared", "-Xcompiler", "-fPIC",
+    "-Xptxas", "-v",
+]
+
+
+def find_nvcc() -> str:
+    for cand in (os.environ.get("NVCC"), shutil.which("nvcc"), "/usr/local/cuda/bin/nvcc"):
+        if cand and Path(cand).exists():
+            return cand
+    raise RuntimeError("nvcc not found (set NVCC or put it on PATH)")
+
+
+def _sources():
+    return sorted(list(CSRC.glob("*.cu")) + list(CSRC.glob("*.cuh")) + list(INCLUDE.glob("*.h")))
+
+
+def source_digest() -> str:
+    h = hashlib.sha256()
+    for f in _sources():
+        h.update(f.name.encode())
+        h.update(f.read_bytes())
+    h.update(" ".join(NVCC_FLAGS).encode())
+    return h.hexdigest()[:16]
+
+
+def is_current() -> bool:
+    stamp = LIB_DIR / "build.stamp"
+    return LIB_PATH.exists() and stamp.exists() and stamp.read_text().strip() == source_digest()
+
+
+def build_library(force: bool = False, verbose: bool = False) -> Path:
+    """Compile if the sources changed since the last build; return the library path."""
+    if not force and is_current():
+        return LIB_PATH
+    LIB_DIR.mkdir(exist_ok=True)
+    cmd = [find_nvcc(), *NVCC_FLAGS, "-I", str(INCLUDE), "-o", str(LIB_PATH), str(CSRC / "capi.cu")]
+    proc = subprocess.run(cmd, capture_output=True, text=True)
+    (LIB_DIR / "ptxas.log").write_text(proc.stdout + proc.stderr)
+    if verbose or proc.returncode != 0:
+        sys.stderr.write(proc.stdout + proc.stderr)
+    if proc.returncode != 0:
+        raise RuntimeError(f"nvcc failed ({proc.returncode}): {' '.join(cmd)}")
+    (LIB_DIR / "build.stamp").write_text(source_digest() + "\n")
+    return LIB_PATH
+
+
+if __name__ == "__main__":
+    path = build_library(force="--force" in sys.argv, verbose="-v" in sys.argv)
+    print(path)

@@ -1,0 +1,299 @@
+// bf16 GEMM for sm_100a: C[M,N] = A[M,K] * B, fp32 accumulation in tensor memory.
+//
+// This is the device kernel that the reference's GEMM tile program
+// (tests/gemm_baseline_v2.py:62-88: zero; k-loop of two TMA loads, wait, MMA;
+// store) lowers to.  The reference emits a 64x64 tile per CTA with every k-step
+// serialised by block barriers (warpir/lowering/lowering.py:436-470); its
+// hand-written targets add a two-slot ring (kernel_examples/gemm_pipelined.cu:21-78)
+// and a producer/consumer split with full/empty semaphores
+// (kernel_examples/gemm_warp_specialized.cu:22-77).  On Blackwell the same program
+// becomes a persistent, warp-specialised kernel:
+//
+//   warp 0   producer: one lane issues TMA loads of A (128 x 64) and B (BN x 64)
+//            tiles into a STAGES-deep shared-memory ring guarded by full/empty
+//            mbarriers;
+//   warp 1   MMA issuer: one lane issues tcgen05.mma (128 x BN x 16, four per
+//            stage) into one of two accumulators in tensor memory, frees each
+//            stage with tcgen05.commit and publishes the finished accumulator;
+//   warps 2-5 epilogue: tcgen05.ld the accumulator (one row per thread), convert
+//            to bf16 and store C, overlapping the next tile's main loop.
+//
+// Work items (output tile x K-split) are handed out statically, `gridDim.x`
+// apart, walking the tile grid in bands of kGroupM row-blocks so that the CTAs
+// running at any moment share A and B panels in L2.
+#pragma once
+
+#include "ptx.cuh"
+
+namespace wir {
+
+constexpr int kGemmBM = 128;      // rows of an output tile = MMA M
+constexpr int kGemmBK = 64;       // K extent of one pipeline stage: 64 bf16 = one 128-byte swizzle row
+constexpr int kGemmThreads = 192; // producer warp + MMA warp + 4 epilogue warps
+constexpr int kGroupM = 16;       // rasterisation band height in row-blocks
+
+struct GemmParams {
+  int M, N, K;
+  int ldc;            // leading dimension of C in elements
+  int tiles_m, tiles_n;
+  int num_kb;         // ceil(K / 64)
+  int splits;         // K-splits per output tile (1 = none)
+  int kb_per_split;
+  __nv_bfloat16* C;
+  float* partial;     // [splits][M][N] fp32 partial sums when splits > 1
+  int* status;        // 4 device status words
+};
+
+template <int BN, int STAGES>
+struct GemmSmem {
+  static constexpr int kABytes = kGemmBM * kGemmBK * 2;
+  static constexpr int kBBytes = BN * kGemmBK * 2;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kBarOffset = STAGES * kStageBytes;
+  // full[STAGES], empty[STAGES], acc_full[2], acc_empty[2], drain
+  static constexpr int kNumBars = 2 * STAGES + 5;
+  static constexpr int kTmemPtrOffset = kBarOffset + kNumBars * 8;
+  static constexpr int kAbortOffset = kTmemPtrOffset + 4;
+  static constexpr int kBytes = kAbortOffset + 4;
+  static constexpr int kDynamicBytes = kBytes + 1024;  // room to align the base to 1024 B
+};
+
+struct TileCoord {
+  int m_blk, n_blk, kb_begin, kb_end, split;
+};
+
+__device__ __forceinline__ TileCoord decode_work(int w, const GemmParams& p) {
+  const int tile = w / p.splits;
+  const int split = w - tile * p.splits;
+  const int band = kGroupM * p.tiles_n;
+  const int g = tile / band;
+  const int first_m = g * kGroupM;
+  const int rows = min(p.tiles_m - first_m, kGroupM);
+  const int in_band = tile - g * band;
+  TileCoord t;
+  t.m_blk = first_m + in_band % rows;
+  t.n_blk = in_band / rows;
+  t.split = split;
+  t.kb_begin = split * p.kb_per_split;
+  t.kb_end = min(p.num_kb, t.kb_begin + p.kb_per_split);
+  return t;
+}
+
+// B_MN = false: B stored [N,K] (K contiguous), one TMA box of BN rows per stage.
+// B_MN = true : B stored [K,N] (N contiguous), BN/64 boxes of 64(k) x 64(n) per stage.
+template <int BN, int STAGES, bool B_MN>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                const GemmParams p) {
+  using L = GemmSmem<BN, STAGES>;
+  constexpr uint32_t kTmemCols = (2 * BN < 32) ? 32 : 2 * BN;
+  static_assert((kTmemCols & (kTmemCols - 1)) == 0 && kTmemCols <= 512, "TMEM columns");
+  static_assert(BN % 16 == 0 && BN >= 16 && BN <= 256, "MMA N");
+  static_assert(!B_MN || BN % 64 == 0, "N-contiguous B is loaded in 64-column boxes");
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const uint32_t smem_base = smem_u32(smem);
+  const uint32_t bar_base = smem_base + L::kBarOffset;
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+  auto acc_full_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + a); };
+  auto acc_empty_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + 2 + a); };
+  const uint32_t drain_bar = bar_base + 8u * (2 * STAGES + 4);
+  volatile uint32_t* tmem_ptr_slot = reinterpret_cast<volatile uint32_t*>(smem + L::kTmemPtrOffset);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kAbortOffset);
+  const AbortCtx ctx{abort_flag, p.status};
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(acc_full_bar(a), 1);
+      mbar_init(acc_empty_bar(a), 128);
+    }
+    mbar_init(drain_bar, 1);
+    fence_mbar_init();
+    prefetch_tensormap(&tmap_a);
+    prefetch_tensormap(&tmap_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_ptr_slot)), kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_ptr_slot;
+
+  const int total_work = p.tiles_m * p.tiles_n * p.splits;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ producer
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int w = blockIdx.x; ok && w < total_work; w += gridDim.x) {
+        const TileCoord t = decode_work(w, p);
+        for (int kb = t.kb_begin; kb < t.kb_end; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(empty_bar(s), ph ^ 1, ctx, kRoleProducer, s, kb)) { ok = false; break; }
+          mbar_arrive_expect_tx(full_bar(s), L::kStageBytes);
+          const uint32_t a_dst = smem_base + s * L::kStageBytes;
+          const uint32_t b_dst = a_dst + L::kABytes;
+          tma_load_2d(a_dst, &tmap_a, full_bar(s), kb * kGemmBK, t.m_blk * kGemmBM);
+          if constexpr (!B_MN) {
+            tma_load_2d(b_dst, &tmap_b, full_bar(s), kb * kGemmBK, t.n_blk * BN);
+          } else {
+#pragma unroll
+            for (int c = 0; c < BN / 64; ++c)
+              tma_load_2d(b_dst + c * 8192, &tmap_b, full_bar(s), t.n_blk * BN + c * 64, kb * kGemmBK);
+          }
+        }
+      }
+      if (!ok || *abort_flag) {
+        // wait (bounded, silently) for the copies still in flight before the CTA may exit
+        const uint32_t n = it < STAGES ? it : STAGES;
+        for (uint32_t back = 1; back <= n; ++back) {
+          const uint32_t idx = it - back;
+          mbar_wait_quiet(full_bar(idx % STAGES), (idx / STAGES) & 1);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = idesc_bf16_f32(kGemmBM, BN, 0, B_MN ? 1 : 0);
+      uint32_t it = 0, acc_it = 0;
+      bool ok = true;
+      for (int w = blockIdx.x; ok && w < total_work; w += gridDim.x, ++acc_it) {
+        const TileCoord t = decode_work(w, p);
+        const uint32_t acc = acc_it & 1;
+        const uint32_t acc_ph = (acc_it >> 1) & 1;
+        if (!mbar_wait(acc_empty_bar(acc), acc_ph ^ 1, ctx, kRoleMma, 100 + acc, w)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = t.kb_begin; kb < t.kb_end; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(full_bar(s), ph, ctx, kRoleMma, s, kb)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t a_src = smem_base + s * L::kStageBytes;
+          const uint32_t b_src = a_src + L::kABytes;
+          const uint64_t a_desc = smem_desc_sw128(a_src, 16, 1024);
+          const uint64_t b_desc = B_MN ? smem_desc_sw128(b_src, 8192, 1024) : smem_desc_sw128(b_src, 16, 1024);
+#pragma unroll
+          for (int k = 0; k < kGemmBK / 16; ++k) {
+            // 16 K-elements further: 32 bytes along a K-major row, 16 rows (2048 B) of an N-major tile
+            const uint64_t a_k = a_desc + static_cast<uint64_t>((k * 32) >> 4);
+            const uint64_t b_k = b_desc + static_cast<uint64_t>(B_MN ? (k * 2048) >> 4 : (k * 32) >> 4);
+            mma_ss(d_tmem, a_k, b_k, idesc, (kb > t.kb_begin || k > 0) ? 1u : 0u);
+          }
+          mma_commit(empty_bar(s));  // stage reusable once these MMAs have read it
+        }
+        if (ok) mma_commit(acc_full_bar(acc));
+      }
+      if (!ok || *abort_flag) {
+        mma_commit(drain_bar);
+        mbar_wait_quiet(drain_bar, 0);
+      }
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------------------------------------ epilogue
+    const int quarter = warp & 3;  // tensor-memory lanes [32*quarter, 32*quarter+32) belong to this warp
+    const bool vec_ok = (p.ldc % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0);
+    uint32_t acc_it = 0;
+    bool ok = true;
+    for (int w = blockIdx.x; ok && w < total_work; w += gridDim.x, ++acc_it) {
+      const TileCoord t = decode_work(w, p);
+      const uint32_t acc = acc_it & 1;
+      const uint32_t acc_ph = (acc_it >> 1) & 1;
+      if (!mbar_wait(acc_full_bar(acc), acc_ph, ctx, kRoleEpilogue, acc, w)) { ok = false; break; }
+      tc_fence_after();
+      const int row = t.m_blk * kGemmBM + quarter * 32 + lane;
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
+      constexpr int kChunk = (BN % 32 == 0) ? 32 : 16;
+#pragma unroll 1
+      for (int c = 0; c < BN / kChunk; ++c) {
+        uint32_t r[kChunk];
+        if constexpr (kChunk == 32) tmem_ld32(t_row + c * kChunk, r);
+        else tmem_ld16(t_row + c * kChunk, r);
+        tmem_wait_ld();
+        const int col0 = t.n_blk * BN + c * kChunk;
+        if (row < p.M && col0 < p.N) {
+          if (p.splits == 1) {
+            __nv_bfloat16* dst = p.C + static_cast<size_t>(row) * p.ldc + col0;
+            if (vec_ok && col0 + kChunk <= p.N) {
+#pragma unroll
+              for (int v = 0; v < kChunk / 8; ++v) {
+                uint4 q;
+                q.x = pack_bf16(__uint_as_float(r[8 * v + 0]), __uint_as_float(r[8 * v + 1]));
+                q.y = pack_bf16(__uint_as_float(r[8 * v + 2]), __uint_as_float(r[8 * v + 3]));
+                q.z = pack_bf16(__uint_as_float(r[8 * v + 4]), __uint_as_float(r[8 * v + 5]));
+                q.w = pack_bf16(__uint_as_float(r[8 * v + 6]), __uint_as_float(r[8 * v + 7]));
+                reinterpret_cast<uint4*>(dst)[v] = q;
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < kChunk; ++j)
+                if (col0 + j < p.N) dst[j] = __float2bfloat16_rn(__uint_as_float(r[j]));
+            }
+          } else {
+            float* dst = p.partial + (static_cast<size_t>(t.split) * p.M + row) * p.N + col0;
+            if ((p.N % 4 == 0) && col0 + kChunk <= p.N) {
+#pragma unroll
+              for (int v = 0; v < kChunk / 4; ++v)
+                reinterpret_cast<uint4*>(dst)[v] = make_uint4(r[4 * v], r[4 * v + 1], r[4 * v + 2], r[4 * v + 3]);
+            } else {
+#pragma unroll
+              for (int j = 0; j < kChunk; ++j)
+                if (col0 + j < p.N) dst[j] = __uint_as_float(r[j]);
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(acc_empty_bar(acc));
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// Deterministic second pass of a split-K GEMM: sums the fp32 partials in split
+// order and rounds to bf16.  One thread per four consecutive columns.
+__global__ void splitk_reduce_bf16(const float* __restrict__ partial, __nv_bfloat16* __restrict__ C,
+                                   int M, int N, int ldc, int splits) {
+  const size_t total4 = (static_cast<size_t>(M) * N) >> 2;
+  const size_t plane = static_cast<size_t>(M) * N;
+  for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total4;
+       i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    float4 acc = reinterpret_cast<const float4*>(partial)[i];
+    for (int s = 1; s < splits; ++s) {
+      const float4 v = reinterpret_cast<const float4*>(partial + s * plane)[i];
+      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    const size_t e = i << 2;
+    const int row = static_cast<int>(e / N);
+    const int col = static_cast<int>(e - static_cast<size_t>(row) * N);
+    __nv_bfloat16* dst = C + static_cast<size_t>(row) * ldc + col;
+    uint2 q;
+    q.x = pack_bf16(acc.x, acc.y);
+    q.y = pack_bf16(acc.z, acc.w);
+    *reinterpret_cast<uint2*>(dst) = q;
+  }
+}
+
+}  // namespace wir

@@ -1,0 +1,174 @@
+"""ctypes binding of the C-ABI launcher and torch-tensor convenience wrappers.
+
+This replaces what the reference does at run time: JIT-build a pybind module per
+generated kernel with ``load_inline`` and call ``launch_gemm(A, B, C)`` /
+``launch_attention(Q, K, V, O)`` (reference: tests/test_gemm_baseline.py:52-74,
+tests/test_modal_attention.py:80-99).  The callables here keep those call
+shapes -- the caller allocates every tensor, outputs included; the call is
+asynchronous on torch's current stream -- and raise instead of silently
+continuing when something is wrong.  There is no fallback: without the compiled
+library, or without an sm_100 GPU, every entry point raises.
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+import threading
+from pathlib import Path
+from typing import Optional
+
+_LIB_PATH = Path(__file__).resolve().parent / "lib" / "libwarpir_b200.so"
+_lib = None
+_lock = threading.Lock()
+
+ABI_VERSION = 1
+
+EXPORTS = (
+    "warpir_abi_version", "warpir_strerror", "warpir_last_error", "warpir_gemm_bf16",
+    "warpir_gemm_bf16_ex", "warpir_attn_fwd_bf16", "warpir_read_status",
+)
+
+
+class WarpirError(RuntimeError):
+    """A C-ABI call returned a negative code."""
+
+    def __init__(self, code: int, what: str, detail: str):
+        super().__init__(f"{what}: {detail}" if detail else what)
+        self.code = code
+
+
+def library_path() -> Path:
+    return _LIB_PATH
+
+
+def load_library() -> ctypes.CDLL:
+    """Load ``libwarpir_b200.so`` (built by ``python -m warpir_b200.build``) and
+    declare its prototypes.  Raises if the file is missing or its ABI differs."""
+    global _lib
+    with _lock:
+        if _lib is not None:
+            return _lib
+        if not _LIB_PATH.exists():
+            raise FileNotFoundError(
+                f"{_LIB_PATH} is missing: build it with `python -m warpir_b200.build` "
+                "(there is no fallback path)")
+        lib = ctypes.CDLL(str(_LIB_PATH))
+        vp, i64, ci, cf = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int, ctypes.c_float
+        lib.warpir_abi_version.restype = ci
+        lib.warpir_abi_version.argtypes = []
+        lib.warpir_strerror.restype = ctypes.c_char_p
+        lib.warpir_strerror.argtypes = [ci]
+        lib.warpir_last_error.restype = ctypes.c_char_p
+        lib.warpir_last_error.argtypes = []
+        lib.warpir_gemm_bf16.restype = ci
+        lib.warpir_gemm_bf16.argtypes = [vp, vp, vp, i64, i64, i64, ci, ci, vp]
+        lib.warpir_gemm_bf16_ex.restype = ci
+        lib.warpir_gemm_bf16_ex.argtypes = [vp, vp, vp, i64, i64, i64, ci, ci, ci, ci, vp]
+        lib.warpir_attn_fwd_bf16.restype = ci
+        lib.warpir_attn_fwd_bf16.argtypes = [vp, vp, vp, vp, vp, i64, i64, i64, i64, i64, cf, ci, ci, vp]
+        lib.warpir_read_status.restype = ci
+        lib.warpir_read_status.argtypes = [ci, vp, ctypes.POINTER(ci), ctypes.POINTER(ci)]
+        if lib.warpir_abi_version() != ABI_VERSION:
+            raise RuntimeError(f"ABI {lib.warpir_abi_version()} != expected {ABI_VERSION}: rebuild the library")
+        _lib = lib
+        return lib
+
+
+def _check(rc: int) -> None:
+    if rc != 0:
+        lib = load_library()
+        raise WarpirError(rc, lib.warpir_strerror(rc).decode(), lib.warpir_last_error().decode())
+
+
+def _stream_of(t) -> int:
+    import torch
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def _require(t, name: str, dtype, ndim: Optional[int] = None):
+    import torch
+    if not isinstance(t, torch.Tensor):
+        raise TypeError(f"{name} must be a torch.Tensor")
+    if not t.is_cuda:
+        raise ValueError(f"{name} must be a CUDA tensor (there is no CPU path)")
+    if t.dtype != dtype:
+        raise TypeError(f"{name} must be {dtype}, got {t.dtype}")
+    if not t.is_contiguous():
+        raise ValueError(f"{name} must be contiguous")
+    if ndim is not None and t.dim() != ndim:
+        raise ValueError(f"{name} must have {ndim} dimensions, got {t.dim()}")
+
+
+def launch_gemm(A, B, C, b_layout: int = 0, block_n: int = 0, splits: int = 0) -> None:
+    """``C = A @ B`` (``b_layout=0``, B stored ``[K,N]``) or ``C = A @ B.T``
+    (``b_layout=1``, B stored ``[N,K]``) on torch's current stream.
+
+    Same call shape as the reference's ``launch_gemm(A, B, C)``
+    (tests/test_gemm_baseline.py:20-31): bf16 CUDA tensors, C pre-allocated,
+    asynchronous.  Sizes need not be square nor tile multiples.
+    """
+    import torch
+    lib = load_library()
+    for t, n in ((A, "A"), (B, "B"), (C, "C")):
+        _require(t, n, torch.bfloat16, 2)
+    M, K = A.shape
+    if b_layout == 1:
+        N, Kb = B.shape
+    elif b_layout == 0:
+        Kb, N = B.shape
+    else:
+        raise ValueError("b_layout must be 0 or 1")
+    if Kb != K or tuple(C.shape) != (M, N):
+        raise ValueError(f"shape mismatch: A {tuple(A.shape)}, B {tuple(B.shape)}, C {tuple(C.shape)}")
+    if not (A.device == B.device == C.device):
+        raise ValueError("A, B and C must be on one device")
+    _check(lib.warpir_gemm_bf16_ex(A.data_ptr(), B.data_ptr(), C.data_ptr(), M, N, K, b_layout,
+                                   block_n, splits, A.device.index, _stream_of(A)))
+
+
+def launch_attention(Q, K, V, O, LSE=None, softmax_scale: Optional[float] = None,
+                     causal: bool = False) -> None:
+    """Attention forward on torch's current stream.
+
+    Accepts the reference's single-head call ``launch_attention(Q, K, V, O)``
+    with ``[N, D]`` tensors (tests/test_modal_attention.py:25-39) as well as
+    ``[B, H, S, D]`` tensors with grouped KV heads; ``LSE`` (fp32 ``[B, H, S]``
+    or ``[N]``) is filled when given.  Scale defaults to ``1/sqrt(D)``.
+    """
+    import torch
+    lib = load_library()
+    if Q.dim() == 2:
+        Bz, Hq, Hkv = 1, 1, 1
+        S, D = Q.shape
+    else:
+        for t, n in ((Q, "Q"), (K, "K"), (V, "V"), (O, "O")):
+            _require(t, n, torch.bfloat16, 4)
+        Bz, Hq, S, D = Q.shape
+        Hkv = K.shape[1]
+    for t, n in ((Q, "Q"), (K, "K"), (V, "V"), (O, "O")):
+        _require(t, n, torch.bfloat16)
+    if K.shape != V.shape or K.shape[-2:] != Q.shape[-2:] or O.shape != Q.shape:
+        raise ValueError(f"shape mismatch: Q {tuple(Q.shape)}, K {tuple(K.shape)}, V {tuple(V.shape)}, O {tuple(O.shape)}")
+    lse_ptr = None
+    if LSE is not None:
+        _require(LSE, "LSE", torch.float32)
+        if LSE.numel() != Bz * Hq * S:
+            raise ValueError("LSE must hold B*H*S elements")
+        lse_ptr = LSE.data_ptr()
+    if softmax_scale is None:
+        softmax_scale = 1.0 / math.sqrt(D)
+    _check(lib.warpir_attn_fwd_bf16(Q.data_ptr(), K.data_ptr(), V.data_ptr(), O.data_ptr(), lse_ptr,
+                                    Bz, Hq, Hkv, S, D, float(softmax_scale), int(bool(causal)),
+                                    Q.device.index, _stream_of(Q)))
+
+
+def read_status(device=None) -> None:
+    """Synchronise torch's current stream on ``device`` and raise ``WarpirError``
+    if any kernel launched so far reported a failed (bounded) wait."""
+    import torch
+    lib = load_library()
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    code, detail = ctypes.c_int(0), ctypes.c_int(0)
+    rc = lib.warpir_read_status(dev.index, torch.cuda.current_stream(dev).cuda_stream,
+                                ctypes.byref(code), ctypes.byref(detail))
+    _check(rc)
