@@ -1,0 +1,408 @@
+#!/usr/bin/env python
+"""Benchmark of the hot path: bf16 GEMM (headline) and attention forward.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload NAME]
+
+One JSON line on stdout (rank 0).  A step is one pass of the hot path over one
+batch of synthetic input: for the headline workload one 8192^3 bf16 GEMM per
+GPU (A row-major, B stored [N,K], fp32 accumulate, bf16 out).  With N GPUs the
+global M is N x 8192, sharded into N row blocks with B replicated: no data-path
+collective, weak scaling.  `value` is the whole-job TFLOP/s with inputs resident
+in HBM; `e2e` is the same metric through the public call with HOST buffers
+(pinned host -> device copies of A and B and the device -> host copy of C inside
+the timed region).  The other measured workloads (attention forward, skinny and
+rectangular GEMMs) are timed after the headline and reported under
+`other_workloads`.
+
+`--impl reference` times the reference's own CPU computation of the same op
+(torch.mm in fp32 on the host cores; reference: tests/test_gemm_baseline.py:85)
+on a bounded row-block sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+METRIC = "bf16 GEMM & attn-fwd TFLOP/s per B200 (% dense peak), 1/2/4/8 GPUs"
+NOMINAL_TFLOPS = 2250.0
+FALLBACK_PEAKS = {"bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "hbm_gbs": 6650.0}
+
+
+def load_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            d = json.loads(p.read_text())
+            return {k: float(d[k]) for k in FALLBACK_PEAKS}, "measured"
+        except Exception:
+            pass
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+# --------------------------------------------------------------------------- workloads
+GEMM_HEADLINE = dict(M=8192, N=8192, K=8192, std=1.0)
+
+
+def workload_table():
+    """name -> description of every measured workload (sizes per GPU)."""
+    return {
+        "gemm_8192": dict(kind="gemm", **GEMM_HEADLINE),
+        "gemm_4096": dict(kind="gemm", M=4096, N=4096, K=4096, std=1.0),
+        "gemm_2048": dict(kind="gemm", M=2048, N=2048, K=2048, std=1.0),
+        "gemm_1024": dict(kind="gemm", M=1024, N=1024, K=1024, std=1.0),
+        "gemm_16384x4096x8192": dict(kind="gemm", M=16384, N=4096, K=8192, std=0.02),
+        "gemm_skinny_m16": dict(kind="gemm", M=16, N=8192, K=8192, std=0.02),
+        "gemm_skinny_m64": dict(kind="gemm", M=64, N=8192, K=8192, std=0.02),
+        "gemm_skinny_m128": dict(kind="gemm", M=128, N=8192, K=8192, std=0.02),
+        "attn_noncausal_b16_h16_s4096_d128": dict(kind="attn", B=16, H=16, S=4096, D=128, causal=False),
+        "attn_causal_b4_h32_s8192_d128": dict(kind="attn", B=4, H=32, S=8192, D=128, causal=True),
+        "attn_causal_b4_h32_s8192_d64": dict(kind="attn", B=4, H=32, S=8192, D=64, causal=True),
+    }
+
+
+def flops_of(w) -> float:
+    if w["kind"] == "gemm":
+        return 2.0 * w["M"] * w["N"] * w["K"]
+    f = 4.0 * w["B"] * w["H"] * w["S"] * w["S"] * w["D"]
+    return f / 2 if w["causal"] else f
+
+
+def bytes_of(w) -> float:
+    if w["kind"] == "gemm":
+        return 2.0 * (w["M"] * w["K"] + w["N"] * w["K"] + w["M"] * w["N"])
+    return 2.0 * 4 * w["B"] * w["H"] * w["S"] * w["D"] + 4.0 * w["B"] * w["H"] * w["S"]
+
+
+# --------------------------------------------------------------------------- clocks
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._pump, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for n, v in zip(names, parts[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        busy = [s for s in sm if s > 0]
+        return {"sm_mhz": statistics.median(busy) if busy else None,
+                "sm_max_mhz": max(mx) if mx else None, "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# --------------------------------------------------------------------------- GPU arm
+def make_inputs(w, device, seed):
+    """Synthetic inputs of the workload's shapes and distributions, created on the device."""
+    import torch
+    g = torch.Generator(device=device).manual_seed(seed)
+    if w["kind"] == "gemm":
+        A = (torch.randn(w["M"], w["K"], generator=g, device=device) * w["std"]).bfloat16()
+        B = (torch.randn(w["N"], w["K"], generator=g, device=device) * w["std"]).bfloat16()
+        C = torch.empty(w["M"], w["N"], dtype=torch.bfloat16, device=device)
+        return (A, B), (C,)
+    shape = (w["B"], w["H"], w["S"], w["D"])
+    Q, K, V = (torch.randn(shape, generator=g, device=device).bfloat16() for _ in range(3))
+    O = torch.empty_like(Q)
+    L = torch.empty(shape[:-1], dtype=torch.float32, device=device)
+    return (Q, K, V), (O, L)
+
+
+def make_step(w, ins, outs):
+    from warpir_b200 import runtime
+    if w["kind"] == "gemm":
+        A, B = ins
+        return lambda: runtime.launch_gemm(A, B, outs[0], 1)
+    Q, K, V = ins
+    return lambda: runtime.launch_attention(Q, K, V, outs[0], outs[1], None, w["causal"])
+
+
+def sync_all(dist_on):
+    import torch
+    torch.cuda.synchronize()
+    if dist_on:
+        import torch.distributed as dist
+        dist.barrier()
+        torch.cuda.synchronize()
+
+
+def max_over_ranks(ms: float, dist_on: bool, device) -> float:
+    if not dist_on:
+        return ms
+    import torch
+    import torch.distributed as dist
+    t = torch.tensor([ms], dtype=torch.float64, device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def time_steps(step, steps, warmup, dist_on, device):
+    """W untimed steps, then exactly `steps` steps between two CUDA events on the
+    launching (current) stream, bracketed by barrier + synchronize; max over ranks."""
+    import torch
+    for _ in range(warmup):
+        step()
+    sync_all(dist_on)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        step()
+    e1.record()
+    sync_all(dist_on)
+    return max_over_ranks(e0.elapsed_time(e1), dist_on, device)
+
+
+def time_e2e(w, steps, warmup, dist_on, device):
+    """Same step through the public call with HOST buffers: every step copies its
+    inputs from pinned host memory and reads its result back."""
+    import torch
+    ins, outs = make_inputs(w, device, seed=1234)
+    h_ins = [t.cpu().pin_memory() for t in ins]
+    h_outs = [torch.empty(t.shape, dtype=t.dtype).pin_memory() for t in outs]
+    step = make_step(w, ins, outs)
+
+    def e2e_step():
+        for d, h in zip(ins, h_ins):
+            d.copy_(h, non_blocking=True)
+        step()
+        for d, h in zip(outs, h_outs):
+            h.copy_(d, non_blocking=True)
+
+    ms = time_steps(e2e_step, steps, warmup, dist_on, device)
+    h2d = sum(t.numel() * t.element_size() for t in h_ins)
+    d2h = sum(t.numel() * t.element_size() for t in h_outs)
+    return ms, h2d, d2h
+
+
+def cpu_baseline_gemm(w, target_seconds=10.0):
+    """The oracle (the reference's torch.mm expression on CPU, fp32) on a row-block
+    sample of the workload, all host threads."""
+    import torch
+    from oracle import reference_ops as R
+    cores = R.host_threads()
+    torch.set_num_threads(cores)
+    g = torch.Generator().manual_seed(0)
+    N, K = w["N"], w["K"]
+    B = R.randn_bf16((N, K), g, w["std"])
+    rows = min(256, w["M"])
+    A = R.randn_bf16((rows, K), g, w["std"])
+    t0 = time.perf_counter()
+    R.gemm_ref(A, B, 1)
+    dt = time.perf_counter() - t0
+    scale = max(1, min(w["M"] // rows, int(target_seconds / max(dt, 1e-3))))
+    rows2 = rows * scale
+    A = R.randn_bf16((rows2, K), g, w["std"])
+    t0 = time.perf_counter()
+    R.gemm_ref(A, B, 1)
+    dt = time.perf_counter() - t0
+    return {"value": 2.0 * rows2 * N * K / dt / 1e12, "unit": "TFLOP/s", "cores": cores, "kind": "port",
+            "sample": f"rows 0..{rows2} of A ({rows2}x{K}) times the full B ({N}x{K}), fp32 torch.mm, {dt:.2f} s"}
+
+
+# --------------------------------------------------------------------------- arms
+def run_reference_arm(args, w, name):
+    """The reference's CPU computation of the op on the host cores (rank 0 only)."""
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    import torch
+    from oracle import reference_ops as R
+    cores = R.host_threads()
+    torch.set_num_threads(cores)
+    g = torch.Generator().manual_seed(0)
+    if w["kind"] != "gemm":
+        raise SystemExit("the reference arm times the GEMM workloads")
+    N, K = w["N"], w["K"]
+    rows = min(w["M"], 1024)                      # bounded sample: a row block of A, the full B
+    A = R.randn_bf16((rows, K), g, w["std"])
+    B = R.randn_bf16((N, K), g, w["std"])
+    for _ in range(max(1, min(args.warmup, 3))):
+        R.gemm_ref(A, B, 1)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        R.gemm_ref(A, B, 1)
+    dt = time.perf_counter() - t0
+    value = 2.0 * rows * N * K * args.steps / dt / 1e12
+    sample = f"rows 0..{rows} of A ({rows}x{K}) times the full B ({N}x{K}) per step, fp32 torch.mm on CPU"
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "TFLOP/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "fp32 on CPU (bf16 inputs)", "data": "synthetic",
+        "config": {"workload": name, **{k: v for k, v in w.items() if k != "kind"}, "sample": sample},
+        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }), flush=True)
+
+
+def measure_workload(name, w, steps, warmup, dist_on, device, world, peaks):
+    ins, outs = make_inputs(w, device, seed=1000 + int(os.environ.get("RANK", "0")))
+    step = make_step(w, ins, outs)
+    ms = time_steps(step, steps, warmup, dist_on, device)
+    per = ms / steps
+    tf = flops_of(w) * world / per / 1e9
+    rec = {"workload": name, "ms_per_step": per, "tflops": tf, "tflops_per_gpu": tf / world,
+           "frac_of_nominal_2250": tf / world / NOMINAL_TFLOPS,
+           "frac_of_measured_burst": tf / world / peaks["bf16_tflops"],
+           "hbm_gbs_per_gpu": bytes_of(w) / per / 1e6,
+           "frac_of_measured_hbm": bytes_of(w) / per / 1e6 / peaks["hbm_gbs"]}
+    del ins, outs
+    return rec
+
+
+def run_gpu_arm(args, w, name):
+    import torch
+    from warpir_b200 import runtime
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    dist_on = world > 1
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: there is no CPU path")
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    runtime.load_library()  # raises if the compiled library is missing
+    if dist_on:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=device)
+    peaks, peak_src = load_peaks()
+
+    ins, outs = make_inputs(w, device, seed=1000 + rank)
+    step = make_step(w, ins, outs)
+    sampler = ClockSampler(local)
+    for _ in range(args.warmup):
+        step()
+    sampler.start()
+    ms = time_steps(step, args.steps, 0, dist_on, device)
+    clocks = sampler.stop()
+    runtime.read_status(device)
+    per = ms / args.steps
+    value = flops_of(w) * world / per / 1e9          # TFLOP/s, whole job
+    del ins, outs
+
+    e2e_steps = max(3, min(args.steps, 10))
+    e2e_ms, h2d, d2h = time_e2e(w, e2e_steps, 3, dist_on, device)
+    e2e_value = flops_of(w) * world / (e2e_ms / e2e_steps) / 1e9
+
+    tensor_bound = w["kind"] == "attn" or min(w["M"], w["N"]) > 1024
+    long_region = ms >= 1000.0
+    if tensor_bound:
+        peak = peaks["bf16_tflops_sustained"] if long_region else peaks["bf16_tflops"]
+        achieved = flops_of(w) / per / 1e9
+        roof = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+                "peak_source": f"{peak_src} {'sustained' if long_region else 'burst'} cuBLAS bf16",
+                "frac_of_nominal_2250": achieved / NOMINAL_TFLOPS, "traffic": None}
+    else:
+        achieved = bytes_of(w) / per / 1e6
+        roof = {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                "frac": achieved / peaks["hbm_gbs"], "peak_source": f"{peak_src} copy bandwidth", "traffic": None}
+    roof["kernel"] = "gemm_bf16_sm100" if w["kind"] == "gemm" else "attn_fwd_sm100"
+    roof["algorithmic_per_launch"] = flops_of(w) if tensor_bound else bytes_of(w)
+
+    others = []
+    if args.others:
+        table = workload_table()
+        for oname, ow in table.items():
+            if oname == name:
+                continue
+            k = 20 if flops_of(ow) > 5e10 else 50
+            others.append(measure_workload(oname, ow, k, 5, dist_on, device, world, peaks))
+        runtime.read_status(device)
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu:
+        cpu = cpu_baseline_gemm(w if w["kind"] == "gemm" else workload_table()["gemm_8192"])
+
+    if dist_on:
+        import torch.distributed as dist
+        dist.barrier()
+        dist.destroy_process_group()
+    if rank != 0:
+        return
+    line = {
+        "metric": METRIC,
+        "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": per, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16 (fp32 accumulate)", "data": "synthetic",
+        "config": {"workload": name, **{k: v for k, v in w.items() if k != "kind"},
+                   "sharding": f"{world} independent row blocks of M (B replicated), no collective"
+                   if w["kind"] == "gemm" else f"batch x head slices split over {world} GPUs, no collective",
+                   "l2": "inputs+outputs per step exceed the 126 MB L2" if bytes_of(w) > 126e6
+                   else "working set fits in L2 (not flushed)"},
+        "clocks": clocks, "gpu_launches": args.steps,
+        "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                "steps": e2e_steps, "ms_per_step": e2e_ms / e2e_steps},
+        "roofline": roof,
+        "cpu_baseline": cpu,
+        "frac_of_nominal_2250_per_gpu": value / world / NOMINAL_TFLOPS,
+        "other_workloads": others,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="warpir_b200", choices=["warpir_b200", "reference"])
+    ap.add_argument("--workload", default="gemm_8192", choices=sorted(workload_table()))
+    ap.add_argument("--no-others", dest="others", action="store_false", help="skip the secondary workloads")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    if args.warmup < 3 and args.impl != "reference":
+        args.warmup = 3
+    w = workload_table()[args.workload]
+    if args.impl == "reference":
+        run_reference_arm(args, w, args.workload)
+    else:
+        run_gpu_arm(args, w, args.workload)
+
+
+if __name__ == "__main__":
+    main()

@@ -78,8 +78,9 @@ def attention_slice_ref(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
     kept in fp32, plus the causal mask and the log-sum-exp.  Returns ``(O[S,D], LSE[S])``."""
     q, k, v = q.float(), k.float(), v.float()
     if scale is None:
-        scale = 1.0 / math.sqrt(q.size(-1))
-    scores = (q @ k.T) * scale
+        scores = q @ k.T / math.sqrt(q.size(-1))   # the reference's own spelling
+    else:
+        scores = (q @ k.T) * scale
     if causal:
         Sq, Sk = scores.shape
         keep = torch.ones(Sq, Sk, dtype=torch.bool).tril(diagonal=Sk - Sq)

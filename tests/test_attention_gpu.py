@@ -1,0 +1,112 @@
+"""Attention-forward parity on a B200 vs the CPU oracle.
+
+Tolerances (stated by the workload definition): max |O - O_ref| <= 2e-2 with
+O_ref kept in fp32, max |LSE - LSE_ref| <= 1e-3.
+"""
+import numpy as np
+import pytest
+import torch
+
+from oracle import reference_ops as R
+from warpir_b200 import runtime
+
+pytestmark = pytest.mark.gpu
+
+
+def run_attn(Q, K, V, causal, scale=None, want_lse=True):
+    Qd = Q.cuda()
+    O = torch.full_like(Qd, float("nan"))
+    L = torch.full(Q.shape[:-1], float("nan"), device="cuda") if want_lse else None
+    runtime.launch_attention(Qd, K.cuda(), V.cuda(), O, L, scale, causal)
+    runtime.read_status()
+    return O.cpu(), (L.cpu() if want_lse else None)
+
+
+def check(O, L, O_ref, L_ref):
+    assert not torch.isnan(O.float()).any() and not torch.isnan(L).any()
+    e = R.attention_errors(O, L, O_ref, L_ref)
+    assert e["o_max_abs"] <= R.ATTN_O_ABS_TOL and e["lse_max_abs"] <= R.ATTN_LSE_ABS_TOL, e
+
+
+@pytest.mark.parametrize("tag", ["n256_d64", "n128_d128"])
+def test_reference_golden_vectors(golden_dir, tag, lib):
+    """Single-head [N, D] call, as the reference's launch_attention is used."""
+    z = np.load(golden_dir / "attention_small.npz")
+    Q, K, V, O_gold = (torch.from_numpy(z[f"{tag}_{n}"].view(np.int16).copy()).view(torch.bfloat16) for n in "QKVO")
+    O, _ = run_attn(Q, K, V, False)
+    assert (O.float() - O_gold.float()).abs().max().item() <= R.ATTN_O_ABS_TOL
+
+
+# the reference's sweep: one head, D = 64, N in {64 .. 1024} (tests/test_modal_attention.py:178)
+@pytest.mark.parametrize("n", [64, 128, 256, 512, 1024])
+def test_reference_sweep_single_head(n, lib):
+    Q, K, V = R.attention_inputs(1, 1, n, 64, seed=n)
+    O, L = run_attn(Q, K, V, False)
+    check(O, L, *R.attention_ref(Q, K, V))
+
+
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("D", [64, 128])
+@pytest.mark.parametrize("S", [1, 100, 128, 129, 384, 1000])
+def test_ragged_lengths(S, D, causal, lib):
+    Q, K, V = R.attention_inputs(2, 3, S, D, seed=S + D)
+    O, L = run_attn(Q, K, V, causal)
+    check(O, L, *R.attention_ref(Q, K, V, None, causal))
+
+
+def test_grouped_kv_heads_and_custom_scale(lib):
+    Q, K, V = R.attention_inputs(2, 8, 640, 128, seed=5, Hkv=2)
+    O, L = run_attn(Q, K, V, True, scale=0.05)
+    check(O, L, *R.attention_ref(Q, K, V, 0.05, True))
+
+
+def test_lse_optional(lib):
+    Q, K, V = R.attention_inputs(1, 2, 256, 64, seed=9)
+    O, _ = run_attn(Q, K, V, False, want_lse=False)
+    O_ref, _ = R.attention_ref(Q, K, V)
+    assert (O.float() - O_ref).abs().max().item() <= R.ATTN_O_ABS_TOL
+
+
+def test_large_magnitude_scores_exercise_the_rescale_path(lib):
+    """Scores grow along the sequence so the running max keeps moving by more than
+    the lazy-rescale threshold."""
+    Q, K, V = R.attention_inputs(1, 2, 1024, 128, seed=2)
+    ramp = torch.linspace(0.2, 6.0, 1024).view(1, 1, 1024, 1)
+    K = (K.float() * ramp).bfloat16()
+    O, L = run_attn(Q, K, V, False)
+    check(O, L, *R.attention_ref(Q, K, V))
+
+
+@pytest.mark.parametrize("cfg", [(1, 4, 4096, 128, False), (1, 4, 8192, 128, True), (1, 2, 8192, 64, True)])
+def test_benchmark_shapes_on_sampled_slices(cfg, lib):
+    """Full sequence lengths of the measured workloads, a few batch x head slices
+    checked against the oracle."""
+    B, H, S, D, causal = cfg
+    Q, K, V = R.attention_inputs(B, H, S, D, seed=S)
+    O, L = run_attn(Q, K, V, causal)
+    O_ref, L_ref = R.attention_ref(Q, K, V, None, causal, slices=range(0, B * H, max(1, B * H // 2)))
+    check(O, L, O_ref, L_ref)
+
+
+def test_full_size_property_v_linearity(lib):
+    """Config-4 sized call; softmax rows sum to one, so with V == 1 every output is 1,
+    and the output is linear in V: attn(Q,K,2V) == 2 attn(Q,K,V) exactly in bf16."""
+    B, H, S, D = 4, 16, 4096, 128
+    g = torch.Generator(device="cuda").manual_seed(1)
+    Q = torch.randn(B, H, S, D, generator=g, device="cuda").bfloat16()
+    K = torch.randn(B, H, S, D, generator=g, device="cuda").bfloat16()
+    V = torch.randn(B, H, S, D, generator=g, device="cuda").bfloat16()
+    O1, O2, O3 = torch.empty_like(Q), torch.empty_like(Q), torch.empty_like(Q)
+    runtime.launch_attention(Q, K, V, O1)
+    runtime.launch_attention(Q, K, V * 2, O2)
+    runtime.launch_attention(Q, K, torch.ones_like(V), O3)
+    runtime.read_status()
+    assert torch.equal((O1.float() * 2).bfloat16(), O2)
+    assert (O3.float() - 1).abs().max().item() <= 8e-3
+
+
+def test_rejections(lib):
+    Q = torch.zeros(1, 1, 128, 96, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(runtime.WarpirError) as ei:
+        runtime.launch_attention(Q, Q, Q, torch.empty_like(Q))
+    assert ei.value.code == -3
