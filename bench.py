@@ -325,9 +325,13 @@ def run_gpu_arm(args, w, name):
     value = flops_of(w) * world / per / 1e9          # TFLOP/s, whole job
     del ins, outs
 
-    e2e_steps = max(3, min(args.steps, 10))
-    e2e_ms, h2d, d2h = time_e2e(w, e2e_steps, 3, dist_on, device)
-    e2e_value = flops_of(w) * world / (e2e_ms / e2e_steps) / 1e9
+    e2e = None
+    if args.e2e:
+        e2e_steps = max(3, min(args.steps, 10))
+        e2e_ms, h2d, d2h = time_e2e(w, e2e_steps, 3, dist_on, device)
+        e2e = {"value": flops_of(w) * world / (e2e_ms / e2e_steps) / 1e9, "unit": "TFLOP/s",
+               "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps,
+               "ms_per_step": e2e_ms / e2e_steps}
 
     tensor_bound = w["kind"] == "attn" or min(w["M"], w["N"]) > 1024
     long_region = ms >= 1000.0
@@ -375,8 +379,7 @@ def run_gpu_arm(args, w, name):
                    "l2": "inputs+outputs per step exceed the 126 MB L2" if bytes_of(w) > 126e6
                    else "working set fits in L2 (not flushed)"},
         "clocks": clocks, "gpu_launches": args.steps,
-        "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                "steps": e2e_steps, "ms_per_step": e2e_ms / e2e_steps},
+        "e2e": e2e,
         "roofline": roof,
         "cpu_baseline": cpu,
         "frac_of_nominal_2250_per_gpu": value / world / NOMINAL_TFLOPS,
@@ -393,6 +396,7 @@ def main():
     ap.add_argument("--impl", default="warpir_b200", choices=["warpir_b200", "reference"])
     ap.add_argument("--workload", default="gemm_8192", choices=sorted(workload_table()))
     ap.add_argument("--no-others", dest="others", action="store_false", help="skip the secondary workloads")
+    ap.add_argument("--no-e2e", dest="e2e", action="store_false", help="skip the host-buffer end-to-end leg")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl != "reference":

@@ -1,0 +1,436 @@
+// Host side of the sm_100a kernels: per-device state, argument validation, TMA tensor
+// maps, tile-shape choice and the launches themselves.  Included by the C-ABI library
+// (capi.cu) and by the translation units that the lowering emits for one tile program,
+// so both go through the same code.  Host code only touches CUDA through the runtime
+// API; cuTensorMapEncodeTiled is fetched with cudaGetDriverEntryPoint, so nothing links
+// against libcuda.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <cudaTypedefs.h>
+
+#include <cmath>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+
+#include "../../include/warpir_b200.h"
+#include "attn_fwd_sm100.cuh"
+#include "gemm_sm100.cuh"
+
+namespace wir {
+namespace host {
+
+inline thread_local char g_last_error[256] = "";
+
+inline int fail(int code, const char* fmt, ...) __attribute__((format(printf, 2, 3)));
+inline int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_last_error, sizeof g_last_error, fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+#define WIR_CUDA(expr)                                                                      \
+  do {                                                                                      \
+    cudaError_t e_ = (expr);                                                                \
+    if (e_ != cudaSuccess) return fail(WARPIR_ECUDA, "%s: %s", #expr, cudaGetErrorString(e_)); \
+  } while (0)
+
+constexpr int kMaxDevices = 64;
+
+struct DeviceState {
+  bool ready = false;
+  int sm_count = 0;
+  int* status = nullptr;        // 4 ints
+  float* splitk = nullptr;      // grown on demand
+  size_t splitk_bytes = 0;
+};
+
+inline std::mutex g_mutex;
+inline DeviceState g_dev[kMaxDevices];
+inline PFN_cuTensorMapEncodeTiled_v12000 g_encode = nullptr;
+
+// Makes `device` current for the calling thread for the lifetime of the object.
+struct DeviceGuard {
+  int prev = -1;
+  bool switched = false;
+  cudaError_t err = cudaSuccess;
+  explicit DeviceGuard(int device) {
+    err = cudaGetDevice(&prev);
+    if (err == cudaSuccess && prev != device) {
+      err = cudaSetDevice(device);
+      switched = (err == cudaSuccess);
+    }
+  }
+  ~DeviceGuard() {
+    if (switched) cudaSetDevice(prev);
+  }
+};
+
+inline int get_device_state(int device, DeviceState** out) {
+  if (device < 0 || device >= kMaxDevices) return fail(WARPIR_EDEVICE, "device index %d out of range", device);
+  std::lock_guard<std::mutex> lock(g_mutex);
+  DeviceState& d = g_dev[device];
+  if (!d.ready) {
+    int count = 0;
+    WIR_CUDA(cudaGetDeviceCount(&count));
+    if (device >= count) return fail(WARPIR_EDEVICE, "device index %d but %d devices", device, count);
+    int major = 0;
+    WIR_CUDA(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device));
+    if (major != 10) return fail(WARPIR_EDEVICE, "device %d has compute capability %d.x; sm_100a needed", device, major);
+    WIR_CUDA(cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, device));
+    WIR_CUDA(cudaMalloc(&d.status, 4 * sizeof(int)));
+    WIR_CUDA(cudaMemset(d.status, 0, 4 * sizeof(int)));
+    d.ready = true;
+  }
+  if (g_encode == nullptr) {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q);
+    if (e != cudaSuccess || q != cudaDriverEntryPointSuccess || fn == nullptr)
+      return fail(WARPIR_EDRIVER, "cuTensorMapEncodeTiled not available from this driver");
+    g_encode = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(fn);
+  }
+  *out = &d;
+  return WARPIR_OK;
+}
+
+inline int check_device_ptr(const void* p, const char* name, int device) {
+  if (p == nullptr) return fail(WARPIR_EINVAL, "%s is NULL", name);
+  if (reinterpret_cast<uintptr_t>(p) & 15) return fail(WARPIR_EALIGN, "%s is not 16-byte aligned", name);
+  cudaPointerAttributes attr;
+  cudaError_t e = cudaPointerGetAttributes(&attr, p);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return fail(WARPIR_EDEVICE, "%s: cudaPointerGetAttributes failed", name);
+  }
+  if (attr.type != cudaMemoryTypeDevice && attr.type != cudaMemoryTypeManaged)
+    return fail(WARPIR_EDEVICE, "%s is not device memory", name);
+  if (attr.type == cudaMemoryTypeDevice && attr.device != device)
+    return fail(WARPIR_EDEVICE, "%s lives on device %d, not %d", name, attr.device, device);
+  return WARPIR_OK;
+}
+
+// bf16 tensor map with 128-byte swizzle.  dims/box innermost first; strides in bytes
+// for dims 1.. (dim 0 is contiguous).
+inline int encode_tmap(CUtensorMap* map, const void* base, int rank, const uint64_t* dims,
+                       const uint64_t* strides_bytes, const uint32_t* box);
+
+// Encoding a tensor map costs a few microseconds of host time, which matters for small
+// problems launched back to back; the last few maps of each thread are kept, keyed by
+// everything that goes into the encoding.
+inline int make_tmap(CUtensorMap* map, const void* base, int rank, const uint64_t* dims, const uint64_t* strides_bytes,
+                     const uint32_t* box) {
+  struct Entry {
+    const void* base;
+    int rank;
+    uint64_t dims[3], strides[2];
+    uint32_t box[3];
+    CUtensorMap map;
+  };
+  constexpr int kEntries = 16;
+  static thread_local Entry cache[kEntries];
+  static thread_local int next = 0, used = 0;
+  Entry key{};
+  key.base = base;
+  key.rank = rank;
+  for (int i = 0; i < rank && i < 3; ++i) {
+    key.dims[i] = dims[i];
+    key.box[i] = box[i];
+    if (i > 0) key.strides[i - 1] = strides_bytes[i - 1];
+  }
+  if (rank <= 3) {
+    for (int i = 0; i < used; ++i) {
+      const Entry& e = cache[i];
+      if (e.base == key.base && e.rank == key.rank && !memcmp(e.dims, key.dims, sizeof key.dims) &&
+          !memcmp(e.strides, key.strides, sizeof key.strides) && !memcmp(e.box, key.box, sizeof key.box)) {
+        *map = e.map;
+        return WARPIR_OK;
+      }
+    }
+  }
+  if (int rc = encode_tmap(map, base, rank, dims, strides_bytes, box)) return rc;
+  if (rank <= 3) {
+    key.map = *map;
+    cache[next] = key;
+    next = (next + 1) % kEntries;
+    if (used < kEntries) ++used;
+  }
+  return WARPIR_OK;
+}
+
+inline int encode_tmap(CUtensorMap* map, const void* base, int rank, const uint64_t* dims,
+                       const uint64_t* strides_bytes, const uint32_t* box) {
+  cuuint64_t gdims[5];
+  cuuint64_t gstrides[4];
+  cuuint32_t gbox[5];
+  cuuint32_t estr[5];
+  for (int i = 0; i < rank; ++i) {
+    gdims[i] = dims[i];
+    gbox[i] = box[i];
+    estr[i] = 1;
+    if (i > 0) gstrides[i - 1] = strides_bytes[i - 1];
+  }
+  CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, rank, const_cast<void*>(base), gdims, gstrides, gbox,
+                        estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(WARPIR_EDRIVER, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+  return WARPIR_OK;
+}
+
+// Raises a kernel's dynamic shared-memory limit, once per (kernel, device).
+inline int opt_in_smem(const void* kernel, int bytes) {
+  struct Seen { const void* fn; int device; };
+  static thread_local Seen seen[32];
+  static thread_local int n_seen = 0;
+  int device = 0;
+  WIR_CUDA(cudaGetDevice(&device));
+  for (int i = 0; i < n_seen; ++i)
+    if (seen[i].fn == kernel && seen[i].device == device) return WARPIR_OK;
+  WIR_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+  if (n_seen < 32) seen[n_seen++] = Seen{kernel, device};
+  return WARPIR_OK;
+}
+
+// ------------------------------------------------------------------------ GEMM
+using GemmLaunchFn = int (*)(const CUtensorMap&, const CUtensorMap&, const wir::GemmParams&, int, cudaStream_t);
+
+template <int BN, int STAGES, bool B_MN>
+int launch_gemm_cfg(const CUtensorMap& ta, const CUtensorMap& tb, const wir::GemmParams& p, int grid,
+                    cudaStream_t stream) {
+  auto kernel = wir::gemm_bf16_sm100<BN, STAGES, B_MN>;
+  constexpr int smem = wir::GemmSmem<BN, STAGES>::kDynamicBytes;
+  static_assert(smem <= 232448, "shared memory budget");
+  static_assert(smem > 116 * 1024, "one CTA per SM is what keeps the tensor-memory allocation from blocking");
+  if (int rc = opt_in_smem(reinterpret_cast<const void*>(kernel), smem)) return rc;
+  kernel<<<grid, wir::kGemmThreads, smem, stream>>>(ta, tb, p);
+  WIR_CUDA(cudaGetLastError());
+  return WARPIR_OK;
+}
+
+struct GemmChoice {
+  int block_n;
+  int splits;
+};
+
+// Tile width: the widest tile keeps the tensor core busiest per byte of shared-memory
+// traffic, but the tile count must fill the SMs.  Score = fraction of SM-waves that do
+// useful work x relative MMA efficiency of the tile width.
+inline GemmChoice choose_gemm(int64_t M, int64_t N, int64_t K, int sms) {
+  const int cands[3] = {256, 128, 64};
+  const double eff[3] = {1.0, 0.92, 0.72};
+  const int64_t tm = (M + wir::kGemmBM - 1) / wir::kGemmBM;
+  double best = -1.0;
+  GemmChoice c{256, 1};
+  for (int i = 0; i < 3; ++i) {
+    const int64_t tiles = tm * ((N + cands[i] - 1) / cands[i]);
+    const int64_t waves = (tiles + sms - 1) / sms;
+    const double score = eff[i] * static_cast<double>(tiles) / static_cast<double>(waves * sms);
+    if (score > best + 1e-9) {
+      best = score;
+      c.block_n = cands[i];
+    }
+  }
+  (void)K;
+  return c;
+}
+
+// `fixed`: when not null, the instantiation to launch (with `block_n` its tile width); used by
+// the translation units the lowering emits, which pin tile width and ring depth.
+inline int gemm_impl(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K, int b_layout, int block_n,
+                     int splits, int device, void* cuda_stream, GemmLaunchFn fixed = nullptr) {
+  g_last_error[0] = 0;
+  if (M < 0 || N < 0 || K < 0) return fail(WARPIR_EINVAL, "negative size");
+  if (b_layout != 0 && b_layout != 1) return fail(WARPIR_EINVAL, "b_layout must be 0 or 1");
+  if (block_n != 0 && block_n != 64 && block_n != 128 && block_n != 256)
+    return fail(WARPIR_EINVAL, "block_n must be 0, 64, 128 or 256");
+  if (splits < 0 || splits > 64) return fail(WARPIR_EINVAL, "splits must be in [0, 64]");
+  if (M > INT32_MAX / 2 || N > INT32_MAX / 2 || K > INT32_MAX / 2) return fail(WARPIR_ESHAPE, "size above 2^30");
+  if (M == 0 || N == 0) return WARPIR_OK;
+  DeviceState* dev = nullptr;
+  if (int rc = get_device_state(device, &dev)) return rc;
+  if (int rc = check_device_ptr(C, "C", device)) return rc;
+  cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+  DeviceGuard guard(device);
+  if (guard.err != cudaSuccess) return fail(WARPIR_ECUDA, "cudaSetDevice(%d): %s", device, cudaGetErrorString(guard.err));
+  if (K == 0) {
+    WIR_CUDA(cudaMemsetAsync(C, 0, static_cast<size_t>(M) * N * 2, stream));
+    return WARPIR_OK;
+  }
+  if (int rc = check_device_ptr(A, "A", device)) return rc;
+  if (int rc = check_device_ptr(B, "B", device)) return rc;
+  if (K % 8 != 0) return fail(WARPIR_ESHAPE, "K = %lld: the row pitch of A must be a multiple of 16 bytes (K %% 8 == 0)", (long long)K);
+  if (b_layout == 0 && N % 8 != 0) return fail(WARPIR_ESHAPE, "N = %lld: with B stored [K,N] its row pitch must be a multiple of 16 bytes (N %% 8 == 0)", (long long)N);
+
+  GemmChoice ch = choose_gemm(M, N, K, dev->sm_count);
+  if (block_n != 0) ch.block_n = block_n;
+  if (splits != 0) ch.splits = splits;
+  const int num_kb = static_cast<int>((K + wir::kGemmBK - 1) / wir::kGemmBK);
+  if (ch.splits > num_kb) ch.splits = num_kb;
+  if (ch.splits > 1 && N % 4 != 0) ch.splits = 1;  // the reduce pass works on groups of four columns
+
+  wir::GemmParams p;
+  p.M = static_cast<int>(M);
+  p.N = static_cast<int>(N);
+  p.K = static_cast<int>(K);
+  p.ldc = p.N;
+  p.tiles_m = static_cast<int>((M + wir::kGemmBM - 1) / wir::kGemmBM);
+  p.tiles_n = static_cast<int>((N + ch.block_n - 1) / ch.block_n);
+  p.num_kb = num_kb;
+  p.kb_per_split = (num_kb + ch.splits - 1) / ch.splits;
+  p.splits = (num_kb + p.kb_per_split - 1) / p.kb_per_split;  // no empty split
+  p.C = static_cast<__nv_bfloat16*>(C);
+  p.partial = nullptr;
+  p.status = dev->status;
+
+  if (p.splits > 1) {
+    const size_t need = static_cast<size_t>(p.splits) * M * N * sizeof(float);
+    std::lock_guard<std::mutex> lock(g_mutex);
+    if (dev->splitk_bytes < need) {
+      if (dev->splitk) {
+        WIR_CUDA(cudaDeviceSynchronize());
+        WIR_CUDA(cudaFree(dev->splitk));
+        dev->splitk = nullptr;
+        dev->splitk_bytes = 0;
+      }
+      if (cudaMalloc(&dev->splitk, need) != cudaSuccess) {
+        cudaGetLastError();
+        return fail(WARPIR_ENOMEM, "split-K scratch of %zu bytes", need);
+      }
+      dev->splitk_bytes = need;
+    }
+    p.partial = dev->splitk;
+  }
+
+  CUtensorMap ta, tb;
+  {
+    const uint64_t dims[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(M)};
+    const uint64_t strides[1] = {static_cast<uint64_t>(K) * 2};
+    const uint32_t box[2] = {wir::kGemmBK, wir::kGemmBM};
+    if (int rc = make_tmap(&ta, A, 2, dims, strides, box)) return rc;
+  }
+  if (b_layout == 1) {
+    const uint64_t dims[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(N)};
+    const uint64_t strides[1] = {static_cast<uint64_t>(K) * 2};
+    const uint32_t box[2] = {wir::kGemmBK, static_cast<uint32_t>(ch.block_n)};
+    if (int rc = make_tmap(&tb, B, 2, dims, strides, box)) return rc;
+  } else {
+    const uint64_t dims[2] = {static_cast<uint64_t>(N), static_cast<uint64_t>(K)};
+    const uint64_t strides[1] = {static_cast<uint64_t>(N) * 2};
+    const uint32_t box[2] = {64, wir::kGemmBK};
+    if (int rc = make_tmap(&tb, B, 2, dims, strides, box)) return rc;
+  }
+
+  const int64_t work = static_cast<int64_t>(p.tiles_m) * p.tiles_n * p.splits;
+  const int grid = static_cast<int>(work < dev->sm_count ? work : dev->sm_count);
+  int rc;
+  const bool mn = (b_layout == 0);
+  if (fixed != nullptr) rc = fixed(ta, tb, p, grid, stream);
+  else switch (ch.block_n) {
+    case 256: rc = mn ? launch_gemm_cfg<256, 4, true>(ta, tb, p, grid, stream) : launch_gemm_cfg<256, 4, false>(ta, tb, p, grid, stream); break;
+    case 128: rc = mn ? launch_gemm_cfg<128, 6, true>(ta, tb, p, grid, stream) : launch_gemm_cfg<128, 6, false>(ta, tb, p, grid, stream); break;
+    default:  rc = mn ? launch_gemm_cfg<64, 8, true>(ta, tb, p, grid, stream) : launch_gemm_cfg<64, 8, false>(ta, tb, p, grid, stream); break;
+  }
+  if (rc) return rc;
+  if (p.splits > 1) {
+    const size_t total4 = (static_cast<size_t>(M) * N) >> 2;
+    int blocks = static_cast<int>((total4 + 255) / 256);
+    if (blocks > dev->sm_count * 8) blocks = dev->sm_count * 8;
+    wir::splitk_reduce_bf16<<<blocks, 256, 0, stream>>>(p.partial, p.C, p.M, p.N, p.ldc, p.splits);
+    WIR_CUDA(cudaGetLastError());
+  }
+  return WARPIR_OK;
+}
+
+// ------------------------------------------------------------------------ attention
+template <int D, bool CAUSAL>
+int launch_attn_cfg(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const wir::AttnParams& p,
+                    cudaStream_t stream) {
+  auto kernel = wir::attn_fwd_sm100<D, CAUSAL>;
+  constexpr int smem = wir::AttnSmem<D>::kDynamicBytes;
+  static_assert(smem <= 232448, "shared memory budget");
+  static_assert(smem > 116 * 1024, "one CTA per SM is what keeps the tensor-memory allocation from blocking");
+  if (int rc = opt_in_smem(reinterpret_cast<const void*>(kernel), smem)) return rc;
+  const int pairs = (p.S + 2 * wir::kAttnBQ - 1) / (2 * wir::kAttnBQ);
+  dim3 grid(pairs, p.H, p.B);
+  kernel<<<grid, wir::kAttnThreads, smem, stream>>>(tq, tk, tv, p);
+  WIR_CUDA(cudaGetLastError());
+  return WARPIR_OK;
+}
+
+
+inline int attn_impl(const void* Q, const void* K, const void* V, void* O, float* LSE, int64_t B, int64_t Hq,
+                     int64_t Hkv, int64_t S, int64_t D, float softmax_scale, int causal, int device,
+                     void* cuda_stream) {
+  g_last_error[0] = 0;
+  if (B < 0 || Hq < 0 || Hkv < 0 || S < 0) return fail(WARPIR_EINVAL, "negative size");
+  if (D != 64 && D != 128) return fail(WARPIR_ESHAPE, "D = %lld: head dimension must be 64 or 128", (long long)D);
+  if (B == 0 || Hq == 0 || S == 0) return WARPIR_OK;
+  if (Hkv <= 0 || Hq % Hkv != 0) return fail(WARPIR_ESHAPE, "Hq = %lld must be a positive multiple of Hkv = %lld", (long long)Hq, (long long)Hkv);
+  if (!(softmax_scale > 0.f) || !std::isfinite(softmax_scale)) return fail(WARPIR_EINVAL, "softmax_scale must be positive and finite");
+  if (B > 65535 || Hq > 65535) return fail(WARPIR_ESHAPE, "B and Hq must be at most 65535");
+  if (S > (1 << 24) || B * Hq * S > INT32_MAX) return fail(WARPIR_ESHAPE, "sequence too long");
+  DeviceState* dev = nullptr;
+  if (int rc = get_device_state(device, &dev)) return rc;
+  if (int rc = check_device_ptr(Q, "Q", device)) return rc;
+  if (int rc = check_device_ptr(K, "K", device)) return rc;
+  if (int rc = check_device_ptr(V, "V", device)) return rc;
+  if (int rc = check_device_ptr(O, "O", device)) return rc;
+  if (LSE != nullptr)
+    if (int rc = check_device_ptr(LSE, "LSE", device)) return rc;
+  cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+  DeviceGuard guard(device);
+  if (guard.err != cudaSuccess) return fail(WARPIR_ECUDA, "cudaSetDevice(%d): %s", device, cudaGetErrorString(guard.err));
+
+  CUtensorMap tq, tk, tv;
+  const uint32_t box[3] = {64, 128, 1};
+  {
+    const uint64_t dims[3] = {static_cast<uint64_t>(D), static_cast<uint64_t>(S), static_cast<uint64_t>(B * Hq)};
+    const uint64_t strides[2] = {static_cast<uint64_t>(D) * 2, static_cast<uint64_t>(S) * D * 2};
+    if (int rc = make_tmap(&tq, Q, 3, dims, strides, box)) return rc;
+  }
+  {
+    const uint64_t dims[3] = {static_cast<uint64_t>(D), static_cast<uint64_t>(S), static_cast<uint64_t>(B * Hkv)};
+    const uint64_t strides[2] = {static_cast<uint64_t>(D) * 2, static_cast<uint64_t>(S) * D * 2};
+    if (int rc = make_tmap(&tk, K, 3, dims, strides, box)) return rc;
+    if (int rc = make_tmap(&tv, V, 3, dims, strides, box)) return rc;
+  }
+  wir::AttnParams p;
+  p.B = static_cast<int>(B);
+  p.H = static_cast<int>(Hq);
+  p.Hkv = static_cast<int>(Hkv);
+  p.S = static_cast<int>(S);
+  p.D = static_cast<int>(D);
+  p.scale_log2 = softmax_scale * 1.4426950408889634f;
+  p.O = static_cast<__nv_bfloat16*>(O);
+  p.LSE = LSE;
+  p.status = dev->status;
+  if (D == 128) return causal ? launch_attn_cfg<128, true>(tq, tk, tv, p, stream) : launch_attn_cfg<128, false>(tq, tk, tv, p, stream);
+  return causal ? launch_attn_cfg<64, true>(tq, tk, tv, p, stream) : launch_attn_cfg<64, false>(tq, tk, tv, p, stream);
+}
+
+inline int read_status_impl(int device, void* cuda_stream, int* code, int* detail) {
+  g_last_error[0] = 0;
+  DeviceState* dev = nullptr;
+  if (int rc = get_device_state(device, &dev)) return rc;
+  DeviceGuard guard(device);
+  if (guard.err != cudaSuccess) return fail(WARPIR_ECUDA, "cudaSetDevice(%d): %s", device, cudaGetErrorString(guard.err));
+  cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+  int host[4] = {0, 0, 0, 0};
+  WIR_CUDA(cudaStreamSynchronize(stream));
+  WIR_CUDA(cudaMemcpy(host, dev->status, sizeof host, cudaMemcpyDeviceToHost));
+  if (host[0] != 0) WIR_CUDA(cudaMemset(dev->status, 0, sizeof host));
+  if (code) *code = host[0];
+  if (detail) *detail = host[2];
+  if (host[0] != 0)
+    return fail(WARPIR_EKERNEL, "kernel status %d: cta %d role %d tag %d detail %d", host[0], host[1], host[2] >> 16,
+                host[2] & 0xffff, host[3]);
+  return WARPIR_OK;
+}
+
+}  // namespace host
+}  // namespace wir
