@@ -1,0 +1,91 @@
+"""Lowering: program recognition, parameters read off the IR, emitted text (CPU only)."""
+import dataclasses
+
+import pytest
+
+from warpir_b200 import ir
+from warpir_b200.ir import ForOp, Kernel
+from warpir_b200.lowering import Sm100Lowerer, ThunderKittensLowerer
+from warpir_b200.lowering.lowering import AttentionPlan, GemmPlan, analyze
+from warpir_b200.passes.modulo_scheduler import REFERENCE_MODEL, kernel_pass
+from warpir_b200.programs import build_attention_kernel, build_gemm_kernel
+
+
+def test_alias_and_statelessness():
+    assert ThunderKittensLowerer is Sm100Lowerer
+    import warpir.lowering
+    assert warpir.lowering.ThunderKittensLowerer is Sm100Lowerer
+    L = Sm100Lowerer()
+    a = L.lower(build_gemm_kernel())
+    L.lower(build_attention_kernel())
+    assert L.lower(build_gemm_kernel()) == a
+
+
+def test_reference_gemm_program_is_retiled():
+    p = analyze(build_gemm_kernel())
+    assert isinstance(p, GemmPlan) and p.tile_as_written == (64, 64, 64) and p.b_row_major
+    assert p.block_n == 0 and (p.a, p.b, p.c) == ("A", "B", "C_global")
+    assert (p.row_builtin, p.col_builtin) == ("blockIdx.y", "blockIdx.x")
+    src = Sm100Lowerer().lower(build_gemm_kernel())
+    assert 'extern "C" int gemm_launch(' in src and "/*b_layout=*/0" in src
+    assert "%c_new: reg_tile<fp32, 16x64, row_major> = mma(" in src      # the IR is quoted in the header comment
+
+
+def test_reference_pipelined_program_lowers_too():
+    p = analyze(kernel_pass(build_gemm_kernel(), REFERENCE_MODEL))
+    assert p.pipelined_in_ir and p.b_row_major and p.block_n == 0
+
+
+@pytest.mark.parametrize("bn,stages", [(256, 4), (128, 6), (64, 8)])
+@pytest.mark.parametrize("pipelined", [False, True])
+def test_hardware_tiles_are_instantiated_as_written(bn, stages, pipelined):
+    k = build_gemm_kernel(128, bn, 64, b_k_major=True)
+    if pipelined:
+        k = kernel_pass(k)
+    L = Sm100Lowerer()
+    src = L.lower(k)
+    assert L.plan.block_n == bn and L.plan.stages == stages and not L.plan.b_row_major
+    assert f"launch_gemm_cfg<{bn}, {stages}, false>" in src and "/*b_layout=*/1" in src
+
+
+def test_attention_parameters():
+    p = analyze(build_attention_kernel())
+    assert isinstance(p, AttentionPlan) and p.head_dim == 64 and p.tile_as_written == (64, 64)
+    assert abs(p.softmax_scale - 0.125) < 1e-9
+    p = analyze(build_attention_kernel(128, 128, 128, scale=0.3))
+    assert p.head_dim == 128 and p.exp2_scale == 0.3
+    src = Sm100Lowerer().lower(build_attention_kernel())
+    assert 'extern "C" int attention_fwd_launch(' in src and "attn_impl(" in src
+
+
+def _replace_loop_body(k: Kernel, fn) -> Kernel:
+    body = []
+    for o in k.body:
+        if isinstance(o, ForOp):
+            o = dataclasses.replace(o, body=tuple(fn(list(o.body))))
+        body.append(o)
+    return dataclasses.replace(k, body=tuple(body))
+
+
+def test_unknown_programs_are_rejected_not_guessed():
+    g = build_gemm_kernel()
+    with pytest.raises(NotImplementedError):                 # no loop at all
+        analyze(Kernel("k", g.inputs, g.outputs, tuple(o for o in g.body if not isinstance(o, ForOp))))
+    with pytest.raises(NotImplementedError, match="zero-initialised"):
+        analyze(dataclasses.replace(g, body=g.body[1:]))
+    with pytest.raises(NotImplementedError, match="transpose_b"):
+        analyze(_replace_loop_body(g, lambda b: [dataclasses.replace(o, transpose_b=True)
+                                                  if isinstance(o, ir.MMAOp) else o for o in b]))
+    a = build_attention_kernel()
+    with pytest.raises(NotImplementedError, match="row sum"):
+        analyze(_replace_loop_body(a, lambda b: [o for o in b if not isinstance(o, ir.RowSumOp)]))
+    with pytest.raises(NotImplementedError, match="head dimension"):
+        analyze(build_attention_kernel(head_dim=32))
+
+
+def test_emitted_source_compiles_for_sm100a():
+    from warpir_b200 import runtime
+    k = runtime.load(build_gemm_kernel())
+    assert k.kind == "gemm" and k.path.exists() and hasattr(k, "launch_gemm")
+    k = runtime.load(build_attention_kernel())
+    assert k.kind == "attention" and hasattr(k, "launch_attention")

@@ -172,3 +172,114 @@ def read_status(device=None) -> None:
     rc = lib.warpir_read_status(dev.index, torch.cuda.current_stream(dev).cuda_stream,
                                 ctypes.byref(code), ctypes.byref(detail))
     _check(rc)
+
+
+# --------------------------------------------------------------------------- lowered programs
+_JIT_DIR = Path(__file__).resolve().parent / "_jit"
+
+
+class LoadedKernel:
+    """A compiled translation unit emitted by ``Sm100Lowerer``, callable on torch tensors.
+
+    Stands in for the module the reference gets from ``load_inline`` plus its
+    hand-written launch wrapper: ``mod.launch_gemm(A, B, C)`` /
+    ``mod.launch_attention(Q, K, V, O)`` work as there (tensors in kernel-signature
+    order, outputs pre-allocated, asynchronous on the current stream).
+    """
+
+    def __init__(self, so_path: Path, name: str):
+        self.path = so_path
+        self.name = name
+        self._dll = ctypes.CDLL(str(so_path))
+        vp, ci = ctypes.c_void_p, ctypes.c_int
+        self._launch = getattr(self._dll, f"{name}_launch")
+        self._launch.restype = ci
+        self._launch.argtypes = [ctypes.POINTER(vp), ctypes.POINTER(ctypes.c_int64),
+                                 ctypes.POINTER(ctypes.c_int64), ci, vp]
+        self._err = getattr(self._dll, f"{name}_last_error")
+        self._err.restype = ctypes.c_char_p
+        kind = getattr(self._dll, f"{name}_kind")
+        kind.restype = ctypes.c_char_p
+        self.kind = kind().decode()
+        self._status = getattr(self._dll, f"{name}_read_status")
+        self._status.restype = ci
+        self._status.argtypes = [ci, vp, ctypes.POINTER(ci), ctypes.POINTER(ci)]
+        if self.kind == "gemm":
+            self.launch_gemm = self.__call__
+        else:
+            self.launch_attention = self.__call__
+
+    def __call__(self, *tensors, causal: bool = False, LSE=None) -> None:
+        import torch
+        for i, t in enumerate(tensors):
+            _require(t, f"tensor {i}", torch.bfloat16)
+        dev = tensors[0].device
+        if any(t.device != dev for t in tensors):
+            raise ValueError("all tensors must be on one device")
+        n = len(tensors)
+        ptrs = (ctypes.c_void_p * (n + 1))(*[t.data_ptr() for t in tensors], None)
+        if LSE is not None:
+            _require(LSE, "LSE", torch.float32)
+            ptrs[n] = LSE.data_ptr()
+        flat = []
+        for t in tensors:
+            shape = list(t.shape)
+            if len(shape) > 4:
+                raise ValueError("tensors have at most four dimensions")
+            flat += [1] * (4 - len(shape)) + shape
+        dims = (ctypes.c_int64 * len(flat))(*flat)
+        # the program's int inputs (its loop extent) are implied by the tensor shapes
+        scalars = (ctypes.c_int64 * 4)(int(tensors[0].shape[-1]), int(bool(causal)), 0, 0)
+        if self.kind == "attention":
+            scalars[0] = int(tensors[0].shape[-2])
+        rc = self._launch(ptrs, dims, scalars, dev.index, _stream_of(tensors[0]))
+        if rc != 0:
+            raise WarpirError(rc, load_library().warpir_strerror(rc).decode(), self._err().decode())
+
+    def read_status(self, device=None) -> None:
+        import torch
+        dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        code, detail = ctypes.c_int(0), ctypes.c_int(0)
+        rc = self._status(dev.index, torch.cuda.current_stream(dev).cuda_stream, ctypes.byref(code),
+                          ctypes.byref(detail))
+        if rc != 0:
+            raise WarpirError(rc, load_library().warpir_strerror(rc).decode(), self._err().decode())
+
+
+def compile_source(source: str, name: str) -> Path:
+    """nvcc the emitted translation unit for sm_100a into ``warpir_b200/_jit`` (cached by
+    content hash, in-tree so the built file travels with the checkout)."""
+    import hashlib
+    import subprocess
+    from . import build as _build
+    repo_root = Path(__file__).resolve().parent.parent
+    deps = "".join(f.read_text() for f in sorted((repo_root / "warpir_b200" / "csrc").glob("*.cuh")))
+    digest = hashlib.sha256((source + deps).encode()).hexdigest()[:16]
+    _JIT_DIR.mkdir(exist_ok=True)
+    so = _JIT_DIR / f"{name}_{digest}.so"
+    if so.exists():
+        return so
+    cu = _JIT_DIR / f"{name}_{digest}.cu"
+    cu.write_text(source)
+    cmd = [_build.find_nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+           "-shared", "-Xcompiler", "-fPIC", "-I", str(repo_root), "-o", str(so), str(cu)]
+    proc = subprocess.run(cmd, capture_output=True, text=True)
+    if proc.returncode != 0:
+        raise RuntimeError(f"nvcc failed on the emitted source:\n{proc.stdout}{proc.stderr}")
+    return so
+
+
+def load(kernel_or_source, name: Optional[str] = None) -> LoadedKernel:
+    """Lower (if given a ``Kernel``), compile and load a tile program.
+
+    Replaces the reference's ``lower`` + ``load_inline`` + launch-wrapper sequence
+    (tests/test_gemm_baseline.py:52-74)."""
+    if isinstance(kernel_or_source, str):
+        if name is None:
+            raise ValueError("name= is needed when loading emitted source text")
+        source = kernel_or_source
+    else:
+        from .lowering import Sm100Lowerer
+        source = Sm100Lowerer().lower(kernel_or_source)
+        name = kernel_or_source.name
+    return LoadedKernel(compile_source(source, name), name)
