@@ -86,6 +86,42 @@ int warpir_gemm_bf16_ex(const void* A, const void* B, void* C, int64_t M, int64_
                         int b_layout, int block_n, int splits, int device, void* cuda_stream);
 
 /*
+ * Split-K GEMM for callers that must not allocate device memory.
+ *
+ * Some hosts cannot tolerate a cudaMalloc coming out of a library call: a serving process
+ * that handed the whole GPU to its own memory pool at start-up (a later cudaMalloc simply
+ * fails, or succeeds only by fragmenting what the pool left over), a latency-critical
+ * loop where the implicit device synchronisation of cudaMalloc/cudaFree is not
+ * acceptable, or code running under a memory budget fixed at load time.
+ * warpir_gemm_bf16_ex with splits > 1 grows a scratch buffer on demand and
+ * warpir_gemm_bf16 allocates its status words on first use, so neither is usable there.
+ *
+ * This entry point computes exactly what warpir_gemm_bf16_ex(A, B, C, M, N, K, b_layout,
+ * block_n, splits, ...) computes -- same kernels, same fixed reduction order, bit-identical
+ * C -- but keeps the fp32 partial sums (and its kernel status words) in a statically
+ * allocated device array that is part of the library image.  It calls no cudaMalloc,
+ * cudaFree or any other allocating routine.  Consequences:
+ *  - every GPU whose context loads this library holds WARPIR_NOALLOC_SCRATCH_BYTES
+ *    (16 MiB) for that array until the process exits, whether or not this function is used;
+ *  - splits * M * N * 4 bytes must fit in it; larger problems are rejected with
+ *    WARPIR_ESHAPE and a message naming the limit (nothing is launched);
+ *  - the first call on a device looks up the array's device address (one
+ *    cudaGetSymbolAddress); make that first call before starting any stream capture;
+ *  - all calls on a device share the one array and it keeps the previous call's
+ *    contents.  Nothing in it needs clearing between calls (every partial sum that is
+ *    read has been written by the same call), but two calls that overlap on the GPU --
+ *    different streams, or different host threads -- race on it: serialise them;
+ *  - a bounded wait that runs out inside these launches is recorded in the static
+ *    status words, not in the ones warpir_read_status reports.
+ * block_n is 0 (choose), 64, 128 or 256; splits is >= 1.  Other arguments, size rules
+ * and return codes are those of warpir_gemm_bf16.
+ * This function has no counterpart in the reference.
+ */
+#define WARPIR_NOALLOC_SCRATCH_BYTES (16u << 20)
+int warpir_gemm_bf16_splitk_noalloc(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K,
+                                    int b_layout, int block_n, int splits, int device, void* cuda_stream);
+
+/*
  * Attention forward: O[b,h] = softmax(softmax_scale * Q[b,h] K[b,hk]^T (+ causal mask)) V[b,hk],
  * LSE[b,h,i] = log sum_j exp(softmax_scale * q_i . k_j) (natural log), hk = h / (Hq / Hkv).
  *   Q, O: [B, Hq, S, D] bf16, contiguous;  K, V: [B, Hkv, S, D] bf16, contiguous;
