@@ -10,15 +10,21 @@
 // K/V ring, a producer warpgroup and causal / 4-D / log-sum-exp handling
 // (kernel_examples/attention/mha_h100.cu:52-232).  Here:
 //
-//   warps 0-3, 4-7  one softmax warpgroup per 128-row Q tile (two tiles per CTA, so the
-//                   tensor core works on one tile while the other is in softmax); one
+//   warps 0-3, 4-7  one softmax warpgroup per 128-row Q tile (two tiles per CTA); one
 //                   row per thread, so row max / row sum need no shuffles;
-//   warp 8          MMA issuer: S_t = Q_t K^T and O_t += P_t V as tcgen05.mma into
-//                   tensor memory, P_t read straight from tensor memory;
-//   warp 9          producer: TMA loads of Q (once) and of the K/V tiles into a ring.
+//   warps 8, 9      MMA issuers, one per Q tile: S_t = Q_t K^T and O_t += P_t V as
+//                   tcgen05.mma into tensor memory, P_t read straight from tensor memory;
+//   warp 10         producer: TMA loads of Q (once) and of the K/V tiles into a ring.
 //
-// Tensor memory (512 columns): S_0, S_1 (128 each; P_t overwrites the low 64 columns
-// of S_t as packed bf16) and O_0, O_1 (D columns each).
+// KV tiles are 64 keys.  Tensor memory (512 columns): for each Q tile t two score
+// buffers S_t[0], S_t[1] of 64 columns (t*128 + b*64) and the output accumulator O_t
+// (256 + t*D).  P_t(j), packed bf16, overwrites the low 32 columns of the score buffer
+// it was computed from.  Double-buffering S is what decouples the tensor core from the
+// softmax: Q K^T for KV tile j+1 is issued before the softmax of tile j has finished, so
+// a softmax warpgroup finds its next scores waiting, and the tensor core always has the
+// other tile's (or the next block's) MMAs queued.  MMAs of one CTA execute in issue
+// order, which is what makes the aliasing safe: S_t[b] is rewritten by Q K^T(j+2) only
+// after P V(j), which reads P from it, has been issued.
 //
 // The O rescale is lazy: the running max m is only advanced when some row of the warp
 // saw its max grow by more than 2^8 in the exponent domain; then that warp multiplies
@@ -31,8 +37,9 @@
 namespace wir {
 
 constexpr int kAttnBQ = 128;       // rows of one Q tile = MMA M
-constexpr int kAttnBKV = 128;      // keys per KV tile
-constexpr int kAttnThreads = 320;  // 2 softmax warpgroups + MMA warp + producer warp
+constexpr int kAttnBKV = 64;       // keys per KV tile
+constexpr int kAttnThreads = 352;  // 2 softmax warpgroups (1 per Q tile) + 2 MMA warps + producer warp
+constexpr int kAttnMmaWarp = 8;    // first MMA-issuing warp; the producer is warp kAttnMmaWarp + 2
 constexpr float kRescaleThreshold = 8.0f;
 
 struct AttnParams {
@@ -42,18 +49,21 @@ struct AttnParams {
   __nv_bfloat16* O;        // [B, H, S, D]
   float* LSE;              // [B, H, S] or nullptr
   int* status;
+  unsigned long long* trace;   // event trace buffer of debug builds (-DWIR_TRACE), else unused
 };
 
 template <int D>
 struct AttnSmem {
-  static constexpr int kStages = (D == 128) ? 5 : 8;
-  static constexpr int kChunkBytes = 128 * 128;           // 128 rows x 64 bf16
-  static constexpr int kTileBytes = (D / 64) * kChunkBytes;
+  static constexpr int kStages = (D == 128) ? 10 : 12;
+  static constexpr int kQChunkBytes = kAttnBQ * 128;        // 128 rows x 64 bf16
+  static constexpr int kQTileBytes = (D / 64) * kQChunkBytes;
+  static constexpr int kKVChunkBytes = kAttnBKV * 128;      // 64 rows x 64 bf16
+  static constexpr int kKVTileBytes = (D / 64) * kKVChunkBytes;
   static constexpr int kQOffset = 0;
-  static constexpr int kKVOffset = 2 * kTileBytes;
-  static constexpr int kBarOffset = kKVOffset + kStages * kTileBytes;
-  // q_full, kv_full[S], kv_empty[S], s_full[2], p_full[2], o_full[2], drain
-  static constexpr int kNumBars = 1 + 2 * kStages + 7;
+  static constexpr int kKVOffset = 2 * kQTileBytes;
+  static constexpr int kBarOffset = kKVOffset + kStages * kKVTileBytes;
+  // q_full, kv_full[S], kv_empty[S], s_full[2][2], p_full[2][2], pv_done[2][2], drain[2]
+  static constexpr int kNumBars = 1 + 2 * kStages + 14;
   static constexpr int kTmemPtrOffset = kBarOffset + kNumBars * 8;
   static constexpr int kAbortOffset = kTmemPtrOffset + 4;
   static constexpr int kBytes = kAbortOffset + 4;
@@ -67,7 +77,6 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
   using L = AttnSmem<D>;
   constexpr int STAGES = L::kStages;
   constexpr uint32_t kTmemCols = 512;
-  constexpr uint32_t kSCol = 0;          // S_t at columns t*128
   constexpr uint32_t kOCol = 256;        // O_t at columns 256 + t*D
 
   extern __shared__ uint8_t smem_raw[];
@@ -77,10 +86,10 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
   const uint32_t q_full = bar_base;
   auto kv_full = [&](int s) { return bar_base + 8u * (1 + s); };
   auto kv_empty = [&](int s) { return bar_base + 8u * (1 + STAGES + s); };
-  auto s_full = [&](int t) { return bar_base + 8u * (1 + 2 * STAGES + t); };
-  auto p_full = [&](int t) { return bar_base + 8u * (3 + 2 * STAGES + t); };
-  auto o_full = [&](int t) { return bar_base + 8u * (5 + 2 * STAGES + t); };
-  const uint32_t drain_bar = bar_base + 8u * (7 + 2 * STAGES);
+  auto s_full = [&](int t, int b) { return bar_base + 8u * (1 + 2 * STAGES + 2 * t + b); };
+  auto p_full = [&](int t, int b) { return bar_base + 8u * (5 + 2 * STAGES + 2 * t + b); };
+  auto pv_done = [&](int t, int b) { return bar_base + 8u * (9 + 2 * STAGES + 2 * t + b); };
+  const uint32_t drain_bar = bar_base + 8u * (13 + 2 * STAGES);
   volatile uint32_t* tmem_ptr_slot = reinterpret_cast<volatile uint32_t*>(smem + L::kTmemPtrOffset);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kAbortOffset);
   const AbortCtx ctx{abort_flag, p.status};
@@ -94,33 +103,36 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
   const int bh = batch * p.H + head;
   const int bh_kv = batch * p.Hkv + head / (p.H / p.Hkv);
   const int nkv = (p.S + kAttnBKV - 1) / kAttnBKV;
-  int n_trip[2];
-#pragma unroll
-  for (int t = 0; t < 2; ++t) {
-    const int qt = 2 * pair + t;
-    n_trip[t] = (qt * kAttnBQ >= p.S) ? 0 : (CAUSAL ? min(nkv, qt + 1) : nkv);
-  }
-  const int n_max = max(n_trip[0], n_trip[1]);
+  // KV tiles each Q tile visits (0: the tile lies beyond the sequence)
+  const int qt0 = 2 * pair, qt1 = 2 * pair + 1;
+  const int n0 = (qt0 * kAttnBQ >= p.S) ? 0 : (CAUSAL ? min(nkv, 2 * qt0 + 2) : nkv);
+  const int n1 = (qt1 * kAttnBQ >= p.S) ? 0 : (CAUSAL ? min(nkv, 2 * qt1 + 2) : nkv);
+  const int n_max = max(n0, n1);
+  // position of K(j) / V(j) in the load sequence K0, K1, V0, K2, V1, K3, ...
+  auto k_index = [&](int j) -> uint32_t { return j == 0 ? 0u : static_cast<uint32_t>(2 * j - 1); };
+  auto v_index = [&](int j) -> uint32_t { return static_cast<uint32_t>(j + 1 < n_max ? 2 * j + 2 : 2 * j + 1); };
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     mbar_init(q_full, 1);
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(kv_full(s), 1);
-      mbar_init(kv_empty(s), 1);
+      mbar_init(kv_empty(s), 2);   // one arrival per MMA issuer
     }
-    for (int t = 0; t < 2; ++t) {
-      mbar_init(s_full(t), 1);
-      mbar_init(p_full(t), 128);
-      mbar_init(o_full(t), 1);
-    }
+    for (int t = 0; t < 2; ++t)
+      for (int b = 0; b < 2; ++b) {
+        mbar_init(s_full(t, b), 1);
+        mbar_init(p_full(t, b), 128);
+        mbar_init(pv_done(t, b), 1);
+      }
     mbar_init(drain_bar, 1);
+    mbar_init(drain_bar + 8u, 1);
     fence_mbar_init();
     prefetch_tensormap(&tmap_q);
     prefetch_tensormap(&tmap_k);
     prefetch_tensormap(&tmap_v);
   }
-  if (warp == 8) {
+  if (warp == kAttnMmaWarp) {
     tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_ptr_slot)), kTmemCols);
     tmem_relinquish();
   }
@@ -129,32 +141,36 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
   tc_fence_after();
   const uint32_t tmem_base = *tmem_ptr_slot;
 
-  if (warp == 9) {
+  if (warp == kAttnMmaWarp + 2) {
     // ------------------------------------------------------------------ producer
     if (lane == 0) {
-      const int n_q = (n_trip[0] > 0) + (n_trip[1] > 0);
-      mbar_arrive_expect_tx(q_full, n_q * L::kTileBytes);
+      const int n_q = (n0 > 0) + (n1 > 0);
+      mbar_arrive_expect_tx(q_full, n_q * L::kQTileBytes);
       for (int t = 0; t < 2; ++t)
-        if (n_trip[t] > 0)
+        if ((t == 0 ? n0 : n1) > 0)
 #pragma unroll
           for (int c = 0; c < D / 64; ++c)
-            tma_load_3d(smem_base + L::kQOffset + t * L::kTileBytes + c * L::kChunkBytes, &tmap_q, q_full,
+            tma_load_3d(smem_base + L::kQOffset + t * L::kQTileBytes + c * L::kQChunkBytes, &tmap_q, q_full,
                         c * 64, (2 * pair + t) * kAttnBQ, bh);
       uint32_t idx = 0;
       bool ok = true;
+      auto load_tile = [&](const CUtensorMap* map, int j) -> bool {
+        const int s = idx % STAGES;
+        const uint32_t ph = (idx / STAGES) & 1;
+        if (!mbar_wait(kv_empty(s), ph ^ 1, ctx, kRoleProducer, s, j)) return false;
+        mbar_arrive_expect_tx(kv_full(s), L::kKVTileBytes);
+        const uint32_t dst = smem_base + L::kKVOffset + s * L::kKVTileBytes;
+#pragma unroll
+        for (int c = 0; c < D / 64; ++c)
+          tma_load_3d(dst + c * L::kKVChunkBytes, map, kv_full(s), c * 64, j * kAttnBKV, bh_kv);
+        ++idx;
+        return true;
+      };
+      // K0, then K(j+1) ahead of V(j): the order in which the MMA warp consumes them
+      if (n_max > 0) ok = load_tile(&tmap_k, 0);
       for (int j = 0; ok && j < n_max; ++j) {
-#pragma unroll
-        for (int which = 0; which < 2; ++which, ++idx) {  // K(j) then V(j)
-          const int s = idx % STAGES;
-          const uint32_t ph = (idx / STAGES) & 1;
-          if (!mbar_wait(kv_empty(s), ph ^ 1, ctx, kRoleProducer, s, j)) { ok = false; break; }
-          mbar_arrive_expect_tx(kv_full(s), L::kTileBytes);
-          const uint32_t dst = smem_base + L::kKVOffset + s * L::kTileBytes;
-#pragma unroll
-          for (int c = 0; c < D / 64; ++c)
-            tma_load_3d(dst + c * L::kChunkBytes, which == 0 ? &tmap_k : &tmap_v, kv_full(s), c * 64,
-                        j * kAttnBKV, bh_kv);
-        }
+        if (j + 1 < n_max) ok = load_tile(&tmap_k, j + 1);
+        if (ok) ok = load_tile(&tmap_v, j);
       }
       if (!ok || *abort_flag) {
         mbar_wait_quiet(q_full, 0);
@@ -165,117 +181,141 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
         }
       }
     }
-  } else if (warp == 8) {
-    // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
-      constexpr uint32_t idesc_qk = idesc_bf16_f32(kAttnBQ, kAttnBKV, 0, 0);
-      constexpr uint32_t idesc_pv = idesc_bf16_f32(kAttnBQ, D, 0, 1);
-      bool ok = true;
+  } else if (warp == kAttnMmaWarp || warp == kAttnMmaWarp + 1) {
+    // ------------------------------------------------------------------ MMA issuer of one Q tile
+    // One issuing warp per Q tile.  The whole warp runs the loop (warp-uniform operands), one
+    // elected lane issues; a single issuer for both tiles cannot hide the waits, fences and
+    // commits that surround each group of MMAs.
+    WIR_TRACE_DECL;
+    const int t = warp - kAttnMmaWarp;
+    const int n = (t == 0) ? n0 : n1;
+    constexpr uint32_t idesc_qk = idesc_bf16_f32(kAttnBQ, kAttnBKV, 0, 0);
+    constexpr uint32_t idesc_pv = idesc_bf16_f32(kAttnBQ, D, 0, 1);
+    constexpr uint32_t desc_hi = smem_desc_hi_sw128(1024);
+    const uint32_t q_lo = smem_desc_lo(smem_base + L::kQOffset + t * L::kQTileBytes, 16);
+    const uint32_t o_tmem = tmem_base + kOCol + t * D;
+    bool ok = true;
+    auto kv_addr = [&](uint32_t idx) { return smem_base + L::kKVOffset + (idx % STAGES) * L::kKVTileBytes; };
+    auto wait_kv = [&](uint32_t idx, int tag) {
+      return mbar_wait_warp(kv_full(idx % STAGES), (idx / STAGES) & 1, ctx, kRoleMma, tag, idx);
+    };
+    // every K/V slot is released by BOTH issuers (its empty barrier counts two arrivals); the
+    // issuer whose tile does not visit a block releases it once the block has landed
+    auto skip_tile = [&](uint32_t idx) -> bool {
+      if (!wait_kv(idx, 40 + t)) return false;
+      mbar_arrive_elect(kv_empty(idx % STAGES));
+      return true;
+    };
+    // S_t[j & 1] = Q_t K(j)^T
+    auto issue_qk = [&](int j) -> bool {
+      const uint32_t idx = k_index(j);
+      if (!wait_kv(idx, 10 + t)) return false;
+      tc_fence_after();
+      const uint32_t k_lo = smem_desc_lo(kv_addr(idx), 16);
+      const uint32_t d_tmem = tmem_base + t * 128 + (j & 1) * 64;
+#pragma unroll
+      for (int k = 0; k < D / 16; ++k) {
+        // 16 elements of the head dimension further: 32 bytes inside a 64-element chunk, then the next chunk
+        const uint32_t q_off = ((k / 4) * L::kQChunkBytes + (k % 4) * 32) >> 4;
+        const uint32_t k_off = ((k / 4) * L::kKVChunkBytes + (k % 4) * 32) >> 4;
+        mma_ss_elect(d_tmem, q_lo + q_off, desc_hi, k_lo + k_off, desc_hi, idesc_qk, k > 0 ? 1u : 0u);
+      }
+      mma_commit_elect(s_full(t, j & 1));
+      mma_commit_elect(kv_empty(idx % STAGES));
+      return true;
+    };
 
-      auto kv_stage_addr = [&](uint32_t idx) { return smem_base + L::kKVOffset + (idx % STAGES) * L::kTileBytes; };
-      auto wait_kv = [&](uint32_t idx, int tag) {
-        return mbar_wait(kv_full(idx % STAGES), (idx / STAGES) & 1, ctx, kRoleMma, tag, idx);
-      };
-      // S_t = Q_t K(j)^T
-      auto issue_qk = [&](int t, int j) -> bool {
-        const uint32_t idx = 2 * j;
-        if (!wait_kv(idx, 10 + t)) return false;
+    if (n > 0) ok = mbar_wait_warp(q_full, 0, ctx, kRoleMma, 1, 0);
+    for (int j = 0; ok && j < 2 && j < n_max; ++j) ok = (j < n) ? issue_qk(j) : skip_tile(k_index(j));
+
+    for (int j = 0; ok && j < n_max; ++j) {
+      const uint32_t idx = v_index(j);
+      if (j < n) {
+        // O_t += P_t(j) V(j)
+        if (lane == 0) WIR_TRACE_EVENT(p.trace, 3 * t, 1 + 10 * t, j);
+        if (!mbar_wait_warp(p_full(t, j & 1), (j >> 1) & 1, ctx, kRoleMma, 20 + t, j)) { ok = false; break; }
+        if (lane == 0) WIR_TRACE_EVENT(p.trace, 3 * t, 2 + 10 * t, j);
+        if (!wait_kv(idx, 30 + t)) { ok = false; break; }
         tc_fence_after();
-        const uint32_t q_src = smem_base + L::kQOffset + t * L::kTileBytes;
-        const uint32_t k_src = kv_stage_addr(idx);
+        const uint32_t v_lo = smem_desc_lo(kv_addr(idx), L::kKVChunkBytes);
+        const uint32_t p_tmem = tmem_base + t * 128 + (j & 1) * 64;
 #pragma unroll
-        for (int k = 0; k < D / 16; ++k) {
-          const uint32_t off = (k / 4) * L::kChunkBytes + (k % 4) * 32;
-          mma_ss(tmem_base + kSCol + t * 128, smem_desc_sw128(q_src + off, 16, 1024),
-                 smem_desc_sw128(k_src + off, 16, 1024), idesc_qk, k > 0 ? 1u : 0u);
+        for (int k = 0; k < kAttnBKV / 16; ++k) {
+          // 16 keys further: 8 packed-bf16 columns of P, 16 rows (2048 B) of V
+          mma_ts_elect(o_tmem, p_tmem + k * 8, v_lo + ((k * 2048) >> 4), desc_hi, idesc_pv,
+                       (j > 0 || k > 0) ? 1u : 0u);
         }
-        mma_commit(s_full(t));
-        // K(j) is free once the last tile that needs it has been issued
-        const bool last_user = (t == 1) || !(j < n_trip[1]);
-        if (last_user) mma_commit(kv_empty(idx % STAGES));
-        return true;
-      };
-
-      ok = mbar_wait(q_full, 0, ctx, kRoleMma, 1, 0);
-      for (int t = 0; ok && t < 2; ++t)
-        if (n_trip[t] > 0) ok = issue_qk(t, 0);
-
-      for (int j = 0; ok && j < n_max; ++j) {
-        for (int t = 0; ok && t < 2; ++t) {
-          if (j >= n_trip[t]) continue;
-          // O_t += P_t(j) V(j)
-          if (!mbar_wait(p_full(t), j & 1, ctx, kRoleMma, 20 + t, j)) { ok = false; break; }
-          const uint32_t idx = 2 * j + 1;
-          if (!wait_kv(idx, 30 + t)) { ok = false; break; }
-          tc_fence_after();
-          const uint32_t v_src = kv_stage_addr(idx);
-#pragma unroll
-          for (int k = 0; k < kAttnBKV / 16; ++k) {
-            // 16 keys further: 8 packed-bf16 columns of P, 16 rows (2048 B) of V
-            mma_ts(tmem_base + kOCol + t * D, tmem_base + kSCol + t * 128 + k * 8,
-                   smem_desc_sw128(v_src + k * 2048, L::kChunkBytes, 1024), idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
-          }
-          const bool last_user = (t == 1) || !(j < n_trip[1]);
-          if (last_user) mma_commit(kv_empty(idx % STAGES));
-          if (j + 1 == n_trip[t]) mma_commit(o_full(t));
-          else ok = issue_qk(t, j + 1);
-        }
+        mma_commit_elect(pv_done(t, j & 1));
+        mma_commit_elect(kv_empty(idx % STAGES));
+        if (lane == 0) WIR_TRACE_EVENT(p.trace, 3 * t, 3 + 10 * t, j);
+      } else {
+        ok = skip_tile(idx);
       }
-      if (!ok || *abort_flag) {
-        mma_commit(drain_bar);
-        mbar_wait_quiet(drain_bar, 0);
-      }
+      if (ok && j + 2 < n_max) ok = (j + 2 < n) ? issue_qk(j + 2) : skip_tile(k_index(j + 2));
+      if (lane == 0) WIR_TRACE_EVENT(p.trace, 3 * t, 4 + 10 * t, j);
+    }
+    if (!ok || *abort_flag) {
+      mma_commit_elect(drain_bar + 8u * t);
+      mbar_wait_quiet(drain_bar + 8u * t, 0);
     }
     __syncwarp();
   } else {
     // ------------------------------------------------------------------ softmax + epilogue
     const int t = warp >> 2;            // which Q tile
     const int quarter = warp & 3;       // tensor-memory lanes 32*quarter .. +31
-    const int row_in_tile = quarter * 32 + lane;
-    const int q_row = (2 * pair + t) * kAttnBQ + row_in_tile;
+    const int qt = 2 * pair + t;
+    const int q_row = qt * kAttnBQ + quarter * 32 + lane;
     const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
-    const uint32_t s_addr = lane_base + kSCol + t * 128;
     const uint32_t o_addr = lane_base + kOCol + t * D;
     const float c = p.scale_log2;
-    const int n = n_trip[t];
+    const int n = (t == 0) ? n0 : n1;
+    const int first_masked = CAUSAL ? 2 * qt : (p.S % kAttnBKV != 0 ? nkv - 1 : nkv);
 
+    WIR_TRACE_DECL;
     float m = -INFINITY;  // running (possibly stale) max of the raw scores
     float l = 0.f;        // running sum of 2^(s c - m c)
     bool ok = true;
 
     for (int j = 0; j < n; ++j) {
-      const bool got = mbar_wait(s_full(t), j & 1, ctx, kRoleSoftmax, t, j);
+      const int b = j & 1;
+      const uint32_t s_addr = lane_base + t * 128 + b * 64;
+      if (quarter == 0 && lane == 0) WIR_TRACE_EVENT(p.trace, 1 + t, 100, j);
+      const bool got = mbar_wait(s_full(t, b), (j >> 1) & 1, ctx, kRoleSoftmax, t, j);
       if (!__all_sync(0xffffffffu, got)) { ok = false; break; }
       tc_fence_after();
+      if (quarter == 0 && lane == 0) WIR_TRACE_EVENT(p.trace, 1 + t, 101, j);
 
-      uint32_t sb[128];  // this thread's row of raw scores, as fp32 bit patterns
-#pragma unroll
-      for (int cidx = 0; cidx < 4; ++cidx) tmem_ld32(s_addr + cidx * 32, sb + cidx * 32);
+      uint32_t sb[64];  // this thread's row of raw scores, as fp32 bit patterns
+      tmem_ld32(s_addr, sb);
+      tmem_ld32(s_addr + 32, sb + 32);
       tmem_wait_ld();
+      if (quarter == 0 && lane == 0) WIR_TRACE_EVENT(p.trace, 1 + t, 102, j);
 #define WIR_S(i) __uint_as_float(sb[i])
 
-      const bool diag = CAUSAL && (j == (2 * pair + t));
-      const bool tail = (j == nkv - 1) && (p.S % kAttnBKV != 0);
-      if (diag || tail) {
+      if (j >= first_masked || (j == nkv - 1 && p.S % kAttnBKV != 0)) {
         const int k0 = j * kAttnBKV;
         const int limit = CAUSAL ? min(q_row, p.S - 1) : (p.S - 1);  // last visible key
 #pragma unroll
-        for (int i = 0; i < 128; ++i)
+        for (int i = 0; i < 64; ++i)
           if (k0 + i > limit) sb[i] = 0xff800000u;  // -inf
       }
 
       float mx0 = WIR_S(0), mx1 = WIR_S(1), mx2 = WIR_S(2), mx3 = WIR_S(3);
 #pragma unroll
-      for (int i = 4; i < 128; i += 4) {
+      for (int i = 4; i < 64; i += 4) {
         mx0 = fmaxf(mx0, WIR_S(i));
         mx1 = fmaxf(mx1, WIR_S(i + 1));
         mx2 = fmaxf(mx2, WIR_S(i + 2));
         mx3 = fmaxf(mx3, WIR_S(i + 3));
       }
       const float m_new = fmaxf(m, fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)));
-      const bool grow = (m_new - m) * c > kRescaleThreshold;  // true on the first tile (m = -inf)
+      const bool grow = (m_new - m) * c > kRescaleThreshold;  // true on the first block (m = -inf)
       if (__any_sync(0xffffffffu, grow)) {
         if (j > 0) {
+          // O_t is being accumulated into by P V(j-1): wait for it before touching O
+          const bool done = mbar_wait(pv_done(t, (j - 1) & 1), ((j - 1) >> 1) & 1, ctx, kRoleSoftmax, 8 + t, j);
+          if (!__all_sync(0xffffffffu, done)) { ok = false; break; }
+          tc_fence_after();
           const float alpha = ex2_approx((m - m_new) * c);
           l *= alpha;
 #pragma unroll 1
@@ -292,29 +332,42 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
       }
 
       const float neg_mc = -m * c;
-      float l0 = 0.f, l1 = 0.f;
+      float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
+      uint32_t pk[32];
+      // in batches of 16: all exponent arguments, then all exponentials, then sums and packing, so
+      // that an in-order warp issues independent work back to back instead of stalling on each
+      // exponential's latency
 #pragma unroll
-      for (int cidx = 0; cidx < 4; ++cidx) {
-        uint32_t pk[16];
+      for (int g = 0; g < 4; ++g) {
+        float e[16];
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const float p0 = ex2_approx(fmaf(WIR_S(cidx * 32 + 2 * i), c, neg_mc));
-          const float p1 = ex2_approx(fmaf(WIR_S(cidx * 32 + 2 * i + 1), c, neg_mc));
-          l0 += p0;
-          l1 += p1;
-          pk[i] = pack_bf16(p0, p1);
+        for (int i = 0; i < 16; ++i) e[i] = fmaf(WIR_S(16 * g + i), c, neg_mc);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) e[i] = ex2_approx(e[i]);
+#pragma unroll
+        for (int i = 0; i < 16; i += 4) {
+          l0 += e[i];
+          l1 += e[i + 1];
+          l2 += e[i + 2];
+          l3 += e[i + 3];
         }
-        tmem_st16(s_addr + cidx * 16, pk);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) pk[8 * g + i] = pack_bf16(e[2 * i], e[2 * i + 1]);
       }
+      l0 += l2;
+      l1 += l3;
 #undef WIR_S
+      if (quarter == 0 && lane == 0) WIR_TRACE_EVENT(p.trace, 1 + t, 103, j);
+      tmem_st32(s_addr, pk);  // P over the low half of the score buffer it came from
       l += l0 + l1;
       tmem_wait_st();
       tc_fence_before();
-      mbar_arrive(p_full(t));
+      mbar_arrive(p_full(t, b));
+      if (quarter == 0 && lane == 0) WIR_TRACE_EVENT(p.trace, 1 + t, 104, j);
     }
 
     if (ok && n > 0) {
-      const bool got = mbar_wait(o_full(t), 0, ctx, kRoleEpilogue, t, 0);
+      const bool got = mbar_wait(pv_done(t, (n - 1) & 1), ((n - 1) >> 1) & 1, ctx, kRoleEpilogue, t, n);
       if (__all_sync(0xffffffffu, got)) {
         tc_fence_after();
         const float inv_l = 1.0f / l;
@@ -345,7 +398,7 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
 
   tc_fence_before();
   __syncthreads();
-  if (warp == 8) {
+  if (warp == kAttnMmaWarp) {
     tc_fence_after();
     tmem_dealloc(tmem_base, kTmemCols);
   }

@@ -46,6 +46,13 @@ int warpir_read_status(int device, void* cuda_stream, int* code, int* detail) {
 
 }  // extern "C"
 
+#ifdef WIR_TRACE
+// Debug builds only: hands the kernels a device buffer for their event trace.
+extern "C" void warpir_debug_set_trace(void* device_buffer) {
+  g_trace = static_cast<unsigned long long*>(device_buffer);
+}
+#endif
+
 // ------------------------------------------------------------------------------------------
 // Split-K GEMM without any allocation (see include/warpir_b200.h).
 //
@@ -145,6 +152,7 @@ extern "C" int warpir_gemm_bf16_splitk_noalloc(const void* A, const void* B, voi
   p.C = static_cast<__nv_bfloat16*>(C);
   p.partial = scratch;
   p.status = reinterpret_cast<int*>(scratch + kNoallocFloats);
+  p.trace = nullptr;
   if (p.splits > 1) {
     const size_t need = static_cast<size_t>(p.splits) * M * N;
     if (need > kNoallocFloats)

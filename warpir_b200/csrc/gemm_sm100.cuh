@@ -18,6 +18,12 @@
 //   warps 2-5 epilogue: tcgen05.ld the accumulator (one row per thread), convert
 //            to bf16 and store C, overlapping the next tile's main loop.
 //
+// MT = 2 makes the CTA tile 256 rows tall: two 128-row MMAs per k-step share one B tile, which
+// halves the B bytes each SM pulls from L2 per FLOP (the 128 x 256 tile moves 96 B/clk/SM, about
+// what L2 can feed to 148 SMs at once; 256 x 256 moves 64).  The two accumulators then fill all
+// 512 tensor-memory columns, so the epilogue (two warpgroups) is not overlapped with the next
+// tile's MMAs; at large K that costs a few percent, at small K the 128-row tile is preferred.
+//
 // Work items (output tile x K-split) are handed out statically, `gridDim.x`
 // apart, walking the tile grid in bands of kGroupM row-blocks so that the CTAs
 // running at any moment share A and B panels in L2.
@@ -29,27 +35,37 @@ namespace wir {
 
 constexpr int kGemmBM = 128;      // rows of an output tile = MMA M
 constexpr int kGemmBK = 64;       // K extent of one pipeline stage: 64 bf16 = one 128-byte swizzle row
-constexpr int kGemmThreads = 192; // producer warp + MMA warp + 4 epilogue warps
+constexpr int kGemmThreads = 192; // producer warp + MMA warp + 4 epilogue warps (per 128 rows of the tile)
+__host__ __device__ constexpr int gemm_threads(int mt) { return 64 + 128 * mt; }
 constexpr int kGroupM = 16;       // rasterisation band height in row-blocks
 
 struct GemmParams {
   int M, N, K;
   int ldc;            // leading dimension of C in elements
-  int tiles_m, tiles_n;
+  int tiles_m, tiles_n;   // tiles_m counts CTA tiles of MT * 128 rows
   int num_kb;         // ceil(K / 64)
   int splits;         // K-splits per output tile (1 = none)
   int kb_per_split;
   __nv_bfloat16* C;
   float* partial;     // [splits][M][N] fp32 partial sums when splits > 1
   int* status;        // 4 device status words
+  unsigned long long* trace;   // event trace buffer of debug builds (-DWIR_TRACE), else unused
 };
 
-template <int BN, int STAGES>
+// Shared memory: the A tiles of all stages first, then the B tiles, then barriers.  A_ROWS < 128
+// (problems with few rows) loads only the rows of A that exist; the MMA still reads 128 rows
+// starting at the tile, i.e. runs on into the tiles behind it, which only produces values for
+// rows of C that are never stored.  The B area behind the A area keeps those reads inside the
+// allocation.
+template <int BN, int STAGES, int MT = 1, int A_ROWS = kGemmBM>
 struct GemmSmem {
-  static constexpr int kABytes = kGemmBM * kGemmBK * 2;
+  static_assert(A_ROWS % 8 == 0 && A_ROWS <= kGemmBM && (A_ROWS == kGemmBM || MT == 1), "A rows");
+  static constexpr int kABytes = (A_ROWS == kGemmBM ? MT * kGemmBM : A_ROWS) * kGemmBK * 2;
   static constexpr int kBBytes = BN * kGemmBK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kBOffset = STAGES * kABytes;
   static constexpr int kBarOffset = STAGES * kStageBytes;
+  static_assert(STAGES * kBBytes >= kGemmBM * kGemmBK * 2, "B area must cover the MMA's over-read of A");
   // full[STAGES], empty[STAGES], acc_full[2], acc_empty[2], drain
   static constexpr int kNumBars = 2 * STAGES + 5;
   static constexpr int kTmemPtrOffset = kBarOffset + kNumBars * 8;
@@ -81,12 +97,14 @@ __device__ __forceinline__ TileCoord decode_work(int w, const GemmParams& p) {
 
 // B_MN = false: B stored [N,K] (K contiguous), one TMA box of BN rows per stage.
 // B_MN = true : B stored [K,N] (N contiguous), BN/64 boxes of 64(k) x 64(n) per stage.
-template <int BN, int STAGES, bool B_MN>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+template <int BN, int STAGES, bool B_MN, int MT = 1, int A_ROWS = kGemmBM>
+__global__ void __launch_bounds__(gemm_threads(MT), 1)
 gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                 const GemmParams p) {
-  using L = GemmSmem<BN, STAGES>;
-  constexpr uint32_t kTmemCols = (2 * BN < 32) ? 32 : 2 * BN;
+  using L = GemmSmem<BN, STAGES, MT, A_ROWS>;
+  constexpr int kAccBufs = (2 * MT * BN <= 512) ? 2 : 1;   // double-buffer the accumulator when it fits
+  constexpr uint32_t kTmemCols = (kAccBufs * MT * BN < 32) ? 32 : kAccBufs * MT * BN;
+  constexpr int kTileM = MT * kGemmBM;
   static_assert((kTmemCols & (kTmemCols - 1)) == 0 && kTmemCols <= 512, "TMEM columns");
   static_assert(BN % 16 == 0 && BN >= 16 && BN <= 256, "MMA N");
   static_assert(!B_MN || BN % 64 == 0, "N-contiguous B is loaded in 64-column boxes");
@@ -115,7 +133,7 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(acc_full_bar(a), 1);
-      mbar_init(acc_empty_bar(a), 128);
+      mbar_init(acc_empty_bar(a), 128 * MT);
     }
     mbar_init(drain_bar, 1);
     fence_mbar_init();
@@ -145,9 +163,9 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
           const uint32_t ph = (it / STAGES) & 1;
           if (!mbar_wait(empty_bar(s), ph ^ 1, ctx, kRoleProducer, s, kb)) { ok = false; break; }
           mbar_arrive_expect_tx(full_bar(s), L::kStageBytes);
-          const uint32_t a_dst = smem_base + s * L::kStageBytes;
-          const uint32_t b_dst = a_dst + L::kABytes;
-          tma_load_2d(a_dst, &tmap_a, full_bar(s), kb * kGemmBK, t.m_blk * kGemmBM);
+          const uint32_t a_dst = smem_base + s * L::kABytes;
+          const uint32_t b_dst = smem_base + L::kBOffset + s * L::kBBytes;
+          tma_load_2d(a_dst, &tmap_a, full_bar(s), kb * kGemmBK, t.m_blk * kTileM);
           if constexpr (!B_MN) {
             tma_load_2d(b_dst, &tmap_b, full_bar(s), kb * kGemmBK, t.n_blk * BN);
           } else {
@@ -168,57 +186,74 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
-      constexpr uint32_t idesc = idesc_bf16_f32(kGemmBM, BN, 0, B_MN ? 1 : 0);
-      uint32_t it = 0, acc_it = 0;
-      bool ok = true;
-      for (int w = blockIdx.x; ok && w < total_work; w += gridDim.x, ++acc_it) {
-        const TileCoord t = decode_work(w, p);
-        const uint32_t acc = acc_it & 1;
-        const uint32_t acc_ph = (acc_it >> 1) & 1;
-        if (!mbar_wait(acc_empty_bar(acc), acc_ph ^ 1, ctx, kRoleMma, 100 + acc, w)) { ok = false; break; }
+    // The whole warp runs this loop (warp-uniform operands); one elected lane issues.
+    constexpr uint32_t idesc = idesc_bf16_f32(kGemmBM, BN, 0, B_MN ? 1 : 0);
+    constexpr uint32_t desc_hi = smem_desc_hi_sw128(1024);
+    uint32_t it = 0, acc_it = 0;
+    bool ok = true;
+    WIR_TRACE_DECL;
+    for (int w = blockIdx.x; ok && w < total_work; w += gridDim.x, ++acc_it) {
+      const TileCoord t = decode_work(w, p);
+      if (lane == 0) WIR_TRACE_EVENT(p.trace, 0, 1, w);
+      long long waited = 0;
+      const uint32_t acc = kAccBufs == 2 ? (acc_it & 1) : 0;
+      const uint32_t acc_ph = kAccBufs == 2 ? ((acc_it >> 1) & 1) : (acc_it & 1);
+      if (!mbar_wait_warp(acc_empty_bar(acc), acc_ph ^ 1, ctx, kRoleMma, 100 + acc, w)) { ok = false; break; }
+      tc_fence_after();
+      const uint32_t d_tmem = tmem_base + acc * (MT * BN);
+      if (lane == 0) WIR_TRACE_EVENT(p.trace, 0, 2, w);
+      for (int kb = t.kb_begin; kb < t.kb_end; ++kb, ++it) {
+        const int s = it % STAGES;
+        const uint32_t ph = (it / STAGES) & 1;
+#ifdef WIR_TRACE
+        const long long w0 = clock64();
+#endif
+        if (!mbar_wait_warp(full_bar(s), ph, ctx, kRoleMma, s, kb)) { ok = false; break; }
+#ifdef WIR_TRACE
+        waited += clock64() - w0;
+#endif
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int kb = t.kb_begin; kb < t.kb_end; ++kb, ++it) {
-          const int s = it % STAGES;
-          const uint32_t ph = (it / STAGES) & 1;
-          if (!mbar_wait(full_bar(s), ph, ctx, kRoleMma, s, kb)) { ok = false; break; }
-          tc_fence_after();
-          const uint32_t a_src = smem_base + s * L::kStageBytes;
-          const uint32_t b_src = a_src + L::kABytes;
-          const uint64_t a_desc = smem_desc_sw128(a_src, 16, 1024);
-          const uint64_t b_desc = B_MN ? smem_desc_sw128(b_src, 8192, 1024) : smem_desc_sw128(b_src, 16, 1024);
+        const uint32_t a_lo = smem_desc_lo(smem_base + s * L::kABytes, 16);
+        const uint32_t b_lo = smem_desc_lo(smem_base + L::kBOffset + s * L::kBBytes, B_MN ? 8192 : 16);
 #pragma unroll
-          for (int k = 0; k < kGemmBK / 16; ++k) {
-            // 16 K-elements further: 32 bytes along a K-major row, 16 rows (2048 B) of an N-major tile
-            const uint64_t a_k = a_desc + static_cast<uint64_t>((k * 32) >> 4);
-            const uint64_t b_k = b_desc + static_cast<uint64_t>(B_MN ? (k * 2048) >> 4 : (k * 32) >> 4);
-            mma_ss(d_tmem, a_k, b_k, idesc, (kb > t.kb_begin || k > 0) ? 1u : 0u);
-          }
-          mma_commit(empty_bar(s));  // stage reusable once these MMAs have read it
+        for (int k = 0; k < kGemmBK / 16; ++k) {
+          // 16 K-elements further: 32 bytes along a K-major row, 16 rows (2048 B) of an N-major tile
+          const uint32_t a_k = a_lo + ((k * 32) >> 4);
+          const uint32_t b_k = b_lo + (B_MN ? (k * 2048) >> 4 : (k * 32) >> 4);
+#pragma unroll
+          for (int mt = 0; mt < MT; ++mt)   // the row halves of the CTA tile: 16 KB apart in the A stage
+            mma_ss_elect(d_tmem + mt * BN, a_k + ((mt * kGemmBM * 128) >> 4), desc_hi, b_k, desc_hi, idesc,
+                         (kb > t.kb_begin || k > 0) ? 1u : 0u);
         }
-        if (ok) mma_commit(acc_full_bar(acc));
+        mma_commit_elect(empty_bar(s));  // stage reusable once these MMAs have read it
       }
-      if (!ok || *abort_flag) {
-        mma_commit(drain_bar);
-        mbar_wait_quiet(drain_bar, 0);
-      }
+      if (ok) mma_commit_elect(acc_full_bar(acc));
+      if (lane == 0) WIR_TRACE_EVENT(p.trace, 0, 3, static_cast<int>(waited));
+    }
+    if (!ok || *abort_flag) {
+      mma_commit_elect(drain_bar);
+      mbar_wait_quiet(drain_bar, 0);
     }
     __syncwarp();
   } else {
     // ------------------------------------------------------------ epilogue
     const int quarter = warp & 3;  // tensor-memory lanes [32*quarter, 32*quarter+32) belong to this warp
+    const int mt = (warp - 2) >> 2;  // which 128-row half of the CTA tile this warpgroup drains
     const bool vec_ok = (p.ldc % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0);
     uint32_t acc_it = 0;
     bool ok = true;
+    WIR_TRACE_DECL;
     for (int w = blockIdx.x; ok && w < total_work; w += gridDim.x, ++acc_it) {
       const TileCoord t = decode_work(w, p);
-      const uint32_t acc = acc_it & 1;
-      const uint32_t acc_ph = (acc_it >> 1) & 1;
-      if (!mbar_wait(acc_full_bar(acc), acc_ph, ctx, kRoleEpilogue, acc, w)) { ok = false; break; }
+      const uint32_t acc = kAccBufs == 2 ? (acc_it & 1) : 0;
+      const uint32_t acc_ph = kAccBufs == 2 ? ((acc_it >> 1) & 1) : (acc_it & 1);
+      if (warp == 2 && lane == 0) WIR_TRACE_EVENT(p.trace, 1, 10, w);
+      const bool got = mbar_wait(acc_full_bar(acc), acc_ph, ctx, kRoleEpilogue, acc, w);
+      if (!__all_sync(0xffffffffu, got)) { ok = false; break; }
       tc_fence_after();
-      const int row = t.m_blk * kGemmBM + quarter * 32 + lane;
-      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
+      if (warp == 2 && lane == 0) WIR_TRACE_EVENT(p.trace, 1, 11, w);
+      const int row = t.m_blk * kTileM + mt * kGemmBM + quarter * 32 + lane;
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * (MT * BN) + mt * BN;
       constexpr int kChunk = (BN % 32 == 0) ? 32 : 16;
 #pragma unroll 1
       for (int c = 0; c < BN / kChunk; ++c) {
@@ -261,6 +296,7 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
       }
       tc_fence_before();
       mbar_arrive(acc_empty_bar(acc));
+      if (warp == 2 && lane == 0) WIR_TRACE_EVENT(p.trace, 1, 12, w);
     }
   }
 

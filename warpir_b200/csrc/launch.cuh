@@ -13,6 +13,7 @@
 #include <cmath>
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 
@@ -53,6 +54,7 @@ struct DeviceState {
 inline std::mutex g_mutex;
 inline DeviceState g_dev[kMaxDevices];
 inline PFN_cuTensorMapEncodeTiled_v12000 g_encode = nullptr;
+inline unsigned long long* g_trace = nullptr;   // event-trace buffer; only debug builds (-DWIR_TRACE) write to it
 
 // Makes `device` current for the calling thread for the lifetime of the object.
 struct DeviceGuard {
@@ -199,15 +201,15 @@ inline int opt_in_smem(const void* kernel, int bytes) {
 // ------------------------------------------------------------------------ GEMM
 using GemmLaunchFn = int (*)(const CUtensorMap&, const CUtensorMap&, const wir::GemmParams&, int, cudaStream_t);
 
-template <int BN, int STAGES, bool B_MN>
+template <int BN, int STAGES, bool B_MN, int MT = 1, int A_ROWS = wir::kGemmBM>
 int launch_gemm_cfg(const CUtensorMap& ta, const CUtensorMap& tb, const wir::GemmParams& p, int grid,
                     cudaStream_t stream) {
-  auto kernel = wir::gemm_bf16_sm100<BN, STAGES, B_MN>;
-  constexpr int smem = wir::GemmSmem<BN, STAGES>::kDynamicBytes;
+  auto kernel = wir::gemm_bf16_sm100<BN, STAGES, B_MN, MT, A_ROWS>;
+  constexpr int smem = wir::GemmSmem<BN, STAGES, MT, A_ROWS>::kDynamicBytes;
   static_assert(smem <= 232448, "shared memory budget");
   static_assert(smem > 116 * 1024, "one CTA per SM is what keeps the tensor-memory allocation from blocking");
   if (int rc = opt_in_smem(reinterpret_cast<const void*>(kernel), smem)) return rc;
-  kernel<<<grid, wir::kGemmThreads, smem, stream>>>(ta, tb, p);
+  kernel<<<grid, wir::gemm_threads(MT), smem, stream>>>(ta, tb, p);
   WIR_CUDA(cudaGetLastError());
   return WARPIR_OK;
 }
@@ -215,14 +217,25 @@ int launch_gemm_cfg(const CUtensorMap& ta, const CUtensorMap& tb, const wir::Gem
 struct GemmChoice {
   int block_n;
   int splits;
+  int mt = 1;   // CTA tile height in units of 128 rows
+  int a_rows = 128;   // rows of A loaded per stage (fewer for problems with few rows)
 };
+
+// Tuning override for experiments: WARPIR_GEMM_MT=1|2 forces the CTA tile height.
+inline int env_gemm_mt() {
+  static const int v = [] {
+    const char* e = getenv("WARPIR_GEMM_MT");
+    return e ? atoi(e) : 0;
+  }();
+  return v;
+}
 
 // Tile width: the widest tile keeps the tensor core busiest per byte of shared-memory
 // traffic, but the tile count must fill the SMs.  Score = fraction of SM-waves that do
 // useful work x relative MMA efficiency of the tile width.
 inline GemmChoice choose_gemm(int64_t M, int64_t N, int64_t K, int sms) {
   const int cands[3] = {256, 128, 64};
-  const double eff[3] = {1.0, 0.92, 0.72};
+  const double eff[3] = {1.0, 0.65, 0.40};
   const int64_t tm = (M + wir::kGemmBM - 1) / wir::kGemmBM;
   double best = -1.0;
   GemmChoice c{256, 1};
@@ -235,7 +248,15 @@ inline GemmChoice choose_gemm(int64_t M, int64_t N, int64_t K, int sms) {
       c.block_n = cands[i];
     }
   }
-  (void)K;
+  // 256-row CTA tiles (two MMAs sharing B) when the k-loop is long enough to amortise the
+  // un-overlapped epilogue and the tile count still fills the SMs as well as before.
+  if (c.block_n == 256 && M >= 512 && K >= 2048) {
+    const int64_t tn = (N + 255) / 256;
+    const int64_t t1 = tm * tn, t2 = ((M + 255) / 256) * tn;
+    const double e1 = static_cast<double>(t1) / static_cast<double>(((t1 + sms - 1) / sms) * sms);
+    const double e2 = static_cast<double>(t2) / static_cast<double>(((t2 + sms - 1) / sms) * sms);
+    if (e2 >= 0.97 * e1) c.mt = 2;
+  }
   return c;
 }
 
@@ -267,8 +288,19 @@ inline int gemm_impl(const void* A, const void* B, void* C, int64_t M, int64_t N
   if (b_layout == 0 && N % 8 != 0) return fail(WARPIR_ESHAPE, "N = %lld: with B stored [K,N] its row pitch must be a multiple of 16 bytes (N %% 8 == 0)", (long long)N);
 
   GemmChoice ch = choose_gemm(M, N, K, dev->sm_count);
-  if (block_n != 0) ch.block_n = block_n;
+  if (block_n != 0) { ch.block_n = block_n; ch.mt = 1; }
   if (splits != 0) ch.splits = splits;
+  if (fixed != nullptr) ch.mt = 1;
+  // few rows: 64-wide tiles (many CTAs streaming B), only the existing rows of A are loaded and
+  // the saved shared memory deepens the ring so more of B is in flight per SM
+  if (fixed == nullptr && block_n == 0 && M <= 64 && N >= 64 * 64) {
+    ch.block_n = 64;
+    ch.mt = 1;
+    ch.a_rows = (M <= 16) ? 16 : 64;
+  }
+  if (env_gemm_mt() == 1) ch.mt = 1;
+  if (env_gemm_mt() == 2 && ch.block_n == 256 && fixed == nullptr) ch.mt = 2;
+  if (ch.splits > 1) ch.mt = 1;
   const int num_kb = static_cast<int>((K + wir::kGemmBK - 1) / wir::kGemmBK);
   if (ch.splits > num_kb) ch.splits = num_kb;
   if (ch.splits > 1 && N % 4 != 0) ch.splits = 1;  // the reduce pass works on groups of four columns
@@ -278,7 +310,8 @@ inline int gemm_impl(const void* A, const void* B, void* C, int64_t M, int64_t N
   p.N = static_cast<int>(N);
   p.K = static_cast<int>(K);
   p.ldc = p.N;
-  p.tiles_m = static_cast<int>((M + wir::kGemmBM - 1) / wir::kGemmBM);
+  const int tile_m = wir::kGemmBM * ch.mt;
+  p.tiles_m = static_cast<int>((M + tile_m - 1) / tile_m);
   p.tiles_n = static_cast<int>((N + ch.block_n - 1) / ch.block_n);
   p.num_kb = num_kb;
   p.kb_per_split = (num_kb + ch.splits - 1) / ch.splits;
@@ -286,6 +319,7 @@ inline int gemm_impl(const void* A, const void* B, void* C, int64_t M, int64_t N
   p.C = static_cast<__nv_bfloat16*>(C);
   p.partial = nullptr;
   p.status = dev->status;
+  p.trace = g_trace;
 
   if (p.splits > 1) {
     const size_t need = static_cast<size_t>(p.splits) * M * N * sizeof(float);
@@ -310,7 +344,7 @@ inline int gemm_impl(const void* A, const void* B, void* C, int64_t M, int64_t N
   {
     const uint64_t dims[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(M)};
     const uint64_t strides[1] = {static_cast<uint64_t>(K) * 2};
-    const uint32_t box[2] = {wir::kGemmBK, wir::kGemmBM};
+    const uint32_t box[2] = {wir::kGemmBK, static_cast<uint32_t>(ch.a_rows < 128 ? ch.a_rows : tile_m)};
     if (int rc = make_tmap(&ta, A, 2, dims, strides, box)) return rc;
   }
   if (b_layout == 1) {
@@ -330,6 +364,9 @@ inline int gemm_impl(const void* A, const void* B, void* C, int64_t M, int64_t N
   int rc;
   const bool mn = (b_layout == 0);
   if (fixed != nullptr) rc = fixed(ta, tb, p, grid, stream);
+  else if (ch.a_rows == 16) rc = mn ? launch_gemm_cfg<64, 19, true, 1, 16>(ta, tb, p, grid, stream) : launch_gemm_cfg<64, 19, false, 1, 16>(ta, tb, p, grid, stream);
+  else if (ch.a_rows == 64) rc = mn ? launch_gemm_cfg<64, 12, true, 1, 64>(ta, tb, p, grid, stream) : launch_gemm_cfg<64, 12, false, 1, 64>(ta, tb, p, grid, stream);
+  else if (ch.mt == 2) rc = mn ? launch_gemm_cfg<256, 3, true, 2>(ta, tb, p, grid, stream) : launch_gemm_cfg<256, 3, false, 2>(ta, tb, p, grid, stream);
   else switch (ch.block_n) {
     case 256: rc = mn ? launch_gemm_cfg<256, 4, true>(ta, tb, p, grid, stream) : launch_gemm_cfg<256, 4, false>(ta, tb, p, grid, stream); break;
     case 128: rc = mn ? launch_gemm_cfg<128, 6, true>(ta, tb, p, grid, stream) : launch_gemm_cfg<128, 6, false>(ta, tb, p, grid, stream); break;
@@ -387,7 +424,8 @@ inline int attn_impl(const void* Q, const void* K, const void* V, void* O, float
   if (guard.err != cudaSuccess) return fail(WARPIR_ECUDA, "cudaSetDevice(%d): %s", device, cudaGetErrorString(guard.err));
 
   CUtensorMap tq, tk, tv;
-  const uint32_t box[3] = {64, 128, 1};
+  const uint32_t box[3] = {64, wir::kAttnBQ, 1};       // one 128-row Q tile chunk
+  const uint32_t box_kv[3] = {64, wir::kAttnBKV, 1};   // one K/V tile chunk
   {
     const uint64_t dims[3] = {static_cast<uint64_t>(D), static_cast<uint64_t>(S), static_cast<uint64_t>(B * Hq)};
     const uint64_t strides[2] = {static_cast<uint64_t>(D) * 2, static_cast<uint64_t>(S) * D * 2};
@@ -396,8 +434,8 @@ inline int attn_impl(const void* Q, const void* K, const void* V, void* O, float
   {
     const uint64_t dims[3] = {static_cast<uint64_t>(D), static_cast<uint64_t>(S), static_cast<uint64_t>(B * Hkv)};
     const uint64_t strides[2] = {static_cast<uint64_t>(D) * 2, static_cast<uint64_t>(S) * D * 2};
-    if (int rc = make_tmap(&tk, K, 3, dims, strides, box)) return rc;
-    if (int rc = make_tmap(&tv, V, 3, dims, strides, box)) return rc;
+    if (int rc = make_tmap(&tk, K, 3, dims, strides, box_kv)) return rc;
+    if (int rc = make_tmap(&tv, V, 3, dims, strides, box_kv)) return rc;
   }
   wir::AttnParams p;
   p.B = static_cast<int>(B);
@@ -409,6 +447,7 @@ inline int attn_impl(const void* Q, const void* K, const void* V, void* O, float
   p.O = static_cast<__nv_bfloat16*>(O);
   p.LSE = LSE;
   p.status = dev->status;
+  p.trace = g_trace;
   if (D == 128) return causal ? launch_attn_cfg<128, true>(tq, tk, tv, p, stream) : launch_attn_cfg<128, false>(tq, tk, tv, p, stream);
   return causal ? launch_attn_cfg<64, true>(tq, tk, tv, p, stream) : launch_attn_cfg<64, false>(tq, tk, tv, p, stream);
 }

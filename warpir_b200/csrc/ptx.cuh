@@ -215,6 +215,18 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr, uint32_t lbo
   return d;
 }
 
+// The same descriptor as two 32-bit halves.  Only the low half depends on the address, and
+// stepping through a tile only adds a constant to it, so a loop that issues many MMAs from
+// one thread keeps `hi` in a register and spends one integer add per operand per MMA (a lone
+// issuing thread executes dependent ALU instructions several clocks apart, so descriptor
+// arithmetic is what bounds its MMA issue rate).
+__device__ __forceinline__ uint32_t smem_desc_lo(uint32_t saddr, uint32_t lbo_bytes) {
+  return ((saddr & 0x3ffff) >> 4) | (((lbo_bytes >> 4) & 0x3fff) << 16);
+}
+__host__ __device__ constexpr uint32_t smem_desc_hi_sw128(uint32_t sbo_bytes) {
+  return ((sbo_bytes >> 4) & 0x3fff) | (1u << 14) | (2u << 29);
+}
+
 // Instruction descriptor for kind::f16 with bf16 inputs and fp32 accumulation.
 //   [4,6) D format (1 = f32)  [7,10) A format (1 = bf16)  [10,13) B format (1 = bf16)
 //   [15] A major (0 = K)      [16] B major (0 = K, 1 = MN)
@@ -245,6 +257,82 @@ __device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_
       ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// Same two instructions with the descriptors given as (low, high) halves.
+__device__ __forceinline__ void mma_ss_lh(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo,
+                                          uint32_t b_hi, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+      "mov.b64 da, {%1, %2};\n\t"
+      "mov.b64 db, {%3, %4};\n\t"
+      "setp.ne.b32 p, %6, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void mma_ts_lh(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t b_hi,
+                                          uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 db;\n\t"
+      "mov.b64 db, {%2, %3};\n\t"
+      "setp.ne.b32 p, %5, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Warp-collective issue.  The whole (converged) warp runs the issuing loop, so barrier
+// addresses, descriptors and tensor-memory addresses are warp-uniform values that the
+// compiler can keep in uniform registers, which is what the MMA and commit instructions take;
+// only the instruction itself is predicated on one elected lane.  Issuing from inside an
+// `if (lane == 0)` region instead makes every operand a per-thread value that has to be
+// moved to a uniform register before each MMA, and the issue rate of the lone thread (about
+// 100 clocks per MMA) becomes the kernel's bottleneck.  elect.sync picks the same lane every
+// time for a given mask, so MMAs and the commits that track them come from one thread.
+__device__ __forceinline__ void mma_ss_elect(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo,
+                                             uint32_t b_hi, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p, e;\n\t.reg .b64 da, db;\n\t"
+      "elect.sync _|e, 0xffffffff;\n\t"
+      "mov.b64 da, {%1, %2};\n\t"
+      "mov.b64 db, {%3, %4};\n\t"
+      "setp.ne.b32 p, %6, 0;\n\t"
+      "@e tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void mma_ts_elect(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t b_hi,
+                                             uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p, e;\n\t.reg .b64 db;\n\t"
+      "elect.sync _|e, 0xffffffff;\n\t"
+      "mov.b64 db, {%2, %3};\n\t"
+      "setp.ne.b32 p, %5, 0;\n\t"
+      "@e tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void mma_commit_elect(uint32_t bar) {
+  asm volatile(
+      "{\n\t.reg .pred e;\n\t"
+      "elect.sync _|e, 0xffffffff;\n\t"
+      "@e tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}"
+      ::"r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_elect(uint32_t bar) {
+  asm volatile(
+      "{\n\t.reg .pred e;\n\t"
+      "elect.sync _|e, 0xffffffff;\n\t"
+      "@e mbarrier.arrive.shared::cta.b64 _, [%0];\n\t}"
+      ::"r"(bar)
+      : "memory");
+}
+// Warp-uniform bounded wait: every lane polls, the warp agrees on the outcome.
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, const AbortCtx& ctx, int role,
+                                               int tag, int detail) {
+  const bool ok = mbar_wait(bar, parity, ctx, role, tag, detail);
+  return __all_sync(0xffffffffu, ok);
+}
+
 // Arrive on `bar` once every MMA issued so far by this thread has completed.
 __device__ __forceinline__ void mma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
@@ -291,6 +379,26 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t* r) {
       ::WIR_W16(r, 0), "r"(taddr)
       : "memory");
 }
+
+// ---- optional event trace (debug builds only: -DWIR_TRACE) --------------------------------
+// A traced thread of CTA (0,0,0) appends (event << 32 | index, clock64) pairs to its own
+// region of a global buffer (plain stores, no round trip, so the perturbation is a few
+// clocks per event).  Compiled out of the product library.
+#ifdef WIR_TRACE
+constexpr int kTraceRegion = 4096;   // entries per region
+#define WIR_TRACE_DECL int wir_trace_n = 0
+__device__ __forceinline__ void trace_event(unsigned long long* buf, int region, int& n, int ev, int idx) {
+  if (buf == nullptr || blockIdx.x != 0 || blockIdx.y != 0 || blockIdx.z != 0 || n >= kTraceRegion) return;
+  unsigned long long* dst = buf + 2ull * (static_cast<unsigned long long>(region) * kTraceRegion + n);
+  dst[0] = (static_cast<unsigned long long>(ev) << 32) | static_cast<unsigned int>(idx);
+  dst[1] = clock64();
+  ++n;
+}
+#define WIR_TRACE_EVENT(buf, region, ev, idx) trace_event(buf, region, wir_trace_n, ev, idx)
+#else
+#define WIR_TRACE_DECL ((void)0)
+#define WIR_TRACE_EVENT(buf, region, ev, idx) ((void)0)
+#endif
 
 // ---- small numeric helpers -----------------------------------------------------
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
