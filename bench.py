@@ -309,6 +309,9 @@ def run_gpu_arm(args, w, name):
     runtime.load_library()  # raises if the compiled library is missing
     if dist_on:
         import torch.distributed as dist
+        # NCCL announces its version on stdout at the VERSION level; stdout carries the one JSON line
+        if os.environ.get("NCCL_DEBUG", "VERSION").upper() == "VERSION":
+            os.environ["NCCL_DEBUG"] = "WARN"
         dist.init_process_group("nccl", device_id=device)
     peaks, peak_src = load_peaks()
 
@@ -374,6 +377,7 @@ def run_gpu_arm(args, w, name):
         "ms_per_step": per, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16 (fp32 accumulate)", "data": "synthetic",
         "config": {"workload": name, **{k: v for k, v in w.items() if k != "kind"},
+                   "per_gpu": "sizes above are per GPU; the job is n_gpus such shards",
                    "sharding": f"{world} independent row blocks of M (B replicated), no collective"
                    if w["kind"] == "gemm" else f"batch x head slices split over {world} GPUs, no collective",
                    "l2": "inputs+outputs per step exceed the 126 MB L2" if bytes_of(w) > 126e6

@@ -127,7 +127,7 @@ __device__ __forceinline__ void mbar_wait_quiet(uint32_t bar, uint32_t parity) {
   }
 }
 
-// ---- TMA (cp.async.bulk.tensor, no multicast anywhere) ------------------------
+// ---- TMA (cp.async.bulk.tensor; every copy targets the issuing CTA only) --------
 __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* m) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");
 }
