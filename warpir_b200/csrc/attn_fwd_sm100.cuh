@@ -50,6 +50,7 @@ struct AttnParams {
   float* LSE;              // [B, H, S] or nullptr
   int* status;
   unsigned long long* trace;   // event trace buffer of debug builds (-DWIR_TRACE), else unused
+  int stagger_clocks;          // one-off delay of the second Q tile's softmax, in SM clocks
 };
 
 template <int D>
@@ -284,6 +285,15 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
       if (!__all_sync(0xffffffffu, got)) { ok = false; break; }
       tc_fence_after();
       if (quarter == 0 && lane == 0) WIR_TRACE_EVENT(p.trace, 1 + t, 101, j);
+      // The two softmax warpgroups share each scheduler's exponential unit.  Started together they
+      // stay in lockstep (both wait, then both compute at half rate); holding the second tile back
+      // once, after its first scores have arrived, lets each one's exponentials run under the
+      // other's waits, loads and stores, and the offset persists.
+      if (j == 0 && t == 1 && p.stagger_clocks > 0) {
+        const long long t0 = clock64();
+        while (clock64() - t0 < p.stagger_clocks) {
+        }
+      }
 
       uint32_t sb[64];  // this thread's row of raw scores, as fp32 bit patterns
       tmem_ld32(s_addr, sb);
@@ -332,30 +342,25 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
       }
 
       const float neg_mc = -m * c;
-      float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
+      // packed f32x2 arithmetic throughout; every fourth pair of exponentials runs on the FMA pipe
+      const float2 c2 = make_float2(c, c), neg_mc2 = make_float2(neg_mc, neg_mc);
+      float2 la = make_float2(0.f, 0.f), lb = make_float2(0.f, 0.f);
       uint32_t pk[32];
-      // in batches of 16: all exponent arguments, then all exponentials, then sums and packing, so
-      // that an in-order warp issues independent work back to back instead of stalling on each
-      // exponential's latency
 #pragma unroll
-      for (int g = 0; g < 4; ++g) {
-        float e[16];
-#pragma unroll
-        for (int i = 0; i < 16; ++i) e[i] = fmaf(WIR_S(16 * g + i), c, neg_mc);
-#pragma unroll
-        for (int i = 0; i < 16; ++i) e[i] = ex2_approx(e[i]);
-#pragma unroll
-        for (int i = 0; i < 16; i += 4) {
-          l0 += e[i];
-          l1 += e[i + 1];
-          l2 += e[i + 2];
-          l3 += e[i + 3];
+      for (int i = 0; i < 32; ++i) {
+        const float2 x = __ffma2_rn(make_float2(WIR_S(2 * i), WIR_S(2 * i + 1)), c2, neg_mc2);
+        float2 e;
+        if ((i & 3) == 3) {
+          e = ex2_fma2(x);
+        } else {
+          e.x = ex2_approx(x.x);
+          e.y = ex2_approx(x.y);
         }
-#pragma unroll
-        for (int i = 0; i < 8; ++i) pk[8 * g + i] = pack_bf16(e[2 * i], e[2 * i + 1]);
+        if (i & 1) lb = __fadd2_rn(lb, e);
+        else la = __fadd2_rn(la, e);
+        pk[i] = pack_bf16(e.x, e.y);
       }
-      l0 += l2;
-      l1 += l3;
+      const float l0 = la.x + lb.x, l1 = la.y + lb.y;
 #undef WIR_S
       if (quarter == 0 && lane == 0) WIR_TRACE_EVENT(p.trace, 1 + t, 103, j);
       tmem_st32(s_addr, pk);  // P over the low half of the score buffer it came from

@@ -221,6 +221,16 @@ struct GemmChoice {
   int a_rows = 128;   // rows of A loaded per stage (fewer for problems with few rows)
 };
 
+// One-off start-up offset between the two Q tiles' softmax warpgroups of the attention kernel,
+// in SM clocks (WARPIR_ATTN_STAGGER overrides the default).
+inline int env_attn_stagger() {
+  static const int v = [] {
+    const char* e = getenv("WARPIR_ATTN_STAGGER");
+    return e ? atoi(e) : 1000;
+  }();
+  return v;
+}
+
 // Tuning override for experiments: WARPIR_GEMM_MT=1|2 forces the CTA tile height.
 inline int env_gemm_mt() {
   static const int v = [] {
@@ -448,6 +458,7 @@ inline int attn_impl(const void* Q, const void* K, const void* V, void* O, float
   p.LSE = LSE;
   p.status = dev->status;
   p.trace = g_trace;
+  p.stagger_clocks = env_attn_stagger();
   if (D == 128) return causal ? launch_attn_cfg<128, true>(tq, tk, tv, p, stream) : launch_attn_cfg<128, false>(tq, tk, tv, p, stream);
   return causal ? launch_attn_cfg<64, true>(tq, tk, tv, p, stream) : launch_attn_cfg<64, false>(tq, tk, tv, p, stream);
 }

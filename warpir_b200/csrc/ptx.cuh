@@ -68,6 +68,18 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t byt
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
                : "memory");
 }
+// Non-blocking probe (try_wait may suspend the thread for a while when the phase is still open).
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(done)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return done != 0;
+}
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t done;
   asm volatile(
@@ -99,7 +111,7 @@ __device__ __forceinline__ void report_error(const AbortCtx& ctx, int code, int 
 // Bounded wait for the phase with parity `parity` of barrier `bar` to complete.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const AbortCtx& ctx,
                                           int role, int tag, int detail) {
-  if (mbar_try_wait(bar, parity)) return true;
+  if (mbar_test_wait(bar, parity)) return true;
   uint64_t t0 = 0;
   for (uint32_t poll = 0; poll < kWaitPolls; ++poll) {
     if (mbar_try_wait(bar, parity)) return true;
@@ -409,6 +421,25 @@ __device__ __forceinline__ float ex2_approx(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
+}
+// Two 2^x (x <= 0) on the FMA pipe instead of the exponential unit, with packed f32x2
+// arithmetic: x = n + f with n the nearest integer (magic-constant rounding), 2^f by a cubic on
+// [-0.5, 0.5] (relative error below 6e-4, far inside bf16's 4e-3), and n added into the
+// exponent field.  The exponential unit retires 16 results per clock per SM, a quarter of what
+// the tensor cores need at head dimension 128; moving a share of the exponentials here is
+// what lets the two overlap.
+__device__ __forceinline__ float2 ex2_fma2(float2 x) {
+  x.x = fmaxf(x.x, -126.f);
+  x.y = fmaxf(x.y, -126.f);
+  const float2 r = __fadd2_rn(x, make_float2(12582912.f, 12582912.f));     // 1.5 * 2^23: n in the low mantissa bits
+  const float2 n = __fadd2_rn(r, make_float2(-12582912.f, -12582912.f));
+  const float2 f = __fadd2_rn(x, make_float2(-n.x, -n.y));
+  float2 q = __ffma2_rn(f, make_float2(0.0555041087f, 0.0555041087f), make_float2(0.2402265070f, 0.2402265070f));
+  q = __ffma2_rn(q, f, make_float2(0.6931471806f, 0.6931471806f));
+  q = __ffma2_rn(q, f, make_float2(1.f, 1.f));
+  q.x = __int_as_float(__float_as_int(q.x) + (__float_as_int(r.x) << 23));
+  q.y = __int_as_float(__float_as_int(q.y) + (__float_as_int(r.y) << 23));
+  return q;
 }
 
 }  // namespace wir
