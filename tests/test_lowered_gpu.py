@@ -30,9 +30,9 @@ def test_reference_gemm_program_baseline_and_pipelined(lib):
         _check_gemm(piped, n, 0)
 
 
-@pytest.mark.parametrize("bn", [64, 128, 256])
-def test_hardware_tile_programs(bn, lib):
-    mod = runtime.load(kernel_pass(build_gemm_kernel(128, bn, 64, b_k_major=True)))
+@pytest.mark.parametrize("bm,bn", [(128, 64), (128, 128), (128, 256), (256, 256)])
+def test_hardware_tile_programs(bm, bn, lib):
+    mod = runtime.load(kernel_pass(build_gemm_kernel(bm, bn, 64, b_k_major=True)))
     for n in (128, 1024):
         _check_gemm(mod, n, 1)
 

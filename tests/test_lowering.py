@@ -36,16 +36,24 @@ def test_reference_pipelined_program_lowers_too():
     assert p.pipelined_in_ir and p.b_row_major and p.block_n == 0
 
 
-@pytest.mark.parametrize("bn,stages", [(256, 4), (128, 6), (64, 8)])
+@pytest.mark.parametrize("bm,bn,stages", [(128, 256, 4), (128, 128, 6), (128, 64, 8), (256, 256, 3)])
 @pytest.mark.parametrize("pipelined", [False, True])
-def test_hardware_tiles_are_instantiated_as_written(bn, stages, pipelined):
-    k = build_gemm_kernel(128, bn, 64, b_k_major=True)
+def test_hardware_tiles_are_instantiated_as_written(bm, bn, stages, pipelined):
+    k = build_gemm_kernel(bm, bn, 64, b_k_major=True)
     if pipelined:
         k = kernel_pass(k)
     L = Sm100Lowerer()
     src = L.lower(k)
-    assert L.plan.block_n == bn and L.plan.stages == stages and not L.plan.b_row_major
-    assert f"launch_gemm_cfg<{bn}, {stages}, false>" in src and "/*b_layout=*/1" in src
+    assert (L.plan.block_m, L.plan.block_n, L.plan.stages) == (bm, bn, stages) and not L.plan.b_row_major
+    assert f"launch_gemm_cfg<{bn}, {stages}, false, {bm // 128}>" in src and "/*b_layout=*/1" in src
+
+
+def test_ring_too_deep_for_shared_memory_is_rejected():
+    from warpir_b200.passes.modulo_scheduler import MachineModel
+    deep = MachineModel("too-deep", 15, 4, 15, {"tma": 16, "tc": 1}, max_cycles=400, depth=10, max_stages=8)
+    k = kernel_pass(build_gemm_kernel(128, 256, 64, b_k_major=True), deep)   # 8 stages of 48 KB
+    with pytest.raises(NotImplementedError, match="do not fit"):
+        analyze(k)
 
 
 def test_attention_parameters():

@@ -30,7 +30,8 @@ def test_reference_demo_model_solves_to_ii6_three_stages():
     assert mgr.solve(10, 5, {"tma": 4, "tc": 1}) == (None,) * 6   # does not fit
 
 
-@pytest.mark.parametrize("shape,stages", [((128, 256, 64), 4), ((128, 128, 64), 6), ((128, 64, 64), 8)])
+@pytest.mark.parametrize("shape,stages", [((128, 256, 64), 4), ((128, 128, 64), 6), ((128, 64, 64), 8),
+                                          ((256, 256, 64), 3)])
 def test_sm100_model_picks_the_ring_depths_the_kernels_use(shape, stages):
     k = build_gemm_kernel(*shape, b_k_major=True)
     loop = next(o for o in k.body if isinstance(o, ForOp))

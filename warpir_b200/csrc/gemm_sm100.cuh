@@ -124,6 +124,9 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+#ifdef WIR_TRACE
+  { WIR_TRACE_DECL; if (threadIdx.x == 64) WIR_TRACE_EVENT(p.trace, 2, 20, 0); }
+#endif
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
@@ -148,6 +151,9 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_ptr_slot;
+#ifdef WIR_TRACE
+  { WIR_TRACE_DECL; if (threadIdx.x == 64) WIR_TRACE_EVENT(p.trace, 3, 21, 0); }
+#endif
 
   const int total_work = p.tiles_m * p.tiles_n * p.splits;
 
@@ -306,6 +312,9 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
     tc_fence_after();
     tmem_dealloc(tmem_base, kTmemCols);
   }
+#ifdef WIR_TRACE
+  { WIR_TRACE_DECL; if (threadIdx.x == 32) WIR_TRACE_EVENT(p.trace, 3, 22, 0); }
+#endif
 }
 
 // Deterministic second pass of a split-K GEMM: sums the fp32 partials in split

@@ -270,10 +270,11 @@ inline GemmChoice choose_gemm(int64_t M, int64_t N, int64_t K, int sms) {
   return c;
 }
 
-// `fixed`: when not null, the instantiation to launch (with `block_n` its tile width); used by
+// `fixed`: when not null, the instantiation to launch (with `block_n` its tile width and
+// `fixed_mt` its tile height in units of 128 rows); used by
 // the translation units the lowering emits, which pin tile width and ring depth.
 inline int gemm_impl(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K, int b_layout, int block_n,
-                     int splits, int device, void* cuda_stream, GemmLaunchFn fixed = nullptr) {
+                     int splits, int device, void* cuda_stream, GemmLaunchFn fixed = nullptr, int fixed_mt = 1) {
   g_last_error[0] = 0;
   if (M < 0 || N < 0 || K < 0) return fail(WARPIR_EINVAL, "negative size");
   if (b_layout != 0 && b_layout != 1) return fail(WARPIR_EINVAL, "b_layout must be 0 or 1");
@@ -300,7 +301,7 @@ inline int gemm_impl(const void* A, const void* B, void* C, int64_t M, int64_t N
   GemmChoice ch = choose_gemm(M, N, K, dev->sm_count);
   if (block_n != 0) { ch.block_n = block_n; ch.mt = 1; }
   if (splits != 0) ch.splits = splits;
-  if (fixed != nullptr) ch.mt = 1;
+  if (fixed != nullptr) ch.mt = fixed_mt;
   // few rows: 64-wide tiles (many CTAs streaming B), only the existing rows of A are loaded and
   // the saved shared memory deepens the ring so more of B is in flight per SM
   if (fixed == nullptr && block_n == 0 && M <= 64 && N >= 64 * 64) {
@@ -308,9 +309,9 @@ inline int gemm_impl(const void* A, const void* B, void* C, int64_t M, int64_t N
     ch.mt = 1;
     ch.a_rows = (M <= 16) ? 16 : 64;
   }
-  if (env_gemm_mt() == 1) ch.mt = 1;
+  if (env_gemm_mt() == 1 && fixed == nullptr) ch.mt = 1;
   if (env_gemm_mt() == 2 && ch.block_n == 256 && fixed == nullptr) ch.mt = 2;
-  if (ch.splits > 1) ch.mt = 1;
+  if (ch.splits > 1 && fixed == nullptr) ch.mt = 1;
   const int num_kb = static_cast<int>((K + wir::kGemmBK - 1) / wir::kGemmBK);
   if (ch.splits > num_kb) ch.splits = num_kb;
   if (ch.splits > 1 && N % 4 != 0) ch.splits = 1;  // the reduce pass works on groups of four columns

@@ -47,10 +47,10 @@ from ..passes.warp_assigner import RoleTable, assign_roles
 from ..printing import format_kernel
 
 LOG2E = 1.4426950408889634
-HW_BLOCK_M = 128
+HW_BLOCK_M = (128, 256)                   # 256: two 128-row MMAs per k-step share one B tile
 HW_BLOCK_K = 64
 HW_BLOCK_N = (64, 128, 256)
-GEMM_STAGES = {256: 4, 128: 6, 64: 8}     # ring depth that fills the 192 KB operand ring
+GEMM_STAGES = {(128, 256): 4, (128, 128): 6, (128, 64): 8, (256, 256): 3}   # fills the 192 KB operand ring
 
 
 @dataclass(frozen=True)
@@ -62,6 +62,7 @@ class GemmPlan:
     tile_as_written: Tuple[int, int, int]      # (block_m, block_n, block_k) in the IR
     b_row_major: bool                          # True: B stored [K,N]; False: B stored [N,K]
     block_n: int                               # hardware tile width, 0 = chosen per launch
+    block_m: int                               # hardware tile height (128 or 256) when block_n is fixed
     stages: int                                # ring depth of the instantiated kernel
     pipelined_in_ir: bool
     row_builtin: str
@@ -177,16 +178,18 @@ def _analyze_gemm(kernel: Kernel, loop: ForOp) -> GemmPlan:
     if tuple(st.coords[2:]) != (ca[2], col):
         _reject(kernel, "the store coordinates do not match the operands' grid mapping")
 
-    hw_legal = block_m == HW_BLOCK_M and block_k == HW_BLOCK_K and block_n in HW_BLOCK_N
+    hw_legal = (block_k == HW_BLOCK_K and (block_m, block_n) in GEMM_STAGES)
     fixed_n = block_n if hw_legal else 0
     if fixed_n and not stages:
         sched = _ms.schedule_loop(loop)
-        stages = sched.num_stages if sched else GEMM_STAGES[fixed_n]
+        stages = sched.num_stages if sched else GEMM_STAGES[(block_m, block_n)]
+    if fixed_n and stages * 2 * block_k * (block_m + block_n) > _ms.SM100_RING_BUDGET:
+        _reject(kernel, f"{stages} stages of a {block_m}x{block_n}x{block_k} tile do not fit in shared memory")
     if not fixed_n:
         stages = 0   # re-tiled: width and ring depth are picked per launch from the problem size
     return GemmPlan(name=kernel.name, a=ld_a.source.name, b=ld_b.source.name, c=st.dest.name,
                     tile_as_written=(block_m, block_n, block_k), b_row_major=b_row_major, block_n=fixed_n,
-                    stages=stages, pipelined_in_ir=pipelined, row_builtin=ca[2].name, col_builtin=col.name,
+                    block_m=block_m if fixed_n else 0, stages=stages, pipelined_in_ir=pipelined, row_builtin=ca[2].name, col_builtin=col.name,
                     roles=assign_roles(kernel))
 
 
@@ -290,8 +293,8 @@ def _emit_gemm(kernel: Kernel, plan: GemmPlan) -> str:
     b_layout = 0 if plan.b_row_major else 1
     if plan.block_n:
         inst = (f"&wir::host::launch_gemm_cfg<{plan.block_n}, {plan.stages}, "
-                f"{'true' if plan.b_row_major else 'false'}>")
-        fixed = f"{plan.block_n}, /*splits=*/1, device, stream, {inst}"
+                f"{'true' if plan.b_row_major else 'false'}, {plan.block_m // 128}>")
+        fixed = f"{plan.block_n}, /*splits=*/1, device, stream, {inst}, /*tile rows / 128=*/{plan.block_m // 128}"
     else:
         fixed = "/*block_n: per launch*/0, /*splits: per launch*/0, device, stream"
     n_dim = "dims[4 * {i} + 3]".format(i=ic)

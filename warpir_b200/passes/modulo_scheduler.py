@@ -261,9 +261,11 @@ def schedule_loop(loop: ForOp, machine: Optional[MachineModel] = None) -> Option
     _, _, _, ii, stages, stage_of = mgr.solve(machine.max_cycles, machine.depth, machine.resources)
     if ii is None:
         return None
-    if machine.max_stages is not None and stages > machine.max_stages:
-        # the ring cannot be deeper than shared memory allows: loads go out at stage 0 and
-        # the MMA consumes them as late as the ring permits
+    if machine.max_stages is not None and stages != machine.max_stages:
+        # On sm_100a the ring is always made as deep as shared memory allows: the schedule says
+        # how many stages the steady state NEEDS, but load latency varies with where the tile
+        # comes from (L2 or HBM), and every extra stage is cover that costs nothing.  Loads go out
+        # at stage 0 and the MMA consumes them at the last stage.
         last = machine.max_stages - 1
         stage_of = {k: (last if nodes[k].resource == "tc" else 0) for k in stage_of}
         stages = machine.max_stages
