@@ -92,7 +92,7 @@ int warpir_gemm_bf16_ex(const void* A, const void* B, void* C, int64_t M, int64_
  * that handed the whole GPU to its own memory pool at start-up (a later cudaMalloc simply
  * fails, or succeeds only by fragmenting what the pool left over), a latency-critical
  * loop where the implicit device synchronisation of cudaMalloc/cudaFree is not
- * acceptable, or code running under a memory budget fixed at load time.
+ * acceptable, or code whose device-memory footprint is fixed at load time.
  * warpir_gemm_bf16_ex with splits > 1 grows a scratch buffer on demand and
  * warpir_gemm_bf16 allocates its status words on first use, so neither is usable there.
  *

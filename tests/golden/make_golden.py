@@ -2,7 +2,7 @@
 
 Run in a container that has the reference checkout (read-only) beside the repo:
 
-    python tests/golden/make_golden.py /root/reference
+    python tests/golden/make_golden.py <path to the reference checkout>
 
 It imports the reference's own Python (its printer, its two tile programs, its
 ``_ref_attention``) and writes:
@@ -279,4 +279,6 @@ def main(ref_root: str) -> None:
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        raise SystemExit("usage: make_golden.py <path to the reference checkout>")
+    main(sys.argv[1])

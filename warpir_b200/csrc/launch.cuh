@@ -206,7 +206,7 @@ int launch_gemm_cfg(const CUtensorMap& ta, const CUtensorMap& tb, const wir::Gem
                     cudaStream_t stream) {
   auto kernel = wir::gemm_bf16_sm100<BN, STAGES, B_MN, MT, A_ROWS>;
   constexpr int smem = wir::GemmSmem<BN, STAGES, MT, A_ROWS>::kDynamicBytes;
-  static_assert(smem <= 232448, "shared memory budget");
+  static_assert(smem <= 232448, "shared memory limit per CTA");
   static_assert(smem > 116 * 1024, "one CTA per SM is what keeps the tensor-memory allocation from blocking");
   if (int rc = opt_in_smem(reinterpret_cast<const void*>(kernel), smem)) return rc;
   kernel<<<grid, wir::gemm_threads(MT), smem, stream>>>(ta, tb, p);
@@ -400,7 +400,7 @@ int launch_attn_cfg(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensor
                     cudaStream_t stream) {
   auto kernel = wir::attn_fwd_sm100<D, CAUSAL>;
   constexpr int smem = wir::AttnSmem<D>::kDynamicBytes;
-  static_assert(smem <= 232448, "shared memory budget");
+  static_assert(smem <= 232448, "shared memory limit per CTA");
   static_assert(smem > 116 * 1024, "one CTA per SM is what keeps the tensor-memory allocation from blocking");
   if (int rc = opt_in_smem(reinterpret_cast<const void*>(kernel), smem)) return rc;
   const int pairs = (p.S + 2 * wir::kAttnBQ - 1) / (2 * wir::kAttnBQ);

@@ -27,7 +27,7 @@ enum DeviceError : int {
 
 enum Role : int { kRoleProducer = 1, kRoleMma = 2, kRoleEpilogue = 3, kRoleSoftmax = 4, kRoleDrain = 5 };
 
-// Time budget of one wait, in nanoseconds of %globaltimer.  Far longer than any
+// Time limit of one wait, in nanoseconds of %globaltimer.  Far longer than any
 // legitimate wait in these kernels (whole launches take milliseconds) and short
 // enough that a protocol bug surfaces as an error status, not as a hung GPU.
 constexpr uint64_t kWaitBudgetNs = 2000000000ull;
