@@ -148,6 +148,17 @@ int warpir_attn_fwd_bf16(const void* Q, const void* K, const void* V, void* O, f
  */
 int warpir_read_status(int device, void* cuda_stream, int* code, int* detail);
 
+/*
+ * Exercises the kernels' failure path without failing anything: launches one small CTA that
+ * waits, for at most `limit_ns` nanoseconds (1 .. 1e9), on a barrier nothing arrives on.  The
+ * wait runs out, the kernel writes the same status words a GEMM or attention kernel would
+ * write when one of its waits runs out, and exits normally; the next warpir_read_status
+ * returns WARPIR_EKERNEL with code 1 and clears the words, after which the device is usable
+ * as before.  Lets a host verify its error handling around warpir_read_status on a healthy
+ * GPU.  No counterpart in the reference, which has no error path at all.
+ */
+int warpir_selftest_bounded_wait(int device, void* cuda_stream, int64_t limit_ns);
+
 #ifdef __cplusplus
 }
 #endif

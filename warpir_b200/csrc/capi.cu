@@ -46,6 +46,10 @@ int warpir_read_status(int device, void* cuda_stream, int* code, int* detail) {
 
 }  // extern "C"
 
+extern "C" int warpir_selftest_bounded_wait(int device, void* cuda_stream, int64_t limit_ns) {
+  return selftest_bounded_wait_impl(device, cuda_stream, limit_ns);
+}
+
 #ifdef WIR_TRACE
 // Debug builds only: hands the kernels a device buffer for their event trace.
 extern "C" void warpir_debug_set_trace(void* device_buffer) {

@@ -464,6 +464,38 @@ inline int attn_impl(const void* Q, const void* K, const void* V, void* O, float
   return causal ? launch_attn_cfg<64, true>(tq, tk, tv, p, stream) : launch_attn_cfg<64, false>(tq, tk, tv, p, stream);
 }
 
+// Self-test of the bounded-wait machinery: one CTA waits, with a limit of `limit_ns`, on an
+// mbarrier that nothing ever arrives on.  The wait runs out, the kernel records the error in the
+// device's status words exactly as the GEMM / attention kernels would, and returns normally.
+__global__ void bounded_wait_selftest_kernel(int* status, unsigned long long limit_ns) {
+  __shared__ __align__(8) unsigned long long bar;
+  __shared__ int abort_flag;
+  const uint32_t bar_addr = wir::smem_u32(&bar);
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    wir::mbar_init(bar_addr, 1);
+    wir::fence_mbar_init();
+  }
+  __syncthreads();
+  wir::AbortCtx ctx{&abort_flag, status, limit_ns};
+  // every thread waits: the first to give up raises the flag, the others then leave quietly
+  wir::mbar_wait(bar_addr, 0, ctx, wir::kRoleDrain, /*tag=*/77, /*detail=*/static_cast<int>(threadIdx.x));
+  __syncthreads();
+}
+
+inline int selftest_bounded_wait_impl(int device, void* cuda_stream, int64_t limit_ns) {
+  g_last_error[0] = 0;
+  if (limit_ns <= 0 || limit_ns > 1000000000ll) return fail(WARPIR_EINVAL, "limit_ns must be in (0, 1e9]");
+  DeviceState* dev = nullptr;
+  if (int rc = get_device_state(device, &dev)) return rc;
+  DeviceGuard guard(device);
+  if (guard.err != cudaSuccess) return fail(WARPIR_ECUDA, "cudaSetDevice(%d): %s", device, cudaGetErrorString(guard.err));
+  bounded_wait_selftest_kernel<<<1, 64, 0, static_cast<cudaStream_t>(cuda_stream)>>>(
+      dev->status, static_cast<unsigned long long>(limit_ns));
+  WIR_CUDA(cudaGetLastError());
+  return WARPIR_OK;
+}
+
 inline int read_status_impl(int device, void* cuda_stream, int* code, int* detail) {
   g_last_error[0] = 0;
   DeviceState* dev = nullptr;

@@ -95,6 +95,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 struct AbortCtx {
   volatile int* flag;   // CTA-wide abort flag in shared memory
   int* status;          // 4 status words in global memory
+  uint64_t limit_ns = kWaitBudgetNs;   // how long one wait may take
 };
 
 __device__ __forceinline__ void report_error(const AbortCtx& ctx, int code, int role, int tag,
@@ -119,7 +120,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const A
       if (*ctx.flag) return false;  // another role gave up: leave quietly
       const uint64_t now = global_timer_ns();
       if (t0 == 0) t0 = now;
-      else if (now - t0 > kWaitBudgetNs) break;
+      else if (now - t0 > ctx.limit_ns) break;
     }
   }
   report_error(ctx, kDevWaitTimeout, role, tag, detail);

@@ -26,7 +26,7 @@ ABI_VERSION = 1
 EXPORTS = (
     "warpir_abi_version", "warpir_strerror", "warpir_last_error", "warpir_gemm_bf16",
     "warpir_gemm_bf16_ex", "warpir_attn_fwd_bf16", "warpir_read_status",
-    "warpir_gemm_bf16_splitk_noalloc",
+    "warpir_gemm_bf16_splitk_noalloc", "warpir_selftest_bounded_wait",
 )
 
 
@@ -69,6 +69,8 @@ def load_library() -> ctypes.CDLL:
         lib.warpir_gemm_bf16_splitk_noalloc.argtypes = [vp, vp, vp, i64, i64, i64, ci, ci, ci, ci, vp]
         lib.warpir_attn_fwd_bf16.restype = ci
         lib.warpir_attn_fwd_bf16.argtypes = [vp, vp, vp, vp, vp, i64, i64, i64, i64, i64, cf, ci, ci, vp]
+        lib.warpir_selftest_bounded_wait.restype = ci
+        lib.warpir_selftest_bounded_wait.argtypes = [ci, vp, i64]
         lib.warpir_read_status.restype = ci
         lib.warpir_read_status.argtypes = [ci, vp, ctypes.POINTER(ci), ctypes.POINTER(ci)]
         if lib.warpir_abi_version() != ABI_VERSION:
