@@ -345,7 +345,7 @@ def run_reference_arm(args, w, name):
     dt = time.perf_counter() - t0
     value = 2.0 * rows * N * K * args.steps / dt / 1e12
     sample = f"rows 0..{rows} of A ({rows}x{K}) times the full B ({N}x{K}) per step, fp32 torch.mm on CPU"
-    print(json.dumps({
+    emit({
         "impl": "reference", "metric": METRIC, "value": value, "unit": "TFLOP/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
@@ -353,7 +353,7 @@ def run_reference_arm(args, w, name):
         "config": {"workload": name, **{k: v for k, v in w.items() if k != "kind"}, "sample": sample},
         "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-    }), flush=True)
+    })
 
 
 def measure_workload(name, w, steps, warmup, dist_on, device, world, peaks):
@@ -388,9 +388,6 @@ def run_gpu_arm(args, w, name):
     runtime.load_library()  # raises if the compiled library is missing
     if dist_on:
         import torch.distributed as dist
-        # NCCL announces its version on stdout at the VERSION level; stdout carries the one JSON line
-        if os.environ.get("NCCL_DEBUG", "VERSION").upper() == "VERSION":
-            os.environ["NCCL_DEBUG"] = "WARN"
         dist.init_process_group("nccl", device_id=device)
     peaks, peak_src = load_peaks()
 
@@ -471,7 +468,28 @@ def run_gpu_arm(args, w, name):
         "frac_of_nominal_2250_per_gpu": value / world / NOMINAL_TFLOPS,
         "other_workloads": others,
     }
-    print(json.dumps(line), flush=True)
+    emit(line)
+
+
+_JSON_FD = None
+
+
+def reserve_stdout():
+    """Keeps stdout for the one JSON line: everything else that writes to file descriptor 1
+    from here on (NCCL announces its version there, whatever NCCL_DEBUG says) goes to stderr."""
+    global _JSON_FD
+    sys.stdout.flush()
+    _JSON_FD = os.dup(1)
+    os.dup2(2, 1)
+
+
+def emit(line):
+    data = (json.dumps(line) + "\n").encode()
+    if _JSON_FD is None:
+        sys.stdout.write(data.decode())
+        sys.stdout.flush()
+    else:
+        os.write(_JSON_FD, data)
 
 
 def main():
@@ -488,6 +506,7 @@ def main():
     if args.warmup < 3 and args.impl != "reference":
         args.warmup = 3
     w = workload_table()[args.workload]
+    reserve_stdout()
     if args.impl == "reference":
         run_reference_arm(args, w, args.workload)
     else:
