@@ -30,8 +30,10 @@ Tile shapes that ``tcgen05.mma`` cannot run as written (the reference's programs
 use 64x64x64; the MMA here is 128 rows tall) are re-tiled: the emitted kernel
 computes the same function with the hardware tile, and the launch grid follows
 from the re-tiled shape exactly as the reference's wrapper derives ``N / 64``.
-Anything that is neither of the two shapes raises ``NotImplementedError``: there
-is no generic fallback and no CPU path.
+Anything that is neither of the two shapes is emitted op by op
+(``lowering/generic.py``): one CTA per block index, one helper call per op, ``mma`` on
+the tensor core through tensor memory.  That path is general, not fast.  Programs it
+cannot express either raise ``NotImplementedError``; there is no CPU path.
 """
 from __future__ import annotations
 
@@ -264,7 +266,7 @@ _PREAMBLE = """\
 //
 // Plan:
 {plan}
-#include "warpir_b200/csrc/launch.cuh"
+{includes}
 
 // Arguments follow the kernel signature: `tensors` holds the device pointers of the
 // global inputs, then the global outputs, in declaration order; `dims` holds four
@@ -277,6 +279,10 @@ extern "C" int {name}_read_status(int device, void* stream, int* code, int* deta
   return wir::host::read_status_impl(device, stream, code, detail);
 }}
 """
+
+
+_INCLUDES_KERNELS = '#include "warpir_b200/csrc/launch.cuh"'
+_INCLUDES_OP_BY_OP = '#include "warpir_b200/csrc/host_common.cuh"\n#include "warpir_b200/csrc/tile_program.cuh"'
 
 
 def _comment(text: str) -> str:
@@ -339,21 +345,40 @@ extern "C" int {plan.name}_launch(const void* const* tensors, const int64_t* dim
 
 
 class Sm100Lowerer:
-    """Tile program -> sm_100a translation unit (see the module docstring)."""
+    """Tile program -> sm_100a translation unit (see the module docstring).
 
-    def __init__(self) -> None:
-        self.plan: Optional[Plan] = None
+    ``op_by_op=True`` skips the recognition step and emits every program, the GEMM and
+    the attention forward included, one helper call per op (``lowering/generic.py``)."""
+
+    def __init__(self, op_by_op: bool = False) -> None:
+        self.op_by_op = op_by_op
+        self.plan = None
 
     def lower(self, kernel: Kernel) -> str:
+        from .generic import emit_tile_program
         self.plan = None
-        plan = analyze(kernel)
+        plan, body, why = None, None, ""
+        if not self.op_by_op:
+            try:
+                plan = analyze(kernel)
+            except NotImplementedError as exc:     # not one of the two recognised programs
+                why = str(exc)
+        if plan is None:
+            plan, body = emit_tile_program(kernel)
+            shown = {k: v for k, v in vars(plan).items() if k != "tiles"}
+            shown["tiles"] = {t.name: f"{t.count} x {t.rows}x{t.cols} at byte {t.offset}, barrier {t.bar}"
+                              for t in plan.tiles.values()}
+            if why:
+                shown["emitted op by op because"] = why
+        else:
+            shown = {k: v for k, v in vars(plan).items() if k != "roles"}
+            shown["warps"] = {r.name: r.warps for r in plan.roles.roles}
+            body = _emit_gemm(kernel, plan) if isinstance(plan, GemmPlan) else _emit_attention(kernel, plan)
         self.plan = plan
-        shown = {k: v for k, v in vars(plan).items() if k != "roles"}
-        shown["warps"] = {r.name: r.warps for r in plan.roles.roles}
         head = _PREAMBLE.format(ir=_comment(format_kernel(kernel)),
                                 plan=_comment("\n".join(f"{k} = {v}" for k, v in shown.items())),
-                                name=kernel.name, kind=plan.kind)
-        body = _emit_gemm(kernel, plan) if isinstance(plan, GemmPlan) else _emit_attention(kernel, plan)
+                                name=kernel.name, kind=plan.kind,
+                                includes=_INCLUDES_OP_BY_OP if plan.kind == "tile_program" else _INCLUDES_KERNELS)
         return head + body
 
 

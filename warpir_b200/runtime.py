@@ -211,10 +211,17 @@ class LoadedKernel:
         self._status.argtypes = [ci, vp, ctypes.POINTER(ci), ctypes.POINTER(ci)]
         if self.kind == "gemm":
             self.launch_gemm = self.__call__
-        else:
+        elif self.kind == "attention":
             self.launch_attention = self.__call__
+        # every kind also answers to the name the reference's wrappers would have
+        # (``launch_<kernel name>``, tests/test_gemm_baseline.py:33-36)
+        setattr(self, f"launch_{name}", self.__call__)
 
-    def __call__(self, *tensors, causal: bool = False, LSE=None) -> None:
+    def __call__(self, *tensors, causal: bool = False, LSE=None, ints=None) -> None:
+        """Launch on torch's current stream.  ``tensors``: the global inputs then outputs in
+        signature order.  ``ints``: the program's int inputs in signature order; programs
+        emitted op by op (kind ``tile_program``) need them spelled out, the two recognised
+        kinds derive their loop extent from the tensor shapes."""
         import torch
         for i, t in enumerate(tensors):
             _require(t, f"tensor {i}", torch.bfloat16)
@@ -234,9 +241,15 @@ class LoadedKernel:
             flat += [1] * (4 - len(shape)) + shape
         dims = (ctypes.c_int64 * len(flat))(*flat)
         # the program's int inputs (its loop extent) are implied by the tensor shapes
-        scalars = (ctypes.c_int64 * 4)(int(tensors[0].shape[-1]), int(bool(causal)), 0, 0)
-        if self.kind == "attention":
-            scalars[0] = int(tensors[0].shape[-2])
+        if self.kind == "tile_program":
+            if causal or LSE is not None:
+                raise ValueError("causal= and LSE= belong to the recognised attention kernel")
+            vals = [int(v) for v in (ints or ())]
+            scalars = (ctypes.c_int64 * max(4, len(vals) + 1))(*vals)
+        else:
+            scalars = (ctypes.c_int64 * 4)(int(tensors[0].shape[-1]), int(bool(causal)), 0, 0)
+            if self.kind == "attention":
+                scalars[0] = int(tensors[0].shape[-2])
         rc = self._launch(ptrs, dims, scalars, dev.index, _stream_of(tensors[0]))
         if rc != 0:
             raise WarpirError(rc, load_library().warpir_strerror(rc).decode(), self._err().decode())
@@ -274,17 +287,18 @@ def compile_source(source: str, name: str) -> Path:
     return so
 
 
-def load(kernel_or_source, name: Optional[str] = None) -> LoadedKernel:
+def load(kernel_or_source, name: Optional[str] = None, op_by_op: bool = False) -> LoadedKernel:
     """Lower (if given a ``Kernel``), compile and load a tile program.
 
     Replaces the reference's ``lower`` + ``load_inline`` + launch-wrapper sequence
-    (tests/test_gemm_baseline.py:52-74)."""
+    (tests/test_gemm_baseline.py:52-74).  ``op_by_op=True`` emits even the two recognised
+    programs one helper call per op instead of instantiating their hand-written kernels."""
     if isinstance(kernel_or_source, str):
         if name is None:
             raise ValueError("name= is needed when loading emitted source text")
         source = kernel_or_source
     else:
         from .lowering import Sm100Lowerer
-        source = Sm100Lowerer().lower(kernel_or_source)
+        source = Sm100Lowerer(op_by_op=op_by_op).lower(kernel_or_source)
         name = kernel_or_source.name
     return LoadedKernel(compile_source(source, name), name)
