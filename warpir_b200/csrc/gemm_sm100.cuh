@@ -47,8 +47,17 @@ struct GemmParams {
   int splits;         // K-splits per output tile (1 = none)
   int kb_per_split;
   __nv_bfloat16* C;
-  float* partial;     // [splits][M][N] fp32 partial sums when splits > 1
+  float* partial;     // [splits][M][N] fp32 partial sums when splits > 1 (stream-K: one slot per tile segment)
   int* status;        // 4 device status words
+  // Stream-K (sk_units > 0): the tiles_m * tiles_n * num_kb k-blocks of the problem are dealt out as
+  // `gridDim.x` contiguous runs of sk_units, so every CTA streams the same amount of B whatever the
+  // number of tiles.  A run covers the tail of one tile, whole tiles, and the head of another; each
+  // piece (segment) of a tile shared between CTAs goes to its own fp32 slot, and the CTA whose
+  // segment lands last sums the slots in segment order and stores the tile.
+  int sk_units = 0;       // k-blocks per CTA, 0 = off
+  int sk_max_seg = 0;     // slots reserved per tile
+  int sk_rows = 0;        // rows of a slot (min(M, 128))
+  int* sk_counters = nullptr;   // one arrival counter per tile; zero between launches
   unsigned long long* trace;   // event trace buffer of debug builds (-DWIR_TRACE), else unused
 };
 
@@ -70,29 +79,66 @@ struct GemmSmem {
   static constexpr int kNumBars = 2 * STAGES + 5;
   static constexpr int kTmemPtrOffset = kBarOffset + kNumBars * 8;
   static constexpr int kAbortOffset = kTmemPtrOffset + 4;
-  static constexpr int kBytes = kAbortOffset + 4;
+  static constexpr int kTicketOffset = kAbortOffset + 4;
+  static constexpr int kBytes = kTicketOffset + 4;
   static constexpr int kDynamicBytes = kBytes + 1024;  // room to align the base to 1024 B
 };
 
 struct TileCoord {
   int m_blk, n_blk, kb_begin, kb_end, split;
+  int tile;   // linear tile index (rasterised order)
+  int nseg;   // pieces this tile's K range is computed in (1: this piece is the whole tile)
 };
 
-__device__ __forceinline__ TileCoord decode_work(int w, const GemmParams& p) {
-  const int tile = w / p.splits;
-  const int split = w - tile * p.splits;
+// Tile index -> block coordinates, walking the tile grid in bands of kGroupM row-blocks.
+__device__ __forceinline__ void decode_tile(int tile, const GemmParams& p, TileCoord& t) {
   const int band = kGroupM * p.tiles_n;
   const int g = tile / band;
   const int first_m = g * kGroupM;
   const int rows = min(p.tiles_m - first_m, kGroupM);
   const int in_band = tile - g * band;
-  TileCoord t;
   t.m_blk = first_m + in_band % rows;
   t.n_blk = in_band / rows;
-  t.split = split;
-  t.kb_begin = split * p.kb_per_split;
-  t.kb_end = min(p.num_kb, t.kb_begin + p.kb_per_split);
-  return t;
+  t.tile = tile;
+}
+
+// The sequence of work items of this CTA; producer, MMA issuer and epilogue each walk their own copy.
+struct WorkIter {
+  int w;          // next item (tile x K-split), static round-robin
+  int g, g_end;   // stream-K: next k-block of this CTA's run, and its end
+};
+
+__device__ __forceinline__ WorkIter work_begin(const GemmParams& p) {
+  WorkIter it;
+  it.w = blockIdx.x;
+  it.g = blockIdx.x * p.sk_units;
+  it.g_end = min(p.tiles_m * p.tiles_n * p.num_kb, it.g + p.sk_units);
+  return it;
+}
+
+__device__ __forceinline__ bool work_next(WorkIter& it, const GemmParams& p, TileCoord& t) {
+  if (p.sk_units == 0) {
+    if (it.w >= p.tiles_m * p.tiles_n * p.splits) return false;
+    const int tile = it.w / p.splits;
+    decode_tile(tile, p, t);
+    t.split = it.w - tile * p.splits;
+    t.nseg = p.splits;
+    t.kb_begin = t.split * p.kb_per_split;
+    t.kb_end = min(p.num_kb, t.kb_begin + p.kb_per_split);
+    it.w += gridDim.x;
+    return true;
+  }
+  if (it.g >= it.g_end) return false;
+  const int tile = it.g / p.num_kb;
+  decode_tile(tile, p, t);
+  t.kb_begin = it.g - tile * p.num_kb;
+  t.kb_end = min(p.num_kb, t.kb_begin + (it.g_end - it.g));
+  const int first_cta = (tile * p.num_kb) / p.sk_units;
+  const int last_cta = ((tile + 1) * p.num_kb - 1) / p.sk_units;
+  t.split = static_cast<int>(blockIdx.x) - first_cta;
+  t.nseg = last_cta - first_cta + 1;
+  it.g += t.kb_end - t.kb_begin;
+  return true;
 }
 
 // B_MN = false: B stored [N,K] (K contiguous), one TMA box of BN rows per stage.
@@ -128,6 +174,39 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
   { WIR_TRACE_DECL; if (threadIdx.x == 64) WIR_TRACE_EVENT(p.trace, 2, 20, 0); }
 #endif
 
+  // Producer state (thread 0 only).  The first ring-full of loads is issued right here, before the
+  // rest of the CTA has allocated tensor memory and met at the barrier, so the start-up latency of
+  // the first copies overlaps the rest of the prologue.
+  WorkIter p_work = work_begin(p);
+  TileCoord p_tile;
+  int p_kb = 0, p_kb_end = 0;
+  uint32_t p_it = 0;
+  // 1: one stage issued, 0: no work left, -1: a wait ran out
+  auto producer_step = [&](bool slot_known_free) -> int {
+    if (p_kb >= p_kb_end) {
+      if (!work_next(p_work, p, p_tile)) return 0;
+      p_kb = p_tile.kb_begin;
+      p_kb_end = p_tile.kb_end;
+    }
+    const int s = p_it % STAGES;
+    const uint32_t ph = (p_it / STAGES) & 1;
+    if (!slot_known_free && !mbar_wait(empty_bar(s), ph ^ 1, ctx, kRoleProducer, s, p_kb)) return -1;
+    mbar_arrive_expect_tx(full_bar(s), L::kStageBytes);
+    const uint32_t a_dst = smem_base + s * L::kABytes;
+    const uint32_t b_dst = smem_base + L::kBOffset + s * L::kBBytes;
+    tma_load_2d(a_dst, &tmap_a, full_bar(s), p_kb * kGemmBK, p_tile.m_blk * kTileM);
+    if constexpr (!B_MN) {
+      tma_load_2d(b_dst, &tmap_b, full_bar(s), p_kb * kGemmBK, p_tile.n_blk * BN);
+    } else {
+#pragma unroll
+      for (int c = 0; c < BN / 64; ++c)
+        tma_load_2d(b_dst + c * 8192, &tmap_b, full_bar(s), p_tile.n_blk * BN + c * 64, p_kb * kGemmBK);
+    }
+    ++p_kb;
+    ++p_it;
+    return 1;
+  };
+
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     for (int s = 0; s < STAGES; ++s) {
@@ -140,8 +219,9 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
     }
     mbar_init(drain_bar, 1);
     fence_mbar_init();
-    prefetch_tensormap(&tmap_a);
-    prefetch_tensormap(&tmap_b);
+    fence_proxy_async_smem();
+    for (int n = 0; n < STAGES; ++n)
+      if (producer_step(true) <= 0) break;
   }
   if (warp == 1) {
     tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_ptr_slot)), kTmemCols);
@@ -155,37 +235,17 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
   { WIR_TRACE_DECL; if (threadIdx.x == 64) WIR_TRACE_EVENT(p.trace, 3, 21, 0); }
 #endif
 
-  const int total_work = p.tiles_m * p.tiles_n * p.splits;
-
   if (warp == 0) {
     // ------------------------------------------------------------ producer
     if (lane == 0) {
-      uint32_t it = 0;
-      bool ok = true;
-      for (int w = blockIdx.x; ok && w < total_work; w += gridDim.x) {
-        const TileCoord t = decode_work(w, p);
-        for (int kb = t.kb_begin; kb < t.kb_end; ++kb, ++it) {
-          const int s = it % STAGES;
-          const uint32_t ph = (it / STAGES) & 1;
-          if (!mbar_wait(empty_bar(s), ph ^ 1, ctx, kRoleProducer, s, kb)) { ok = false; break; }
-          mbar_arrive_expect_tx(full_bar(s), L::kStageBytes);
-          const uint32_t a_dst = smem_base + s * L::kABytes;
-          const uint32_t b_dst = smem_base + L::kBOffset + s * L::kBBytes;
-          tma_load_2d(a_dst, &tmap_a, full_bar(s), kb * kGemmBK, t.m_blk * kTileM);
-          if constexpr (!B_MN) {
-            tma_load_2d(b_dst, &tmap_b, full_bar(s), kb * kGemmBK, t.n_blk * BN);
-          } else {
-#pragma unroll
-            for (int c = 0; c < BN / 64; ++c)
-              tma_load_2d(b_dst + c * 8192, &tmap_b, full_bar(s), t.n_blk * BN + c * 64, kb * kGemmBK);
-          }
-        }
+      int r;
+      while ((r = producer_step(false)) > 0) {
       }
-      if (!ok || *abort_flag) {
+      if (r < 0 || *abort_flag) {
         // wait (bounded, silently) for the copies still in flight before the CTA may exit
-        const uint32_t n = it < STAGES ? it : STAGES;
+        const uint32_t n = p_it < STAGES ? p_it : STAGES;
         for (uint32_t back = 1; back <= n; ++back) {
-          const uint32_t idx = it - back;
+          const uint32_t idx = p_it - back;
           mbar_wait_quiet(full_bar(idx % STAGES), (idx / STAGES) & 1);
         }
       }
@@ -198,8 +258,10 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
     uint32_t it = 0, acc_it = 0;
     bool ok = true;
     WIR_TRACE_DECL;
-    for (int w = blockIdx.x; ok && w < total_work; w += gridDim.x, ++acc_it) {
-      const TileCoord t = decode_work(w, p);
+    WorkIter work = work_begin(p);
+    TileCoord t;
+    for (; ok && work_next(work, p, t); ++acc_it) {
+      const int w = t.tile;
       if (lane == 0) WIR_TRACE_EVENT(p.trace, 0, 1, w);
       long long waited = 0;
       const uint32_t acc = kAccBufs == 2 ? (acc_it & 1) : 0;
@@ -249,13 +311,29 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
     uint32_t acc_it = 0;
     bool ok = true;
     WIR_TRACE_DECL;
-    for (int w = blockIdx.x; ok && w < total_work; w += gridDim.x, ++acc_it) {
-      const TileCoord t = decode_work(w, p);
+    WorkIter work = work_begin(p);
+    TileCoord t;
+    for (; ok && work_next(work, p, t); ++acc_it) {
+      const int w = t.tile;
       const uint32_t acc = kAccBufs == 2 ? (acc_it & 1) : 0;
       const uint32_t acc_ph = kAccBufs == 2 ? ((acc_it >> 1) & 1) : (acc_it & 1);
       if (warp == 2 && lane == 0) WIR_TRACE_EVENT(p.trace, 1, 10, w);
-      const bool got = mbar_wait(acc_full_bar(acc), acc_ph, ctx, kRoleEpilogue, acc, w);
-      if (!__all_sync(0xffffffffu, got)) { ok = false; break; }
+      bool got = mbar_wait(acc_full_bar(acc), acc_ph, ctx, kRoleEpilogue, acc, w);
+      got = __all_sync(0xffffffffu, got);
+      if (p.sk_units != 0) {
+        // the four epilogue warps meet at named barriers below, so they must agree on whether to go on
+        uint32_t all;
+        asm volatile(
+            "{\n\t.reg .pred a, q;\n\t"
+            "setp.ne.u32 q, %1, 0;\n\t"
+            "bar.red.and.pred a, 1, 128, q;\n\t"
+            "selp.u32 %0, 1, 0, a;\n\t}"
+            : "=r"(all)
+            : "r"(got ? 1u : 0u)
+            : "memory");
+        got = all != 0;
+      }
+      if (!got) { ok = false; break; }
       tc_fence_after();
       if (warp == 2 && lane == 0) WIR_TRACE_EVENT(p.trace, 1, 11, w);
       const int row = t.m_blk * kTileM + mt * kGemmBM + quarter * 32 + lane;
@@ -269,7 +347,7 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
         tmem_wait_ld();
         const int col0 = t.n_blk * BN + c * kChunk;
         if (row < p.M && col0 < p.N) {
-          if (p.splits == 1) {
+          if (t.nseg == 1) {
             __nv_bfloat16* dst = p.C + static_cast<size_t>(row) * p.ldc + col0;
             if (vec_ok && col0 + kChunk <= p.N) {
 #pragma unroll
@@ -286,6 +364,13 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
               for (int j = 0; j < kChunk; ++j)
                 if (col0 + j < p.N) dst[j] = __float2bfloat16_rn(__uint_as_float(r[j]));
             }
+          } else if (p.sk_units != 0) {
+            // stream-K: slot [tile][segment] of sk_rows x BN floats, whole chunks (columns past N are never read)
+            float* dst = p.partial + ((static_cast<size_t>(t.tile) * p.sk_max_seg + t.split) * p.sk_rows +
+                                      (mt * kGemmBM + quarter * 32 + lane)) * BN + c * kChunk;
+#pragma unroll
+            for (int v = 0; v < kChunk / 4; ++v)
+              reinterpret_cast<uint4*>(dst)[v] = make_uint4(r[4 * v], r[4 * v + 1], r[4 * v + 2], r[4 * v + 3]);
           } else {
             float* dst = p.partial + (static_cast<size_t>(t.split) * p.M + row) * p.N + col0;
             if ((p.N % 4 == 0) && col0 + kChunk <= p.N) {
@@ -303,6 +388,70 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
       tc_fence_before();
       mbar_arrive(acc_empty_bar(acc));
       if (warp == 2 && lane == 0) WIR_TRACE_EVENT(p.trace, 1, 12, w);
+      if (p.sk_units != 0 && t.nseg > 1) {
+        // Whoever brings the last segment of a tile finishes it.  Nobody waits: each CTA publishes
+        // its slot, takes a ticket, and only the holder of the last ticket reads the slots back
+        // (in segment order, so the sum does not depend on who arrived when).
+        volatile int* ticket_slot = reinterpret_cast<volatile int*>(smem + L::kTicketOffset);
+        const int epi_tid = threadIdx.x - 64;
+        __threadfence();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (epi_tid == 0) *ticket_slot = atomicAdd(p.sk_counters + t.tile, 1);
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        const bool last = (*ticket_slot == t.nseg - 1);
+        asm volatile("bar.sync 1, 128;" ::: "memory");   // the slot is free for the next item
+        if (last) {
+          __threadfence();
+          const int row0 = t.m_blk * kTileM, col0 = t.n_blk * BN;
+          const int rows = min(p.sk_rows, p.M - row0);
+          const float* slot0 = p.partial + static_cast<size_t>(t.tile) * p.sk_max_seg * p.sk_rows * BN;
+          // all loads of a batch (kFixU float4 per thread x up to kFixSeg segments) are issued before
+          // the first add, so a batch costs about one L2 round trip
+          constexpr int kFixU = 8, kFixSeg = 4;
+          const int n4 = (rows * BN) >> 2;
+          const size_t seg_stride4 = (static_cast<size_t>(p.sk_rows) * BN) >> 2;
+          const float4* base4 = reinterpret_cast<const float4*>(slot0);
+          for (int first = epi_tid; first < n4; first += 128 * kFixU) {
+            float4 v[kFixSeg][kFixU];
+#pragma unroll
+            for (int sgm = 0; sgm < kFixSeg; ++sgm)
+#pragma unroll
+              for (int u = 0; u < kFixU; ++u) {
+                const int idx = first + u * 128;
+                v[sgm][u] = (sgm < t.nseg && idx < n4) ? __ldcg(base4 + sgm * seg_stride4 + idx)
+                                                       : make_float4(0.f, 0.f, 0.f, 0.f);
+              }
+#pragma unroll
+            for (int u = 0; u < kFixU; ++u) {
+              const int idx = first + u * 128;
+              if (idx >= n4) break;
+              float4 sum = v[0][u];
+#pragma unroll
+              for (int sgm = 1; sgm < kFixSeg; ++sgm)
+                if (sgm < t.nseg) { sum.x += v[sgm][u].x; sum.y += v[sgm][u].y; sum.z += v[sgm][u].z; sum.w += v[sgm][u].w; }
+              for (int sgm = kFixSeg; sgm < t.nseg; ++sgm) {   // tiles cut into more pieces than a batch holds
+                const float4 w4 = __ldcg(base4 + sgm * seg_stride4 + idx);
+                sum.x += w4.x; sum.y += w4.y; sum.z += w4.z; sum.w += w4.w;
+              }
+              const int e = idx << 2;
+              const int r_in = e / BN, c_in = e - r_in * BN;
+              const int col = col0 + c_in;
+              __nv_bfloat16* dst = p.C + static_cast<size_t>(row0 + r_in) * p.ldc + col;
+              if (vec_ok && col + 4 <= p.N) {
+                uint2 q;
+                q.x = pack_bf16(sum.x, sum.y);
+                q.y = pack_bf16(sum.z, sum.w);
+                *reinterpret_cast<uint2*>(dst) = q;
+              } else {
+                const float vals[4] = {sum.x, sum.y, sum.z, sum.w};
+                for (int k4 = 0; k4 < 4; ++k4)
+                  if (col + k4 < p.N) dst[k4] = __float2bfloat16_rn(vals[k4]);
+              }
+            }
+          }
+          if (epi_tid == 0) p.sk_counters[t.tile] = 0;   // ready for the next launch
+        }
+      }
     }
   }
 

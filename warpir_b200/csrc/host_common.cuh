@@ -46,7 +46,9 @@ struct DeviceState {
   int* status = nullptr;        // 4 ints
   float* splitk = nullptr;      // grown on demand
   size_t splitk_bytes = 0;
+  int* sk_counters = nullptr;   // kSkMaxTiles arrival counters of the stream-K GEMM, zero between launches
 };
+constexpr int kSkMaxTiles = 8192;
 
 inline std::mutex g_mutex;
 inline DeviceState g_dev[kMaxDevices];
@@ -84,6 +86,8 @@ inline int get_device_state(int device, DeviceState** out) {
     WIR_CUDA(cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, device));
     WIR_CUDA(cudaMalloc(&d.status, 4 * sizeof(int)));
     WIR_CUDA(cudaMemset(d.status, 0, 4 * sizeof(int)));
+    WIR_CUDA(cudaMalloc(&d.sk_counters, kSkMaxTiles * sizeof(int)));
+    WIR_CUDA(cudaMemset(d.sk_counters, 0, kSkMaxTiles * sizeof(int)));
     d.ready = true;
   }
   if (g_encode == nullptr) {
@@ -218,7 +222,11 @@ inline int read_status_impl(int device, void* cuda_stream, int* code, int* detai
   int host[4] = {0, 0, 0, 0};
   WIR_CUDA(cudaStreamSynchronize(stream));
   WIR_CUDA(cudaMemcpy(host, dev->status, sizeof host, cudaMemcpyDeviceToHost));
-  if (host[0] != 0) WIR_CUDA(cudaMemset(dev->status, 0, sizeof host));
+  if (host[0] != 0) {
+    WIR_CUDA(cudaMemset(dev->status, 0, sizeof host));
+    // a kernel that gave up may have left stream-K tickets behind
+    WIR_CUDA(cudaMemset(dev->sk_counters, 0, kSkMaxTiles * sizeof(int)));
+  }
   if (code) *code = host[0];
   if (detail) *detail = host[2];
   if (host[0] != 0)

@@ -30,6 +30,7 @@ int launch_gemm_cfg(const CUtensorMap& ta, const CUtensorMap& tb, const wir::Gem
 struct GemmChoice {
   int block_n;
   int splits;
+  bool stream_k = false;   // deal k-blocks, not tiles, out to the CTAs (few rows: HBM-bound on B)
   int mt = 1;   // CTA tile height in units of 128 rows
   int a_rows = 128;   // rows of A loaded per stage (fewer for problems with few rows)
 };
@@ -40,6 +41,16 @@ inline int env_attn_stagger() {
   static const int v = [] {
     const char* e = getenv("WARPIR_ATTN_STAGGER");
     return e ? atoi(e) : 1000;
+  }();
+  return v;
+}
+
+// Tuning override for experiments: WARPIR_SKINNY_BN=64|128|256 picks the tile width for problems
+// with few rows (64: static tiles, no stream-K).
+inline int env_skinny_bn() {
+  static const int v = [] {
+    const char* e = getenv("WARPIR_SKINNY_BN");
+    return e ? atoi(e) : 0;
   }();
   return v;
 }
@@ -117,10 +128,27 @@ inline int gemm_impl(const void* A, const void* B, void* C, int64_t M, int64_t N
   if (fixed != nullptr) ch.mt = fixed_mt;
   // few rows: 64-wide tiles (many CTAs streaming B), only the existing rows of A are loaded and
   // the saved shared memory deepens the ring so more of B is in flight per SM
+  // With splits left to the library the k-blocks are dealt out evenly over all SMs (stream-K)
+  // and the tiles are wider, which makes the TMA boxes of B larger.
   if (fixed == nullptr && block_n == 0 && M <= 64 && N >= 64 * 64) {
     ch.block_n = 64;
     ch.mt = 1;
     ch.a_rows = (M <= 16) ? 16 : 64;
+    const int want = env_skinny_bn() ? env_skinny_bn() : 128;
+    // Shared tiles cost a round trip of fp32 partial sums through L2, which grows with the row
+    // count: above 32 rows the static 64-wide tiling wins unless it leaves many SMs idle.
+    const int64_t tiles64 = (N + 63) / 64;
+    const double static_fill = static_cast<double>(tiles64) /
+                               static_cast<double>(((tiles64 + dev->sm_count - 1) / dev->sm_count) * dev->sm_count);
+    if (splits == 0 && (want == 128 || want == 256) && N % 4 == 0 && (M <= 32 || static_fill < 0.7)) {
+      const int64_t tiles = (N + want - 1) / want;
+      const int64_t units = tiles * ((K + wir::kGemmBK - 1) / wir::kGemmBK);
+      if (tiles <= kSkMaxTiles && units >= 4 * dev->sm_count) {
+        ch.block_n = want;
+        ch.stream_k = true;
+        ch.splits = 1;
+      }
+    }
   }
   if (env_gemm_mt() == 1 && fixed == nullptr) ch.mt = 1;
   if (env_gemm_mt() == 2 && ch.block_n == 256 && fixed == nullptr) ch.mt = 2;
@@ -145,8 +173,21 @@ inline int gemm_impl(const void* A, const void* B, void* C, int64_t M, int64_t N
   p.status = dev->status;
   p.trace = g_trace;
 
-  if (p.splits > 1) {
-    const size_t need = static_cast<size_t>(p.splits) * M * N * sizeof(float);
+  int64_t work = static_cast<int64_t>(p.tiles_m) * p.tiles_n * p.splits;
+  int grid = static_cast<int>(work < dev->sm_count ? work : dev->sm_count);
+  size_t sk_bytes = 0;
+  if (ch.stream_k) {
+    const int64_t units = static_cast<int64_t>(p.tiles_m) * p.tiles_n * num_kb;
+    p.sk_units = static_cast<int>((units + dev->sm_count - 1) / dev->sm_count);
+    grid = static_cast<int>((units + p.sk_units - 1) / p.sk_units);
+    p.sk_max_seg = (num_kb + p.sk_units - 2) / p.sk_units + 1;
+    p.sk_rows = static_cast<int>(M < wir::kGemmBM ? M : wir::kGemmBM);
+    p.sk_counters = dev->sk_counters;
+    sk_bytes = static_cast<size_t>(p.tiles_m) * p.tiles_n * p.sk_max_seg * p.sk_rows * ch.block_n * sizeof(float);
+  }
+
+  if (p.splits > 1 || ch.stream_k) {
+    const size_t need = ch.stream_k ? sk_bytes : static_cast<size_t>(p.splits) * M * N * sizeof(float);
     std::lock_guard<std::mutex> lock(g_mutex);
     if (dev->splitk_bytes < need) {
       if (dev->splitk) {
@@ -183,11 +224,13 @@ inline int gemm_impl(const void* A, const void* B, void* C, int64_t M, int64_t N
     if (int rc = make_tmap(&tb, B, 2, dims, strides, box)) return rc;
   }
 
-  const int64_t work = static_cast<int64_t>(p.tiles_m) * p.tiles_n * p.splits;
-  const int grid = static_cast<int>(work < dev->sm_count ? work : dev->sm_count);
   int rc;
   const bool mn = (b_layout == 0);
   if (fixed != nullptr) rc = fixed(ta, tb, p, grid, stream);
+  else if (ch.stream_k && ch.block_n == 128 && ch.a_rows == 16) rc = mn ? launch_gemm_cfg<128, 10, true, 1, 16>(ta, tb, p, grid, stream) : launch_gemm_cfg<128, 10, false, 1, 16>(ta, tb, p, grid, stream);
+  else if (ch.stream_k && ch.block_n == 128) rc = mn ? launch_gemm_cfg<128, 8, true, 1, 64>(ta, tb, p, grid, stream) : launch_gemm_cfg<128, 8, false, 1, 64>(ta, tb, p, grid, stream);
+  else if (ch.stream_k && ch.a_rows == 16) rc = mn ? launch_gemm_cfg<256, 6, true, 1, 16>(ta, tb, p, grid, stream) : launch_gemm_cfg<256, 6, false, 1, 16>(ta, tb, p, grid, stream);
+  else if (ch.stream_k) rc = mn ? launch_gemm_cfg<256, 5, true, 1, 64>(ta, tb, p, grid, stream) : launch_gemm_cfg<256, 5, false, 1, 64>(ta, tb, p, grid, stream);
   else if (ch.a_rows == 16) rc = mn ? launch_gemm_cfg<64, 19, true, 1, 16>(ta, tb, p, grid, stream) : launch_gemm_cfg<64, 19, false, 1, 16>(ta, tb, p, grid, stream);
   else if (ch.a_rows == 64) rc = mn ? launch_gemm_cfg<64, 12, true, 1, 64>(ta, tb, p, grid, stream) : launch_gemm_cfg<64, 12, false, 1, 64>(ta, tb, p, grid, stream);
   else if (ch.mt == 2) rc = mn ? launch_gemm_cfg<256, 3, true, 2>(ta, tb, p, grid, stream) : launch_gemm_cfg<256, 3, false, 2>(ta, tb, p, grid, stream);

@@ -264,6 +264,23 @@ class LoadedKernel:
             raise WarpirError(rc, load_library().warpir_strerror(rc).decode(), self._err().decode())
 
 
+def _included_text(source: str, repo_root: Path) -> str:
+    """Text of every header of this package that ``source`` includes, directly or not (the
+    cache key of a compiled translation unit covers exactly what it is built from)."""
+    import re
+    csrc = repo_root / "warpir_b200" / "csrc"
+    seen, todo = {}, re.findall(r'#include "warpir_b200/csrc/([\w.]+)"', source)
+    while todo:
+        name = todo.pop()
+        path = csrc / name
+        if name in seen or not path.exists():
+            continue
+        seen[name] = path.read_text()
+        todo += re.findall(r'#include "([\w.]+)"', seen[name])
+    seen["warpir_b200.h"] = (repo_root / "include" / "warpir_b200.h").read_text()
+    return "".join(seen[k] for k in sorted(seen))
+
+
 def compile_source(source: str, name: str) -> Path:
     """nvcc the emitted translation unit for sm_100a into ``warpir_b200/_jit`` (cached by
     content hash, in-tree so the built file travels with the checkout)."""
@@ -271,7 +288,7 @@ def compile_source(source: str, name: str) -> Path:
     import subprocess
     from . import build as _build
     repo_root = Path(__file__).resolve().parent.parent
-    deps = "".join(f.read_text() for f in sorted((repo_root / "warpir_b200" / "csrc").glob("*.cuh")))
+    deps = _included_text(source, repo_root)
     digest = hashlib.sha256((source + deps).encode()).hexdigest()[:16]
     _JIT_DIR.mkdir(exist_ok=True)
     so = _JIT_DIR / f"{name}_{digest}.so"
