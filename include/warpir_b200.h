@@ -138,6 +138,24 @@ int warpir_attn_fwd_bf16(const void* Q, const void* K, const void* V, void* O, f
                          float softmax_scale, int causal, int device, void* cuda_stream);
 
 /*
+ * Attention backward: gradients of warpir_attn_fwd_bf16's O with respect to Q, K and V.
+ *   Q, O, dO: [B, Hq, S, D] bf16;  K, V: [B, Hkv, S, D] bf16;  LSE: [B, Hq, S] fp32 as written
+ *   by the forward (natural log);  dQ: [B, Hq, S, D] fp32;  dK, dV: [B, Hkv, S, D] fp32
+ *   (summed over the query heads that share a K/V head);  delta_ws: [B, Hq, S] fp32
+ *   workspace owned by the caller (receives rowsum(dO * O)).  All contiguous, 16-byte
+ *   aligned; same size rules, scale and causal convention as the forward.
+ * Two launches on `cuda_stream` (dQ, then dK and dV); no atomics, results repeat bit for bit.
+ * Replaces the host wrapper `attention_backward(q, k, v, o, l_vec, og, causal)` of the
+ * reference's hand-written target (kernel_examples/attention/mha_h100.cu:799-1010), which
+ * likewise returns fp32 gradients and keeps a d_vec workspace; unlike it, LSE here is the
+ * plain log-sum-exp, not the reference's negated and rescaled L vector (mha_h100.cu:216-221).
+ */
+int warpir_attn_bwd_bf16(const void* Q, const void* K, const void* V, const void* O, const void* dO,
+                         const float* LSE, float* dQ, float* dK, float* dV, float* delta_ws,
+                         int64_t B, int64_t Hq, int64_t Hkv, int64_t S, int64_t D,
+                         float softmax_scale, int causal, int device, void* cuda_stream);
+
+/*
  * Waits for `cuda_stream`, then reports and clears the device's status words:
  * *code is 0 when every kernel launched so far on this device ran to completion,
  * otherwise the kernel-side error (1 = a bounded wait ran out); *detail packs

@@ -108,6 +108,32 @@ def attention_ref(Q: torch.Tensor, K: torch.Tensor, V: torch.Tensor,
     return O, L
 
 
+def attention_backward_ref(Q: torch.Tensor, K: torch.Tensor, V: torch.Tensor, dO: torch.Tensor,
+                           scale: Optional[float] = None, causal: bool = False):
+    """Gradients of ``attention_ref``'s output by torch autograd on fp32 CPU tensors (the
+    definition the reference's own backward, kernel_examples/attention/mha_h100.cu:483-642,
+    is meant to match; the reference ships no test of it).  With grouped K/V heads the
+    gradients of K and V are summed over the query heads of a group.  Returns
+    ``(dQ, dK, dV)`` in fp32."""
+    Bz, H, S, D = Q.shape
+    Hkv = K.shape[1]
+    q = Q.float().clone().requires_grad_(True)
+    k = K.float().clone().requires_grad_(True)
+    v = V.float().clone().requires_grad_(True)
+    total = None
+    for b in range(Bz):
+        for h in range(H):
+            hk = h // (H // Hkv)
+            o, _ = attention_slice_ref(q[b, h], k[b, hk], v[b, hk], scale, causal)
+            term = (o * dO[b, h].float()).sum()
+            total = term if total is None else total + term
+    total.backward()
+    return q.grad, k.grad, v.grad
+
+
+ATTN_GRAD_REL_TOL = 1e-2  # max |grad - ref| / max |ref|, attention backward (P and dS are rounded to bf16)
+
+
 # ---------------------------------------------------------------------------
 # error metrics
 # ---------------------------------------------------------------------------

@@ -94,3 +94,30 @@ def test_tile_attention_reproduces_reference_golden(golden_dir):
     Q, K, V, O = (bf16(z[f"n256_d64_{n}"]) for n in "QKVO")
     O_c, _ = T.tile_attention(Q, K, V, 0.125, False, 64, 64)
     assert (O_c.float() - O.float()).abs().max().item() <= R.ATTN_O_ABS_TOL
+
+
+@pytest.mark.parametrize("causal", [False, True])
+def test_backward_oracle_matches_the_closed_form(causal):
+    """The autograd oracle of the attention backward against the textbook expressions
+    dV = P^T dO, dP = dO V^T, dS = P * (dP - rowsum(dO * O)) * scale, dQ = dS K, dK = dS^T Q,
+    with grouped K/V heads summed over their query heads."""
+    B, H, Hkv, S, D = 1, 4, 2, 96, 64
+    Q, K, V = R.attention_inputs(B, H, S, D, seed=21, Hkv=Hkv)
+    dO = R.randn_bf16((B, H, S, D), torch.Generator().manual_seed(22))
+    dQ, dK, dV = R.attention_backward_ref(Q, K, V, dO, None, causal)
+    scale = 1.0 / math.sqrt(D)
+    dK2, dV2 = torch.zeros_like(dK), torch.zeros_like(dV)
+    for h in range(H):
+        hk = h // (H // Hkv)
+        q, k, v, g = Q[0, h].double(), K[0, hk].double(), V[0, hk].double(), dO[0, h].double()
+        s = q @ k.T * scale
+        if causal:
+            s = s.masked_fill(~torch.ones(S, S, dtype=torch.bool).tril(), float("-inf"))
+        p = torch.softmax(s, dim=-1)
+        o = p @ v
+        ds = p * (g @ v.T - (g * o).sum(-1, keepdim=True)) * scale
+        assert torch.allclose(dQ[0, h].double(), ds @ k, atol=1e-4, rtol=1e-4)
+        dK2[0, hk] += (ds.T @ q).float()
+        dV2[0, hk] += (p.T @ g).float()
+    assert torch.allclose(dK, dK2, atol=1e-4, rtol=1e-4)
+    assert torch.allclose(dV, dV2, atol=1e-4, rtol=1e-4)

@@ -1,0 +1,396 @@
+// Attention backward for sm_100a: given Q, K, V, O, dO and the forward's LSE, computes
+// dQ, dK, dV (fp32), the counterpart of the reference's hand-written Hopper backward
+// (kernel_examples/attention/mha_h100.cu:239-642: a preparation kernel for
+// delta = rowsum(dO * O), then the gradient kernel; host wrapper attention_backward,
+// mha_h100.cu:799-1010, which also returns fp32 gradients).
+//
+// With c = scale * log2(e):  P = 2^(c Q K^T - LSE log2 e),  dP = dO V^T,
+// dS = P * (dP - delta) * scale,  dV = P^T dO,  dK = dS^T Q,  dQ = dS K.
+//
+// The reference accumulates dQ with atomics from the CTAs that own the K/V tiles.  Here
+// the work is two launches of ONE kernel template, each deterministic and atomic-free:
+//
+//   DKV = false (grid over 128-row Q tiles):  streams 64-key K/V tiles, recomputes S and
+//     dP, accumulates dQ in tensor memory.  Its prologue also computes delta and stores
+//     it for the second launch.
+//   DKV = true  (grid over 128-key K/V tiles): streams 64-row Q/dO tiles of every query
+//     head of the group, recomputes S^T and dP^T, accumulates dV and dK.
+//
+// Both are the same pipeline on different operands.  With X0, X1 the two resident
+// 128 x D tiles and Y0, Y1 the streamed 64 x D tiles of step `it`:
+//
+//   stage 1 (tcgen05.mma, SS):  T0 = X0 Y0^T,  T1 = X1 Y1^T          (128 x 64 each)
+//   compute warps:              P = 2^(c T0 - L2),  dS = P (T1 - delta) scale, both
+//                               packed to bf16 over the low columns of T0 / T1
+//   stage 2 (tcgen05.mma, TS):  DKV:  acc0 += P  Y1   (dV),  acc1 += dS Y0   (dK)
+//                               else: acc0 += dS Y0   (dQ)
+//
+//   (DKV = false: X = Q, dO and Y = K, V, statistics per row.
+//    DKV = true:  X = K, V  and Y = Q, dO, statistics per column.)
+//
+// Tensor memory: T0[2] at columns 0 / 64, T1[2] at 128 / 192 (double-buffered so stage 1
+// of step it+1 runs while the compute warps work on step it), acc0 at 256, acc1 at
+// 256 + D.  Warp 0 is the TMA producer, warp 1 issues every MMA (whole warp, one elected
+// lane), warps 2-5 are the compute warps (one tensor-memory lane = one row per thread).
+// MMAs execute in issue order, which makes the aliasing safe: stage 1 of step it+2
+// overwrites T0/T1[b] only after stage 2 of step it, which reads P/dS from them.
+#pragma once
+
+#include "ptx.cuh"
+
+namespace wir {
+
+constexpr int kBwdBX = 128;        // rows of the resident tiles = MMA M
+constexpr int kBwdBY = 64;         // rows of the streamed tiles = MMA N of stage 1, K of stage 2
+constexpr int kBwdThreads = 192;
+
+struct AttnBwdParams {
+  int B, H, Hkv, S;
+  float scale;             // softmax scale
+  float scale_log2;        // scale * log2(e)
+  const __nv_bfloat16* O;  // [B, H, S, D]   (DKV = false: for delta)
+  const __nv_bfloat16* dO; // [B, H, S, D]
+  const float* LSE;        // [B, H, S] natural-log logsumexp of the scaled scores
+  float* delta;            // [B, H, S] written by the DKV = false launch, read by the other
+  float* out0;             // DKV = false: dQ [B, H, S, D];  DKV = true: dV [B, Hkv, S, D]
+  float* out1;             // DKV = true: dK [B, Hkv, S, D]
+  int* status;
+};
+
+template <int D>
+struct AttnBwdSmem {
+  static constexpr int kStages = (D == 128) ? 4 : 8;
+  static constexpr int kXChunkBytes = kBwdBX * 128;
+  static constexpr int kXTileBytes = (D / 64) * kXChunkBytes;
+  static constexpr int kYChunkBytes = kBwdBY * 128;
+  static constexpr int kYTileBytes = (D / 64) * kYChunkBytes;
+  static constexpr int kYOffset = 2 * kXTileBytes;
+  static constexpr int kStatsOffset = kYOffset + kStages * 2 * kYTileBytes;   // [2 buffers][2 vectors][64] floats
+  static constexpr int kBarOffset = kStatsOffset + 2 * 2 * kBwdBY * 4;
+  // x_full, y_full[S], y_empty[S], t_full[2], pds_full[2], acc_done, drain
+  static constexpr int kNumBars = 1 + 2 * kStages + 6;
+  static constexpr int kTmemPtrOffset = kBarOffset + kNumBars * 8;
+  static constexpr int kAbortOffset = kTmemPtrOffset + 4;
+  static constexpr int kBytes = kAbortOffset + 4;
+  static constexpr int kDynamicBytes = kBytes + 1024;
+};
+
+template <int D, bool CAUSAL, bool DKV>
+__global__ void __launch_bounds__(kBwdThreads, 1)
+attn_bwd_sm100(const __grid_constant__ CUtensorMap tmap_x0, const __grid_constant__ CUtensorMap tmap_x1,
+               const __grid_constant__ CUtensorMap tmap_y0, const __grid_constant__ CUtensorMap tmap_y1,
+               const AttnBwdParams p) {
+  using L = AttnBwdSmem<D>;
+  constexpr int STAGES = L::kStages;
+  constexpr uint32_t kTmemCols = 512;
+  constexpr uint32_t kAccCol = 256;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const uint32_t smem_base = smem_u32(smem);
+  const uint32_t bar_base = smem_base + L::kBarOffset;
+  const uint32_t x_full = bar_base;
+  auto y_full = [&](int s) { return bar_base + 8u * (1 + s); };
+  auto y_empty = [&](int s) { return bar_base + 8u * (1 + STAGES + s); };
+  auto t_full = [&](int b) { return bar_base + 8u * (1 + 2 * STAGES + b); };
+  auto pds_full = [&](int b) { return bar_base + 8u * (3 + 2 * STAGES + b); };
+  const uint32_t acc_done = bar_base + 8u * (5 + 2 * STAGES);
+  const uint32_t drain_bar = bar_base + 8u * (6 + 2 * STAGES);
+  volatile uint32_t* tmem_ptr_slot = reinterpret_cast<volatile uint32_t*>(smem + L::kTmemPtrOffset);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kAbortOffset);
+  float* stats = reinterpret_cast<float*>(smem + L::kStatsOffset);
+  const AbortCtx ctx{abort_flag, p.status};
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  // ---- which tile, which steps ---------------------------------------------------------
+  const int group = p.H / p.Hkv;
+  const int batch = blockIdx.z;
+  const int ny = (p.S + kBwdBY - 1) / kBwdBY;          // 64-row tiles along the sequence
+  // DKV = false: blockIdx.x (heaviest causal tiles first) is the Q tile, blockIdx.y the query head.
+  // DKV = true : blockIdx.x is the K/V tile, blockIdx.y the K/V head.
+  const int xt = (!DKV && CAUSAL) ? (gridDim.x - 1 - blockIdx.x) : blockIdx.x;
+  const int x_row0 = xt * kBwdBX;
+  const int head = blockIdx.y;
+  const int x_plane = DKV ? (batch * p.Hkv + head) : (batch * p.H + head);
+  // steps: DKV = false walks K/V tiles 0 .. y_end-1 of the head's K/V head;
+  //        DKV = true  walks, for each query head of the group, Q tiles y_begin .. ny-1
+  const int y_begin = (DKV && CAUSAL) ? (x_row0 / kBwdBY) : 0;
+  const int y_end = (!DKV && CAUSAL) ? min(ny, (x_row0 + kBwdBX) / kBwdBY) : ny;
+  const int per_head = max(0, y_end - y_begin);
+  const int n_it = DKV ? per_head * group : per_head;
+  auto y_tile_of = [&](int it) { return y_begin + (DKV ? it % per_head : it); };
+  auto y_plane_of = [&](int it) {
+    return DKV ? (batch * p.H + head * group + it / per_head) : (batch * p.Hkv + head / group);
+  };
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    mbar_init(x_full, 1);
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(y_full(s), 1);
+      mbar_init(y_empty(s), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(t_full(b), 1);
+      mbar_init(pds_full(b), 128);
+    }
+    mbar_init(acc_done, 1);
+    mbar_init(drain_bar, 1);
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_ptr_slot)), kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_ptr_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ producer
+    if (lane == 0 && n_it > 0) {
+      mbar_arrive_expect_tx(x_full, 2 * L::kXTileBytes);
+#pragma unroll
+      for (int c = 0; c < D / 64; ++c) {
+        tma_load_3d(smem_base + c * L::kXChunkBytes, &tmap_x0, x_full, c * 64, x_row0, x_plane);
+        tma_load_3d(smem_base + L::kXTileBytes + c * L::kXChunkBytes, &tmap_x1, x_full, c * 64, x_row0, x_plane);
+      }
+      bool ok = true;
+      int it = 0;
+      for (; ok && it < n_it; ++it) {
+        const int s = it % STAGES;
+        const uint32_t ph = (it / STAGES) & 1;
+        if (!mbar_wait(y_empty(s), ph ^ 1, ctx, kRoleProducer, s, it)) { ok = false; break; }
+        mbar_arrive_expect_tx(y_full(s), 2 * L::kYTileBytes);
+        const uint32_t dst = smem_base + L::kYOffset + s * 2 * L::kYTileBytes;
+        const int row = y_tile_of(it) * kBwdBY, plane = y_plane_of(it);
+#pragma unroll
+        for (int c = 0; c < D / 64; ++c) {
+          tma_load_3d(dst + c * L::kYChunkBytes, &tmap_y0, y_full(s), c * 64, row, plane);
+          tma_load_3d(dst + L::kYTileBytes + c * L::kYChunkBytes, &tmap_y1, y_full(s), c * 64, row, plane);
+        }
+      }
+      if (!ok || *abort_flag) {
+        mbar_wait_quiet(x_full, 0);
+        const int n = it < STAGES ? it : STAGES;
+        for (int back = 1; back <= n; ++back) {
+          const int i = it - back;
+          mbar_wait_quiet(y_full(i % STAGES), (i / STAGES) & 1);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    constexpr uint32_t idesc_t = idesc_bf16_f32(kBwdBX, kBwdBY, 0, 0);   // X Y^T: both K-major
+    constexpr uint32_t idesc_acc = idesc_bf16_f32(kBwdBX, D, 0, 1);      // (P | dS) Y: B is MN-major
+    constexpr uint32_t desc_hi = smem_desc_hi_sw128(1024);
+    const uint32_t x0_lo = smem_desc_lo(smem_base, 16);
+    const uint32_t x1_lo = smem_desc_lo(smem_base + L::kXTileBytes, 16);
+    auto y_addr = [&](int it) { return smem_base + L::kYOffset + (it % STAGES) * 2 * L::kYTileBytes; };
+    bool ok = true;
+    auto stage1 = [&](int it) -> bool {
+      if (!mbar_wait_warp(y_full(it % STAGES), (it / STAGES) & 1, ctx, kRoleMma, 10, it)) return false;
+      tc_fence_after();
+      const int b = it & 1;
+      const uint32_t y0_lo = smem_desc_lo(y_addr(it), 16);
+      const uint32_t y1_lo = smem_desc_lo(y_addr(it) + L::kYTileBytes, 16);
+#pragma unroll
+      for (int k = 0; k < D / 16; ++k) {
+        const uint32_t x_off = ((k / 4) * L::kXChunkBytes + (k % 4) * 32) >> 4;
+        const uint32_t y_off = ((k / 4) * L::kYChunkBytes + (k % 4) * 32) >> 4;
+        mma_ss_elect(tmem_base + b * 64, x0_lo + x_off, desc_hi, y0_lo + y_off, desc_hi, idesc_t, k > 0 ? 1u : 0u);
+      }
+#pragma unroll
+      for (int k = 0; k < D / 16; ++k) {
+        const uint32_t x_off = ((k / 4) * L::kXChunkBytes + (k % 4) * 32) >> 4;
+        const uint32_t y_off = ((k / 4) * L::kYChunkBytes + (k % 4) * 32) >> 4;
+        mma_ss_elect(tmem_base + 128 + b * 64, x1_lo + x_off, desc_hi, y1_lo + y_off, desc_hi, idesc_t, k > 0 ? 1u : 0u);
+      }
+      mma_commit_elect(t_full(b));
+      return true;
+    };
+
+    if (n_it > 0) ok = mbar_wait_warp(x_full, 0, ctx, kRoleMma, 1, 0);
+    for (int it = 0; ok && it < 2 && it < n_it; ++it) ok = stage1(it);
+    for (int it = 0; ok && it < n_it; ++it) {
+      const int b = it & 1;
+      if (!mbar_wait_warp(pds_full(b), (it >> 1) & 1, ctx, kRoleMma, 20, it)) { ok = false; break; }
+      tc_fence_after();
+      // as B operands the streamed tiles are read with the 64 tile rows as K: chunks of 64
+      // columns kYChunkBytes apart, 16 rows (2048 bytes) per k-step
+      const uint32_t y0_mn = smem_desc_lo(y_addr(it), L::kYChunkBytes);
+      const uint32_t y1_mn = smem_desc_lo(y_addr(it) + L::kYTileBytes, L::kYChunkBytes);
+      const uint32_t p_tmem = tmem_base + b * 64;          // bf16 P over T0[b]
+      const uint32_t ds_tmem = tmem_base + 128 + b * 64;   // bf16 dS over T1[b]
+#pragma unroll
+      for (int k = 0; k < kBwdBY / 16; ++k) {
+        const uint32_t acc = (it > 0 || k > 0) ? 1u : 0u;
+        if constexpr (DKV) {
+          mma_ts_elect(tmem_base + kAccCol, p_tmem + k * 8, y1_mn + ((k * 2048) >> 4), desc_hi, idesc_acc, acc);
+          mma_ts_elect(tmem_base + kAccCol + D, ds_tmem + k * 8, y0_mn + ((k * 2048) >> 4), desc_hi, idesc_acc, acc);
+        } else {
+          mma_ts_elect(tmem_base + kAccCol, ds_tmem + k * 8, y0_mn + ((k * 2048) >> 4), desc_hi, idesc_acc, acc);
+        }
+      }
+      mma_commit_elect(y_empty(it % STAGES));
+      if (it + 1 == n_it) mma_commit_elect(acc_done);
+      if (it + 2 < n_it) ok = stage1(it + 2);
+    }
+    if (!ok || *abort_flag) {
+      mma_commit_elect(drain_bar);
+      mbar_wait_quiet(drain_bar, 0);
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------------------------------------------ compute warps
+    const int quarter = warp & 3;                       // tensor-memory lanes 32*quarter .. +31
+    const int tid = quarter * 32 + lane;                // row of the resident tiles owned by this thread
+    const int x_row = x_row0 + tid;
+    const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+    const float c = p.scale_log2;
+    constexpr float kLog2e = 1.4426950408889634f;
+    bool ok = true;
+
+    // per-row statistics (DKV = false): L2 = LSE log2 e, ds = delta * scale; delta is computed here
+    float row_l2 = 0.f, row_ds = 0.f;
+    if constexpr (!DKV) {
+      if (x_row < p.S) {
+        const size_t r = static_cast<size_t>(x_plane) * p.S + x_row;
+        const uint4* o4 = reinterpret_cast<const uint4*>(p.O + r * D);
+        const uint4* g4 = reinterpret_cast<const uint4*>(p.dO + r * D);
+        float acc = 0.f;
+#pragma unroll
+        for (int v = 0; v < D / 8; ++v) {
+          const uint4 a = __ldg(o4 + v), g = __ldg(g4 + v);
+          const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&a);
+          const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&g);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float2 af = __bfloat1622float2(a2[e]), gf = __bfloat1622float2(g2[e]);
+            acc = fmaf(af.x, gf.x, acc);
+            acc = fmaf(af.y, gf.y, acc);
+          }
+        }
+        p.delta[r] = acc;
+        row_ds = acc * p.scale;
+        row_l2 = p.LSE[r] * kLog2e;
+      }
+    }
+
+    for (int it = 0; it < n_it; ++it) {
+      const int b = it & 1;
+      const int y_row0 = y_tile_of(it) * kBwdBY;
+      float* st = stats + b * 2 * kBwdBY;
+      if constexpr (DKV) {
+        // stage the 64 per-column statistics of this Q tile: threads 0-63 LSE, 64-127 delta
+        const int col = tid & 63;
+        const int q = y_row0 + col;
+        const size_t r = static_cast<size_t>(y_plane_of(it)) * p.S + min(q, p.S - 1);
+        st[tid] = (tid < 64) ? p.LSE[r] * kLog2e : p.delta[r] * p.scale;
+        asm volatile("bar.sync 2, 128;" ::: "memory");
+      }
+      const bool got = mbar_wait(t_full(b), (it >> 1) & 1, ctx, kRoleSoftmax, b, it);
+      if (DKV) {
+        // the compute warps meet at a named barrier every step, so they must agree on going on
+        uint32_t all;
+        asm volatile(
+            "{\n\t.reg .pred a, q;\n\t"
+            "setp.ne.u32 q, %1, 0;\n\t"
+            "bar.red.and.pred a, 3, 128, q;\n\t"
+            "selp.u32 %0, 1, 0, a;\n\t}"
+            : "=r"(all)
+            : "r"(got ? 1u : 0u)
+            : "memory");
+        if (all == 0) { ok = false; break; }
+      } else if (!__all_sync(0xffffffffu, got)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+
+      uint32_t t0[64], t1[64];
+      tmem_ld32(lane_base + b * 64, t0);
+      tmem_ld32(lane_base + b * 64 + 32, t0 + 32);
+      tmem_ld32(lane_base + 128 + b * 64, t1);
+      tmem_ld32(lane_base + 128 + b * 64 + 32, t1 + 32);
+      tmem_wait_ld();
+
+      // masks are only needed on tiles that touch the diagonal or the end of the sequence
+      const bool ragged = (y_row0 + kBwdBY > p.S) || (x_row0 + kBwdBX > p.S);
+      const bool diagonal = CAUSAL && (DKV ? (y_row0 < x_row0 + kBwdBX) : (y_row0 + kBwdBY > x_row0));
+      const bool masked = ragged || diagonal;
+      uint32_t pk[32], dk[32];
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        float pv[2], dv[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const int col = 2 * i + h;
+          const float l2 = DKV ? st[col] : row_l2;
+          const float dsc = DKV ? st[kBwdBY + col] : row_ds;
+          float pe = ex2_approx(fmaf(__uint_as_float(t0[col]), c, -l2));
+          if (masked) {
+            const int y = y_row0 + col;                 // index along the streamed tile
+            const int qi = DKV ? y : x_row;             // query index
+            const int ki = DKV ? x_row : y;             // key index
+            if (qi >= p.S || ki >= p.S || (CAUSAL && ki > qi)) pe = 0.f;
+          }
+          pv[h] = pe;
+          dv[h] = pe * fmaf(__uint_as_float(t1[col]), p.scale, -dsc);
+        }
+        pk[i] = pack_bf16(pv[0], pv[1]);
+        dk[i] = pack_bf16(dv[0], dv[1]);
+      }
+      if constexpr (DKV) tmem_st32(lane_base + b * 64, pk);
+      tmem_st32(lane_base + 128 + b * 64, dk);
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(pds_full(b));
+    }
+
+    if (ok && n_it > 0) {
+      const bool got = mbar_wait(acc_done, 0, ctx, kRoleEpilogue, 0, n_it);
+      if (__all_sync(0xffffffffu, got)) {
+        tc_fence_after();
+        const bool live = x_row < p.S;
+        const size_t r = static_cast<size_t>(x_plane) * p.S + (live ? x_row : 0);
+#pragma unroll 1
+        for (int a = 0; a < (DKV ? 2 : 1); ++a) {
+          float* dst = (a == 0 ? p.out0 : p.out1) + r * D;
+#pragma unroll 1
+          for (int cidx = 0; cidx < D / 32; ++cidx) {
+            uint32_t o[32];
+            tmem_ld32(lane_base + kAccCol + a * D + cidx * 32, o);
+            tmem_wait_ld();
+            if (live) {
+#pragma unroll
+              for (int v = 0; v < 8; ++v)
+                reinterpret_cast<uint4*>(dst + cidx * 32)[v] = make_uint4(o[4 * v], o[4 * v + 1], o[4 * v + 2], o[4 * v + 3]);
+            }
+          }
+        }
+      }
+    } else if (ok && n_it == 0) {
+      // nothing attends here (only possible past the end of the sequence): gradients are zero
+      if (x_row < p.S) {
+        const size_t r = static_cast<size_t>(x_plane) * p.S + x_row;
+        for (int a = 0; a < (DKV ? 2 : 1); ++a) {
+          float* dst = (a == 0 ? p.out0 : p.out1) + r * D;
+          for (int v = 0; v < D / 4; ++v) reinterpret_cast<uint4*>(dst)[v] = make_uint4(0, 0, 0, 0);
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+}  // namespace wir

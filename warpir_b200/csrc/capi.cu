@@ -40,6 +40,13 @@ int warpir_attn_fwd_bf16(const void* Q, const void* K, const void* V, void* O, f
   return attn_impl(Q, K, V, O, LSE, B, Hq, Hkv, S, D, softmax_scale, causal, device, cuda_stream);
 }
 
+int warpir_attn_bwd_bf16(const void* Q, const void* K, const void* V, const void* O, const void* dO, const float* LSE,
+                         float* dQ, float* dK, float* dV, float* delta_ws, int64_t B, int64_t Hq, int64_t Hkv,
+                         int64_t S, int64_t D, float softmax_scale, int causal, int device, void* cuda_stream) {
+  return attn_bwd_impl(Q, K, V, O, dO, LSE, dQ, dK, dV, delta_ws, B, Hq, Hkv, S, D, softmax_scale, causal, device,
+                       cuda_stream);
+}
+
 int warpir_read_status(int device, void* cuda_stream, int* code, int* detail) {
   return read_status_impl(device, cuda_stream, code, detail);
 }

@@ -5,6 +5,7 @@
 #pragma once
 
 #include "host_common.cuh"
+#include "attn_bwd_sm100.cuh"
 #include "attn_fwd_sm100.cuh"
 #include "gemm_sm100.cuh"
 
@@ -318,6 +319,84 @@ inline int attn_impl(const void* Q, const void* K, const void* V, void* O, float
   p.stagger_clocks = env_attn_stagger();
   if (D == 128) return causal ? launch_attn_cfg<128, true>(tq, tk, tv, p, stream) : launch_attn_cfg<128, false>(tq, tk, tv, p, stream);
   return causal ? launch_attn_cfg<64, true>(tq, tk, tv, p, stream) : launch_attn_cfg<64, false>(tq, tk, tv, p, stream);
+}
+
+// ------------------------------------------------------------------------ attention backward
+template <int D, bool CAUSAL, bool DKV>
+int launch_attn_bwd_cfg(const CUtensorMap& x0, const CUtensorMap& x1, const CUtensorMap& y0, const CUtensorMap& y1,
+                        const wir::AttnBwdParams& p, cudaStream_t stream) {
+  auto kernel = wir::attn_bwd_sm100<D, CAUSAL, DKV>;
+  constexpr int smem = wir::AttnBwdSmem<D>::kDynamicBytes;
+  static_assert(smem <= 232448, "shared memory limit per CTA");
+  static_assert(smem > 116 * 1024, "one CTA per SM is what keeps the tensor-memory allocation from blocking");
+  if (int rc = opt_in_smem(reinterpret_cast<const void*>(kernel), smem)) return rc;
+  dim3 grid((p.S + wir::kBwdBX - 1) / wir::kBwdBX, DKV ? p.Hkv : p.H, p.B);
+  kernel<<<grid, wir::kBwdThreads, smem, stream>>>(x0, x1, y0, y1, p);
+  WIR_CUDA(cudaGetLastError());
+  return WARPIR_OK;
+}
+
+inline int attn_bwd_impl(const void* Q, const void* K, const void* V, const void* O, const void* dO, const float* LSE,
+                         float* dQ, float* dK, float* dV, float* delta, int64_t B, int64_t Hq, int64_t Hkv, int64_t S,
+                         int64_t D, float softmax_scale, int causal, int device, void* cuda_stream) {
+  g_last_error[0] = 0;
+  if (B < 0 || Hq < 0 || Hkv < 0 || S < 0) return fail(WARPIR_EINVAL, "negative size");
+  if (D != 64 && D != 128) return fail(WARPIR_ESHAPE, "D = %lld: head dimension must be 64 or 128", (long long)D);
+  if (B == 0 || Hq == 0 || S == 0) return WARPIR_OK;
+  if (Hkv <= 0 || Hq % Hkv != 0) return fail(WARPIR_ESHAPE, "Hq = %lld must be a positive multiple of Hkv = %lld", (long long)Hq, (long long)Hkv);
+  if (!(softmax_scale > 0.f) || !std::isfinite(softmax_scale)) return fail(WARPIR_EINVAL, "softmax_scale must be positive and finite");
+  if (B > 65535 || Hq > 65535) return fail(WARPIR_ESHAPE, "B and Hq must be at most 65535");
+  if (S > (1 << 24) || B * Hq * S > INT32_MAX) return fail(WARPIR_ESHAPE, "sequence too long");
+  DeviceState* dev = nullptr;
+  if (int rc = get_device_state(device, &dev)) return rc;
+  const void* ptrs[10] = {Q, K, V, O, dO, LSE, dQ, dK, dV, delta};
+  const char* names[10] = {"Q", "K", "V", "O", "dO", "LSE", "dQ", "dK", "dV", "delta"};
+  for (int i = 0; i < 10; ++i)
+    if (int rc = check_device_ptr(ptrs[i], names[i], device)) return rc;
+  cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+  DeviceGuard guard(device);
+  if (guard.err != cudaSuccess) return fail(WARPIR_ECUDA, "cudaSetDevice(%d): %s", device, cudaGetErrorString(guard.err));
+
+  // every bf16 operand is read both as resident 128-row tiles and as streamed 64-row tiles
+  auto maps = [&](const void* base, int64_t planes, CUtensorMap* big, CUtensorMap* small) -> int {
+    const uint64_t dims[3] = {static_cast<uint64_t>(D), static_cast<uint64_t>(S), static_cast<uint64_t>(planes)};
+    const uint64_t strides[2] = {static_cast<uint64_t>(D) * 2, static_cast<uint64_t>(S) * D * 2};
+    const uint32_t box_x[3] = {64, wir::kBwdBX, 1}, box_y[3] = {64, wir::kBwdBY, 1};
+    if (int rc = make_tmap(big, base, 3, dims, strides, box_x)) return rc;
+    return make_tmap(small, base, 3, dims, strides, box_y);
+  };
+  CUtensorMap q_x, q_y, k_x, k_y, v_x, v_y, g_x, g_y;
+  if (int rc = maps(Q, B * Hq, &q_x, &q_y)) return rc;
+  if (int rc = maps(dO, B * Hq, &g_x, &g_y)) return rc;
+  if (int rc = maps(K, B * Hkv, &k_x, &k_y)) return rc;
+  if (int rc = maps(V, B * Hkv, &v_x, &v_y)) return rc;
+
+  wir::AttnBwdParams p;
+  p.B = static_cast<int>(B);
+  p.H = static_cast<int>(Hq);
+  p.Hkv = static_cast<int>(Hkv);
+  p.S = static_cast<int>(S);
+  p.scale = softmax_scale;
+  p.scale_log2 = softmax_scale * 1.4426950408889634f;
+  p.O = static_cast<const __nv_bfloat16*>(O);
+  p.dO = static_cast<const __nv_bfloat16*>(dO);
+  p.LSE = LSE;
+  p.delta = delta;
+  p.status = dev->status;
+  const bool c = causal != 0;
+  int rc;
+  // 1: dQ (and delta) per Q tile, streaming K and V
+  p.out0 = dQ;
+  p.out1 = nullptr;
+  if (D == 128) rc = c ? launch_attn_bwd_cfg<128, true, false>(q_x, g_x, k_y, v_y, p, stream) : launch_attn_bwd_cfg<128, false, false>(q_x, g_x, k_y, v_y, p, stream);
+  else rc = c ? launch_attn_bwd_cfg<64, true, false>(q_x, g_x, k_y, v_y, p, stream) : launch_attn_bwd_cfg<64, false, false>(q_x, g_x, k_y, v_y, p, stream);
+  if (rc) return rc;
+  // 2: dV and dK per K/V tile, streaming Q and dO of the head group
+  p.out0 = dV;
+  p.out1 = dK;
+  if (D == 128) rc = c ? launch_attn_bwd_cfg<128, true, true>(k_x, v_x, q_y, g_y, p, stream) : launch_attn_bwd_cfg<128, false, true>(k_x, v_x, q_y, g_y, p, stream);
+  else rc = c ? launch_attn_bwd_cfg<64, true, true>(k_x, v_x, q_y, g_y, p, stream) : launch_attn_bwd_cfg<64, false, true>(k_x, v_x, q_y, g_y, p, stream);
+  return rc;
 }
 
 // Self-test of the bounded-wait machinery: one CTA waits, with a limit of `limit_ns`, on an

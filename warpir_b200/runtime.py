@@ -25,7 +25,7 @@ ABI_VERSION = 1
 
 EXPORTS = (
     "warpir_abi_version", "warpir_strerror", "warpir_last_error", "warpir_gemm_bf16",
-    "warpir_gemm_bf16_ex", "warpir_attn_fwd_bf16", "warpir_read_status",
+    "warpir_gemm_bf16_ex", "warpir_attn_fwd_bf16", "warpir_attn_bwd_bf16", "warpir_read_status",
     "warpir_gemm_bf16_splitk_noalloc", "warpir_selftest_bounded_wait",
 )
 
@@ -69,6 +69,8 @@ def load_library() -> ctypes.CDLL:
         lib.warpir_gemm_bf16_splitk_noalloc.argtypes = [vp, vp, vp, i64, i64, i64, ci, ci, ci, ci, vp]
         lib.warpir_attn_fwd_bf16.restype = ci
         lib.warpir_attn_fwd_bf16.argtypes = [vp, vp, vp, vp, vp, i64, i64, i64, i64, i64, cf, ci, ci, vp]
+        lib.warpir_attn_bwd_bf16.restype = ci
+        lib.warpir_attn_bwd_bf16.argtypes = [vp] * 10 + [i64] * 5 + [cf, ci, ci, vp]
         lib.warpir_selftest_bounded_wait.restype = ci
         lib.warpir_selftest_bounded_wait.argtypes = [ci, vp, i64]
         lib.warpir_read_status.restype = ci
@@ -163,6 +165,46 @@ def launch_attention(Q, K, V, O, LSE=None, softmax_scale: Optional[float] = None
     if softmax_scale is None:
         softmax_scale = 1.0 / math.sqrt(D)
     _check(lib.warpir_attn_fwd_bf16(Q.data_ptr(), K.data_ptr(), V.data_ptr(), O.data_ptr(), lse_ptr,
+                                    Bz, Hq, Hkv, S, D, float(softmax_scale), int(bool(causal)),
+                                    Q.device.index, _stream_of(Q)))
+
+
+def launch_attention_backward(Q, K, V, O, dO, LSE, dQ, dK, dV, delta=None, softmax_scale: Optional[float] = None,
+                              causal: bool = False) -> None:
+    """Gradients of ``launch_attention``'s output: fills ``dQ`` (shape of Q), ``dK`` and
+    ``dV`` (shape of K), all fp32, from ``dO`` and the forward's ``O`` and ``LSE``.
+
+    Mirrors the reference's ``attention_backward(q, k, v, o, l_vec, og, causal)``
+    (kernel_examples/attention/mha_h100.cu:799-1010) with caller-allocated outputs.
+    ``delta`` is an fp32 ``[B, Hq, S]`` workspace; one is allocated with torch when omitted.
+    Asynchronous on torch's current stream."""
+    import torch
+    lib = load_library()
+    if Q.dim() == 2:
+        Bz, Hq, Hkv = 1, 1, 1
+        S, D = Q.shape
+    else:
+        Bz, Hq, S, D = Q.shape
+        Hkv = K.shape[1]
+    for t, n in ((Q, "Q"), (K, "K"), (V, "V"), (O, "O"), (dO, "dO")):
+        _require(t, n, torch.bfloat16, Q.dim())
+    for t, n in ((LSE, "LSE"), (dQ, "dQ"), (dK, "dK"), (dV, "dV")):
+        _require(t, n, torch.float32)
+    if K.shape != V.shape or O.shape != Q.shape or dO.shape != Q.shape or K.shape[-2:] != Q.shape[-2:]:
+        raise ValueError("shape mismatch between Q, K, V, O and dO")
+    if dQ.shape != Q.shape or dK.shape != K.shape or dV.shape != V.shape:
+        raise ValueError("dQ, dK, dV must have the shapes of Q, K, V")
+    if LSE.numel() != Bz * Hq * S:
+        raise ValueError("LSE must hold B*H*S elements")
+    if delta is None:
+        delta = torch.empty(Bz * Hq * S, dtype=torch.float32, device=Q.device)
+    _require(delta, "delta", torch.float32)
+    if delta.numel() < Bz * Hq * S:
+        raise ValueError("delta must hold B*H*S elements")
+    if softmax_scale is None:
+        softmax_scale = 1.0 / math.sqrt(D)
+    _check(lib.warpir_attn_bwd_bf16(Q.data_ptr(), K.data_ptr(), V.data_ptr(), O.data_ptr(), dO.data_ptr(),
+                                    LSE.data_ptr(), dQ.data_ptr(), dK.data_ptr(), dV.data_ptr(), delta.data_ptr(),
                                     Bz, Hq, Hkv, S, D, float(softmax_scale), int(bool(causal)),
                                     Q.device.index, _stream_of(Q)))
 
