@@ -76,6 +76,9 @@ def workload_table():
         "attn_noncausal_b16_h16_s4096_d128": dict(kind="attn", B=16, H=16, S=4096, D=128, causal=False),
         "attn_causal_b4_h32_s8192_d128": dict(kind="attn", B=4, H=32, S=8192, D=128, causal=True),
         "attn_causal_b4_h32_s8192_d64": dict(kind="attn", B=4, H=32, S=8192, D=64, causal=True),
+        # backward of the two D = 128 configurations (FLOPs counted as five matrix products, 2.5 x forward)
+        "attn_bwd_noncausal_b16_h16_s4096_d128": dict(kind="attn_bwd", B=16, H=16, S=4096, D=128, causal=False),
+        "attn_bwd_causal_b4_h32_s8192_d128": dict(kind="attn_bwd", B=4, H=32, S=8192, D=128, causal=True),
     }
 
 
@@ -83,13 +86,18 @@ def flops_of(w) -> float:
     if w["kind"] == "gemm":
         return 2.0 * w["M"] * w["N"] * w["K"]
     f = 4.0 * w["B"] * w["H"] * w["S"] * w["S"] * w["D"]
+    if w["kind"] == "attn_bwd":
+        f *= 2.5
     return f / 2 if w["causal"] else f
 
 
 def bytes_of(w) -> float:
     if w["kind"] == "gemm":
         return 2.0 * (w["M"] * w["K"] + w["N"] * w["K"] + w["M"] * w["N"])
-    return 2.0 * 4 * w["B"] * w["H"] * w["S"] * w["D"] + 4.0 * w["B"] * w["H"] * w["S"]
+    elems = w["B"] * w["H"] * w["S"] * w["D"]
+    if w["kind"] == "attn_bwd":   # reads Q, K, V, O, dO (bf16) and LSE; writes dQ, dK, dV (fp32) and delta
+        return 2.0 * 5 * elems + 4.0 * 3 * elems + 4.0 * 2 * w["B"] * w["H"] * w["S"]
+    return 2.0 * 4 * elems + 4.0 * w["B"] * w["H"] * w["S"]
 
 
 # --------------------------------------------------------------------------- clocks
@@ -160,6 +168,13 @@ def make_inputs(w, device, seed):
     Q, K, V = (torch.randn(shape, generator=g, device=device).bfloat16() for _ in range(3))
     O = torch.empty_like(Q)
     L = torch.empty(shape[:-1], dtype=torch.float32, device=device)
+    if w["kind"] == "attn_bwd":
+        from warpir_b200 import runtime
+        runtime.launch_attention(Q, K, V, O, L, None, w["causal"])      # the forward's O and LSE are inputs
+        dO = torch.randn(shape, generator=g, device=device).bfloat16()
+        grads = tuple(torch.empty(shape, dtype=torch.float32, device=device) for _ in range(3))
+        delta = torch.empty(shape[:-1], dtype=torch.float32, device=device)
+        return (Q, K, V, O, dO, L), (*grads, delta)
     return (Q, K, V), (O, L)
 
 
@@ -168,6 +183,10 @@ def make_step(w, ins, outs):
     if w["kind"] == "gemm":
         A, B = ins
         return lambda: runtime.launch_gemm(A, B, outs[0], 1)
+    if w["kind"] == "attn_bwd":
+        Q, K, V, O, dO, L = ins
+        dQ, dK, dV, delta = outs
+        return lambda: runtime.launch_attention_backward(Q, K, V, O, dO, L, dQ, dK, dV, delta, None, w["causal"])
     Q, K, V = ins
     return lambda: runtime.launch_attention(Q, K, V, outs[0], outs[1], None, w["causal"])
 
@@ -412,7 +431,7 @@ def run_gpu_arm(args, w, name):
                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps,
                "ms_per_step": e2e_ms / e2e_steps}
 
-    tensor_bound = w["kind"] == "attn" or min(w["M"], w["N"]) > 1024
+    tensor_bound = w["kind"] != "gemm" or min(w["M"], w["N"]) > 1024
     long_region = ms >= 1000.0
     if tensor_bound:
         peak = peaks["bf16_tflops_sustained"] if long_region else peaks["bf16_tflops"]
@@ -427,7 +446,7 @@ def run_gpu_arm(args, w, name):
     roof["traffic"] = NCU_DRAM_BYTES_PER_LAUNCH.get(name)
     roof["traffic_unit"] = "bytes per launch (ncu dram read + write)"
     roof["algorithmic_bytes_per_launch"] = bytes_of(w)
-    roof["kernel"] = "gemm_bf16_sm100" if w["kind"] == "gemm" else "attn_fwd_sm100"
+    roof["kernel"] = {"gemm": "gemm_bf16_sm100", "attn": "attn_fwd_sm100", "attn_bwd": "attn_bwd_sm100"}[w["kind"]]
     roof["algorithmic_per_launch"] = flops_of(w) if tensor_bound else bytes_of(w)
 
     others = []

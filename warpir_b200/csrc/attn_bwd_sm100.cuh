@@ -21,7 +21,7 @@
 //
 //   stage 1 (tcgen05.mma, SS):  T0 = X0 Y0^T,  T1 = X1 Y1^T          (128 x 64 each)
 //   compute warps:              P = 2^(c T0 - L2),  dS = P (T1 - delta) scale, both
-//                               packed to bf16 over the low columns of T0 / T1
+//                               packed to bf16 over columns 16..47 of T0 / T1
 //   stage 2 (tcgen05.mma, TS):  DKV:  acc0 += P  Y1   (dV),  acc1 += dS Y0   (dK)
 //                               else: acc0 += dS Y0   (dQ)
 //
@@ -31,7 +31,10 @@
 // Tensor memory: T0[2] at columns 0 / 64, T1[2] at 128 / 192 (double-buffered so stage 1
 // of step it+1 runs while the compute warps work on step it), acc0 at 256, acc1 at
 // 256 + D.  Warp 0 is the TMA producer, warp 1 issues every MMA (whole warp, one elected
-// lane), warps 2-5 are the compute warps (one tensor-memory lane = one row per thread).
+// lane), warps 2-9 are two compute warpgroups: thread = one tensor-memory lane (row), and the
+// two groups split the 64 columns of T0 / T1 between them (there is no row reduction in the
+// backward, so the split needs no exchange; two warps per scheduler hide each other's
+// tensor-memory and exponential latencies).
 // MMAs execute in issue order, which makes the aliasing safe: stage 1 of step it+2
 // overwrites T0/T1[b] only after stage 2 of step it, which reads P/dS from them.
 #pragma once
@@ -42,7 +45,8 @@ namespace wir {
 
 constexpr int kBwdBX = 128;        // rows of the resident tiles = MMA M
 constexpr int kBwdBY = 64;         // rows of the streamed tiles = MMA N of stage 1, K of stage 2
-constexpr int kBwdThreads = 192;
+constexpr int kBwdThreads = 320;        // producer warp, MMA warp, two compute warpgroups
+constexpr int kBwdComputeThreads = 256;
 
 struct AttnBwdParams {
   int B, H, Hkv, S;
@@ -55,6 +59,7 @@ struct AttnBwdParams {
   float* out0;             // DKV = false: dQ [B, H, S, D];  DKV = true: dV [B, Hkv, S, D]
   float* out1;             // DKV = true: dK [B, Hkv, S, D]
   int* status;
+  unsigned long long* trace;   // event trace buffer of debug builds (-DWIR_TRACE), else unused
 };
 
 template <int D>
@@ -134,7 +139,7 @@ attn_bwd_sm100(const __grid_constant__ CUtensorMap tmap_x0, const __grid_constan
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(t_full(b), 1);
-      mbar_init(pds_full(b), 128);
+      mbar_init(pds_full(b), kBwdComputeThreads);
     }
     mbar_init(acc_done, 1);
     mbar_init(drain_bar, 1);
@@ -191,6 +196,7 @@ attn_bwd_sm100(const __grid_constant__ CUtensorMap tmap_x0, const __grid_constan
     const uint32_t x1_lo = smem_desc_lo(smem_base + L::kXTileBytes, 16);
     auto y_addr = [&](int it) { return smem_base + L::kYOffset + (it % STAGES) * 2 * L::kYTileBytes; };
     bool ok = true;
+    WIR_TRACE_DECL;
     auto stage1 = [&](int it) -> bool {
       if (!mbar_wait_warp(y_full(it % STAGES), (it / STAGES) & 1, ctx, kRoleMma, 10, it)) return false;
       tc_fence_after();
@@ -217,14 +223,16 @@ attn_bwd_sm100(const __grid_constant__ CUtensorMap tmap_x0, const __grid_constan
     for (int it = 0; ok && it < 2 && it < n_it; ++it) ok = stage1(it);
     for (int it = 0; ok && it < n_it; ++it) {
       const int b = it & 1;
+      if (lane == 0) WIR_TRACE_EVENT(p.trace, 0, 0, it);
       if (!mbar_wait_warp(pds_full(b), (it >> 1) & 1, ctx, kRoleMma, 20, it)) { ok = false; break; }
       tc_fence_after();
+      if (lane == 0) WIR_TRACE_EVENT(p.trace, 0, 1, it);
       // as B operands the streamed tiles are read with the 64 tile rows as K: chunks of 64
       // columns kYChunkBytes apart, 16 rows (2048 bytes) per k-step
       const uint32_t y0_mn = smem_desc_lo(y_addr(it), L::kYChunkBytes);
       const uint32_t y1_mn = smem_desc_lo(y_addr(it) + L::kYTileBytes, L::kYChunkBytes);
-      const uint32_t p_tmem = tmem_base + b * 64;          // bf16 P over T0[b]
-      const uint32_t ds_tmem = tmem_base + 128 + b * 64;   // bf16 dS over T1[b]
+      const uint32_t p_tmem = tmem_base + b * 64 + 16;          // bf16 P inside T0[b]
+      const uint32_t ds_tmem = tmem_base + 128 + b * 64 + 16;   // bf16 dS inside T1[b]
 #pragma unroll
       for (int k = 0; k < kBwdBY / 16; ++k) {
         const uint32_t acc = (it > 0 || k > 0) ? 1u : 0u;
@@ -237,7 +245,9 @@ attn_bwd_sm100(const __grid_constant__ CUtensorMap tmap_x0, const __grid_constan
       }
       mma_commit_elect(y_empty(it % STAGES));
       if (it + 1 == n_it) mma_commit_elect(acc_done);
+      if (lane == 0) WIR_TRACE_EVENT(p.trace, 0, 2, it);
       if (it + 2 < n_it) ok = stage1(it + 2);
+      if (lane == 0) WIR_TRACE_EVENT(p.trace, 0, 3, it);
     }
     if (!ok || *abort_flag) {
       mma_commit_elect(drain_bar);
@@ -247,12 +257,15 @@ attn_bwd_sm100(const __grid_constant__ CUtensorMap tmap_x0, const __grid_constan
   } else {
     // ------------------------------------------------------------------ compute warps
     const int quarter = warp & 3;                       // tensor-memory lanes 32*quarter .. +31
+    const int half = (warp - 2) >> 2;                   // which 32 of the 64 columns of T0 / T1
     const int tid = quarter * 32 + lane;                // row of the resident tiles owned by this thread
     const int x_row = x_row0 + tid;
     const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
     const float c = p.scale_log2;
     constexpr float kLog2e = 1.4426950408889634f;
     bool ok = true;
+    WIR_TRACE_DECL;
+    const bool traced = (quarter == 0 && lane == 0);
 
     // per-row statistics (DKV = false): L2 = LSE log2 e, ds = delta * scale; delta is computed here
     float row_l2 = 0.f, row_ds = 0.f;
@@ -274,7 +287,7 @@ attn_bwd_sm100(const __grid_constant__ CUtensorMap tmap_x0, const __grid_constan
             acc = fmaf(af.y, gf.y, acc);
           }
         }
-        p.delta[r] = acc;
+        if (half == 0) p.delta[r] = acc;
         row_ds = acc * p.scale;
         row_l2 = p.LSE[r] * kLog2e;
       }
@@ -285,13 +298,16 @@ attn_bwd_sm100(const __grid_constant__ CUtensorMap tmap_x0, const __grid_constan
       const int y_row0 = y_tile_of(it) * kBwdBY;
       float* st = stats + b * 2 * kBwdBY;
       if constexpr (DKV) {
-        // stage the 64 per-column statistics of this Q tile: threads 0-63 LSE, 64-127 delta
-        const int col = tid & 63;
-        const int q = y_row0 + col;
-        const size_t r = static_cast<size_t>(y_plane_of(it)) * p.S + min(q, p.S - 1);
-        st[tid] = (tid < 64) ? p.LSE[r] * kLog2e : p.delta[r] * p.scale;
-        asm volatile("bar.sync 2, 128;" ::: "memory");
+        // stage the 64 per-column statistics of this Q tile: one warpgroup's threads 0-63 LSE, 64-127 delta
+        if (half == 0) {
+          const int col = tid & 63;
+          const int q = y_row0 + col;
+          const size_t r = static_cast<size_t>(y_plane_of(it)) * p.S + min(q, p.S - 1);
+          st[tid] = (tid < 64) ? p.LSE[r] * kLog2e : p.delta[r] * p.scale;
+        }
+        asm volatile("bar.sync 2, 256;" ::: "memory");
       }
+      if (traced) WIR_TRACE_EVENT(p.trace, 1 + half, 10, it);
       const bool got = mbar_wait(t_full(b), (it >> 1) & 1, ctx, kRoleSoftmax, b, it);
       if (DKV) {
         // the compute warps meet at a named barrier every step, so they must agree on going on
@@ -299,7 +315,7 @@ attn_bwd_sm100(const __grid_constant__ CUtensorMap tmap_x0, const __grid_constan
         asm volatile(
             "{\n\t.reg .pred a, q;\n\t"
             "setp.ne.u32 q, %1, 0;\n\t"
-            "bar.red.and.pred a, 3, 128, q;\n\t"
+            "bar.red.and.pred a, 3, 256, q;\n\t"
             "selp.u32 %0, 1, 0, a;\n\t}"
             : "=r"(all)
             : "r"(got ? 1u : 0u)
@@ -311,27 +327,27 @@ attn_bwd_sm100(const __grid_constant__ CUtensorMap tmap_x0, const __grid_constan
       }
       tc_fence_after();
 
-      uint32_t t0[64], t1[64];
-      tmem_ld32(lane_base + b * 64, t0);
-      tmem_ld32(lane_base + b * 64 + 32, t0 + 32);
-      tmem_ld32(lane_base + 128 + b * 64, t1);
-      tmem_ld32(lane_base + 128 + b * 64 + 32, t1 + 32);
+      if (traced) WIR_TRACE_EVENT(p.trace, 1 + half, 11, it);
+      uint32_t t0[32], t1[32];
+      tmem_ld32(lane_base + b * 64 + half * 32, t0);
+      tmem_ld32(lane_base + 128 + b * 64 + half * 32, t1);
       tmem_wait_ld();
+      if (traced) WIR_TRACE_EVENT(p.trace, 1 + half, 12, it);
 
       // masks are only needed on tiles that touch the diagonal or the end of the sequence
       const bool ragged = (y_row0 + kBwdBY > p.S) || (x_row0 + kBwdBX > p.S);
       const bool diagonal = CAUSAL && (DKV ? (y_row0 < x_row0 + kBwdBX) : (y_row0 + kBwdBY > x_row0));
       const bool masked = ragged || diagonal;
-      uint32_t pk[32], dk[32];
+      uint32_t pk[16], dk[16];
 #pragma unroll
-      for (int i = 0; i < 32; ++i) {
+      for (int i = 0; i < 16; ++i) {
         float pv[2], dv[2];
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
-          const int col = 2 * i + h;
+          const int col = half * 32 + 2 * i + h;        // column of T0 / T1
           const float l2 = DKV ? st[col] : row_l2;
           const float dsc = DKV ? st[kBwdBY + col] : row_ds;
-          float pe = ex2_approx(fmaf(__uint_as_float(t0[col]), c, -l2));
+          float pe = ex2_approx(fmaf(__uint_as_float(t0[2 * i + h]), c, -l2));
           if (masked) {
             const int y = y_row0 + col;                 // index along the streamed tile
             const int qi = DKV ? y : x_row;             // query index
@@ -339,16 +355,22 @@ attn_bwd_sm100(const __grid_constant__ CUtensorMap tmap_x0, const __grid_constan
             if (qi >= p.S || ki >= p.S || (CAUSAL && ki > qi)) pe = 0.f;
           }
           pv[h] = pe;
-          dv[h] = pe * fmaf(__uint_as_float(t1[col]), p.scale, -dsc);
+          dv[h] = pe * fmaf(__uint_as_float(t1[2 * i + h]), p.scale, -dsc);
         }
         pk[i] = pack_bf16(pv[0], pv[1]);
         dk[i] = pack_bf16(dv[0], dv[1]);
       }
-      if constexpr (DKV) tmem_st32(lane_base + b * 64, pk);
-      tmem_st32(lane_base + 128 + b * 64, dk);
+      // Packed bf16: this group's 32 values fill 16 columns.  The 32 packed columns sit at
+      // columns 16..47 of the buffer, so each group overwrites only columns it has read itself
+      // (group 0 read 0..31 and writes 16..31, group 1 read 32..63 and writes 32..47) and the
+      // groups need no barrier between their loads and stores.
+      if constexpr (DKV) tmem_st16(lane_base + b * 64 + 16 + half * 16, pk);
+      tmem_st16(lane_base + 128 + b * 64 + 16 + half * 16, dk);
+      if (traced) WIR_TRACE_EVENT(p.trace, 1 + half, 13, it);
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(pds_full(b));
+      if (traced) WIR_TRACE_EVENT(p.trace, 1 + half, 14, it);
     }
 
     if (ok && n_it > 0) {
@@ -361,7 +383,7 @@ attn_bwd_sm100(const __grid_constant__ CUtensorMap tmap_x0, const __grid_constan
         for (int a = 0; a < (DKV ? 2 : 1); ++a) {
           float* dst = (a == 0 ? p.out0 : p.out1) + r * D;
 #pragma unroll 1
-          for (int cidx = 0; cidx < D / 32; ++cidx) {
+          for (int cidx = half * (D / 64); cidx < (half + 1) * (D / 64); ++cidx) {   // each group stores half the columns
             uint32_t o[32];
             tmem_ld32(lane_base + kAccCol + a * D + cidx * 32, o);
             tmem_wait_ld();
@@ -375,7 +397,7 @@ attn_bwd_sm100(const __grid_constant__ CUtensorMap tmap_x0, const __grid_constan
       }
     } else if (ok && n_it == 0) {
       // nothing attends here (only possible past the end of the sequence): gradients are zero
-      if (x_row < p.S) {
+      if (x_row < p.S && half == 0) {
         const size_t r = static_cast<size_t>(x_plane) * p.S + x_row;
         for (int a = 0; a < (DKV ? 2 : 1); ++a) {
           float* dst = (a == 0 ? p.out0 : p.out1) + r * D;

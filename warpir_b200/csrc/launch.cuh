@@ -383,6 +383,7 @@ inline int attn_bwd_impl(const void* Q, const void* K, const void* V, const void
   p.LSE = LSE;
   p.delta = delta;
   p.status = dev->status;
+  p.trace = g_trace;
   const bool c = causal != 0;
   int rc;
   // 1: dQ (and delta) per Q tile, streaming K and V
@@ -391,6 +392,9 @@ inline int attn_bwd_impl(const void* Q, const void* K, const void* V, const void
   if (D == 128) rc = c ? launch_attn_bwd_cfg<128, true, false>(q_x, g_x, k_y, v_y, p, stream) : launch_attn_bwd_cfg<128, false, false>(q_x, g_x, k_y, v_y, p, stream);
   else rc = c ? launch_attn_bwd_cfg<64, true, false>(q_x, g_x, k_y, v_y, p, stream) : launch_attn_bwd_cfg<64, false, false>(q_x, g_x, k_y, v_y, p, stream);
   if (rc) return rc;
+#ifdef WIR_TRACE
+  if (getenv("WARPIR_BWD_DQ_ONLY")) return rc;   // debug builds: keep the first launch's trace
+#endif
   // 2: dV and dK per K/V tile, streaming Q and dO of the head group
   p.out0 = dV;
   p.out1 = dK;
