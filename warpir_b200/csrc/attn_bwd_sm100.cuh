@@ -52,6 +52,7 @@ struct AttnBwdParams {
   int B, H, Hkv, S;
   float scale;             // softmax scale
   float scale_log2;        // scale * log2(e)
+  const __nv_bfloat16* Q;  // [B, H, S, D]   (DKV = false: copied into tensor memory)
   const __nv_bfloat16* O;  // [B, H, S, D]   (DKV = false: for delta)
   const __nv_bfloat16* dO; // [B, H, S, D]
   const float* LSE;        // [B, H, S] natural-log logsumexp of the scaled scores
@@ -62,14 +63,15 @@ struct AttnBwdParams {
   unsigned long long* trace;   // event trace buffer of debug builds (-DWIR_TRACE), else unused
 };
 
-template <int D>
+template <int D, bool DKV>
 struct AttnBwdSmem {
-  static constexpr int kStages = (D == 128) ? 4 : 8;
+  // DKV = false keeps its resident operands (Q, dO) in tensor memory, not in shared memory
+  static constexpr int kStages = DKV ? ((D == 128) ? 4 : 8) : ((D == 128) ? 6 : 12);
   static constexpr int kXChunkBytes = kBwdBX * 128;
   static constexpr int kXTileBytes = (D / 64) * kXChunkBytes;
   static constexpr int kYChunkBytes = kBwdBY * 128;
   static constexpr int kYTileBytes = (D / 64) * kYChunkBytes;
-  static constexpr int kYOffset = 2 * kXTileBytes;
+  static constexpr int kYOffset = DKV ? 2 * kXTileBytes : 0;
   static constexpr int kStatsOffset = kYOffset + kStages * 2 * kYTileBytes;   // [2 buffers][2 vectors][64] floats
   static constexpr int kBarOffset = kStatsOffset + 2 * 2 * kBwdBY * 4;
   // x_full, y_full[S], y_empty[S], t_full[2], pds_full[2], acc_done, drain
@@ -85,10 +87,11 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
 attn_bwd_sm100(const __grid_constant__ CUtensorMap tmap_x0, const __grid_constant__ CUtensorMap tmap_x1,
                const __grid_constant__ CUtensorMap tmap_y0, const __grid_constant__ CUtensorMap tmap_y1,
                const AttnBwdParams p) {
-  using L = AttnBwdSmem<D>;
+  using L = AttnBwdSmem<D, DKV>;
   constexpr int STAGES = L::kStages;
   constexpr uint32_t kTmemCols = 512;
   constexpr uint32_t kAccCol = 256;
+  constexpr uint32_t kXCol = 256 + D;   // DKV = false: Q and dO rows as packed bf16, D/2 columns each
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -132,7 +135,7 @@ attn_bwd_sm100(const __grid_constant__ CUtensorMap tmap_x0, const __grid_constan
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
-    mbar_init(x_full, 1);
+    mbar_init(x_full, DKV ? 1 : kBwdComputeThreads);
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(y_full(s), 1);
       mbar_init(y_empty(s), 1);
@@ -157,11 +160,13 @@ attn_bwd_sm100(const __grid_constant__ CUtensorMap tmap_x0, const __grid_constan
   if (warp == 0) {
     // ------------------------------------------------------------------ producer
     if (lane == 0 && n_it > 0) {
-      mbar_arrive_expect_tx(x_full, 2 * L::kXTileBytes);
+      if constexpr (DKV) {
+        mbar_arrive_expect_tx(x_full, 2 * L::kXTileBytes);
 #pragma unroll
-      for (int c = 0; c < D / 64; ++c) {
-        tma_load_3d(smem_base + c * L::kXChunkBytes, &tmap_x0, x_full, c * 64, x_row0, x_plane);
-        tma_load_3d(smem_base + L::kXTileBytes + c * L::kXChunkBytes, &tmap_x1, x_full, c * 64, x_row0, x_plane);
+        for (int c = 0; c < D / 64; ++c) {
+          tma_load_3d(smem_base + c * L::kXChunkBytes, &tmap_x0, x_full, c * 64, x_row0, x_plane);
+          tma_load_3d(smem_base + L::kXTileBytes + c * L::kXChunkBytes, &tmap_x1, x_full, c * 64, x_row0, x_plane);
+        }
       }
       bool ok = true;
       int it = 0;
@@ -179,7 +184,7 @@ attn_bwd_sm100(const __grid_constant__ CUtensorMap tmap_x0, const __grid_constan
         }
       }
       if (!ok || *abort_flag) {
-        mbar_wait_quiet(x_full, 0);
+        if (DKV) mbar_wait_quiet(x_full, 0);
         const int n = it < STAGES ? it : STAGES;
         for (int back = 1; back <= n; ++back) {
           const int i = it - back;
@@ -203,23 +208,29 @@ attn_bwd_sm100(const __grid_constant__ CUtensorMap tmap_x0, const __grid_constan
       const int b = it & 1;
       const uint32_t y0_lo = smem_desc_lo(y_addr(it), 16);
       const uint32_t y1_lo = smem_desc_lo(y_addr(it) + L::kYTileBytes, 16);
+      // groups of four k-steps (one 64-column chunk of the head dimension: 32 bytes per step)
 #pragma unroll
-      for (int k = 0; k < D / 16; ++k) {
-        const uint32_t x_off = ((k / 4) * L::kXChunkBytes + (k % 4) * 32) >> 4;
-        const uint32_t y_off = ((k / 4) * L::kYChunkBytes + (k % 4) * 32) >> 4;
-        mma_ss_elect(tmem_base + b * 64, x0_lo + x_off, desc_hi, y0_lo + y_off, desc_hi, idesc_t, k > 0 ? 1u : 0u);
-      }
-#pragma unroll
-      for (int k = 0; k < D / 16; ++k) {
-        const uint32_t x_off = ((k / 4) * L::kXChunkBytes + (k % 4) * 32) >> 4;
-        const uint32_t y_off = ((k / 4) * L::kYChunkBytes + (k % 4) * 32) >> 4;
-        mma_ss_elect(tmem_base + 128 + b * 64, x1_lo + x_off, desc_hi, y1_lo + y_off, desc_hi, idesc_t, k > 0 ? 1u : 0u);
+      for (int c4 = 0; c4 < D / 64; ++c4) {
+        const uint32_t xo = (c4 * L::kXChunkBytes) >> 4, yo = (c4 * L::kYChunkBytes) >> 4;
+        const uint32_t acc = c4 > 0 ? 1u : 0u;
+        const uint64_t y0d = desc64(y0_lo + yo, desc_hi), y1d = desc64(y1_lo + yo, desc_hi);
+        if constexpr (DKV) {
+          const uint64_t x0d = desc64(x0_lo + xo, desc_hi), x1d = desc64(x1_lo + xo, desc_hi);
+          mma_ss_elect_x4(tmem_base + b * 64, x0d, x0d + 2, x0d + 4, x0d + 6, y0d, y0d + 2, y0d + 4, y0d + 6, idesc_t, acc);
+          mma_ss_elect_x4(tmem_base + 128 + b * 64, x1d, x1d + 2, x1d + 4, x1d + 6, y1d, y1d + 2, y1d + 4, y1d + 6,
+                          idesc_t, acc);
+        } else {   // A operands (Q, dO) from tensor memory
+          mma_ts_elect_x4(tmem_base + b * 64, tmem_base + kXCol + c4 * 32, y0d, y0d + 2, y0d + 4, y0d + 6, idesc_t, acc);
+          mma_ts_elect_x4(tmem_base + 128 + b * 64, tmem_base + kXCol + D / 2 + c4 * 32, y1d, y1d + 2, y1d + 4, y1d + 6,
+                          idesc_t, acc);
+        }
       }
       mma_commit_elect(t_full(b));
       return true;
     };
 
     if (n_it > 0) ok = mbar_wait_warp(x_full, 0, ctx, kRoleMma, 1, 0);
+    tc_fence_after();
     for (int it = 0; ok && it < 2 && it < n_it; ++it) ok = stage1(it);
     for (int it = 0; ok && it < n_it; ++it) {
       const int b = it & 1;
@@ -233,14 +244,15 @@ attn_bwd_sm100(const __grid_constant__ CUtensorMap tmap_x0, const __grid_constan
       const uint32_t y1_mn = smem_desc_lo(y_addr(it) + L::kYTileBytes, L::kYChunkBytes);
       const uint32_t p_tmem = tmem_base + b * 64 + 16;          // bf16 P inside T0[b]
       const uint32_t ds_tmem = tmem_base + 128 + b * 64 + 16;   // bf16 dS inside T1[b]
-#pragma unroll
-      for (int k = 0; k < kBwdBY / 16; ++k) {
-        const uint32_t acc = (it > 0 || k > 0) ? 1u : 0u;
+      {
+        // four k-steps of 16 streamed rows (2048 bytes of an MN-major tile) each
+        const uint32_t acc = it > 0 ? 1u : 0u;
+        const uint64_t y0d = desc64(y0_mn, desc_hi), y1d = desc64(y1_mn, desc_hi);
         if constexpr (DKV) {
-          mma_ts_elect(tmem_base + kAccCol, p_tmem + k * 8, y1_mn + ((k * 2048) >> 4), desc_hi, idesc_acc, acc);
-          mma_ts_elect(tmem_base + kAccCol + D, ds_tmem + k * 8, y0_mn + ((k * 2048) >> 4), desc_hi, idesc_acc, acc);
+          mma_ts_elect_x4(tmem_base + kAccCol, p_tmem, y1d, y1d + 128, y1d + 256, y1d + 384, idesc_acc, acc);
+          mma_ts_elect_x4(tmem_base + kAccCol + D, ds_tmem, y0d, y0d + 128, y0d + 256, y0d + 384, idesc_acc, acc);
         } else {
-          mma_ts_elect(tmem_base + kAccCol, ds_tmem + k * 8, y0_mn + ((k * 2048) >> 4), desc_hi, idesc_acc, acc);
+          mma_ts_elect_x4(tmem_base + kAccCol, ds_tmem, y0d, y0d + 128, y0d + 256, y0d + 384, idesc_acc, acc);
         }
       }
       mma_commit_elect(y_empty(it % STAGES));
@@ -270,10 +282,17 @@ attn_bwd_sm100(const __grid_constant__ CUtensorMap tmap_x0, const __grid_constan
     // per-row statistics (DKV = false): L2 = LSE log2 e, ds = delta * scale; delta is computed here
     float row_l2 = 0.f, row_ds = 0.f;
     if constexpr (!DKV) {
+      // Each thread reads its row of O and dO (for delta) and copies one of the two resident
+      // operands into tensor memory as the A operand of stage 1: group 0 the Q row, group 1 the
+      // dO row.  A row of D bf16 is D/2 32-bit words, exactly the packed layout the MMA reads.
+      uint32_t xw[D / 2];
+#pragma unroll
+      for (int i = 0; i < D / 2; ++i) xw[i] = 0u;
       if (x_row < p.S) {
         const size_t r = static_cast<size_t>(x_plane) * p.S + x_row;
         const uint4* o4 = reinterpret_cast<const uint4*>(p.O + r * D);
         const uint4* g4 = reinterpret_cast<const uint4*>(p.dO + r * D);
+        const uint4* q4 = reinterpret_cast<const uint4*>(p.Q + r * D);
         float acc = 0.f;
 #pragma unroll
         for (int v = 0; v < D / 8; ++v) {
@@ -286,26 +305,42 @@ attn_bwd_sm100(const __grid_constant__ CUtensorMap tmap_x0, const __grid_constan
             acc = fmaf(af.x, gf.x, acc);
             acc = fmaf(af.y, gf.y, acc);
           }
+          const uint4 x = (half == 0) ? __ldg(q4 + v) : g;
+          xw[4 * v + 0] = x.x;
+          xw[4 * v + 1] = x.y;
+          xw[4 * v + 2] = x.z;
+          xw[4 * v + 3] = x.w;
         }
         if (half == 0) p.delta[r] = acc;
         row_ds = acc * p.scale;
         row_l2 = p.LSE[r] * kLog2e;
       }
+#pragma unroll
+      for (int i = 0; i < D / 2; i += 32) tmem_st32(lane_base + kXCol + half * (D / 2) + i, xw + i);
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(x_full);
     }
+
+    // DKV: the 64 per-column statistics of a Q tile are staged in shared memory by one warpgroup
+    // (threads 0-63 LSE, 64-127 delta), fetched from global memory one step ahead so that the
+    // round trip is off the critical path
+    auto fetch_stat = [&](int it) -> float {
+      const int q = y_tile_of(it) * kBwdBY + (tid & 63);
+      const size_t r = static_cast<size_t>(y_plane_of(it)) * p.S + min(q, p.S - 1);
+      return (tid < 64) ? p.LSE[r] * kLog2e : p.delta[r] * p.scale;
+    };
+    float stat_next = 0.f;
+    if (DKV && half == 0 && n_it > 0) stat_next = fetch_stat(0);
 
     for (int it = 0; it < n_it; ++it) {
       const int b = it & 1;
       const int y_row0 = y_tile_of(it) * kBwdBY;
       float* st = stats + b * 2 * kBwdBY;
       if constexpr (DKV) {
-        // stage the 64 per-column statistics of this Q tile: one warpgroup's threads 0-63 LSE, 64-127 delta
-        if (half == 0) {
-          const int col = tid & 63;
-          const int q = y_row0 + col;
-          const size_t r = static_cast<size_t>(y_plane_of(it)) * p.S + min(q, p.S - 1);
-          st[tid] = (tid < 64) ? p.LSE[r] * kLog2e : p.delta[r] * p.scale;
-        }
+        if (half == 0) st[tid] = stat_next;
         asm volatile("bar.sync 2, 256;" ::: "memory");
+        if (half == 0 && it + 1 < n_it) stat_next = fetch_stat(it + 1);
       }
       if (traced) WIR_TRACE_EVENT(p.trace, 1 + half, 10, it);
       const bool got = mbar_wait(t_full(b), (it >> 1) & 1, ctx, kRoleSoftmax, b, it);

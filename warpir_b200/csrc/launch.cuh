@@ -326,7 +326,7 @@ template <int D, bool CAUSAL, bool DKV>
 int launch_attn_bwd_cfg(const CUtensorMap& x0, const CUtensorMap& x1, const CUtensorMap& y0, const CUtensorMap& y1,
                         const wir::AttnBwdParams& p, cudaStream_t stream) {
   auto kernel = wir::attn_bwd_sm100<D, CAUSAL, DKV>;
-  constexpr int smem = wir::AttnBwdSmem<D>::kDynamicBytes;
+  constexpr int smem = wir::AttnBwdSmem<D, DKV>::kDynamicBytes;
   static_assert(smem <= 232448, "shared memory limit per CTA");
   static_assert(smem > 116 * 1024, "one CTA per SM is what keeps the tensor-memory allocation from blocking");
   if (int rc = opt_in_smem(reinterpret_cast<const void*>(kernel), smem)) return rc;
@@ -378,6 +378,7 @@ inline int attn_bwd_impl(const void* Q, const void* K, const void* V, const void
   p.S = static_cast<int>(S);
   p.scale = softmax_scale;
   p.scale_log2 = softmax_scale * 1.4426950408889634f;
+  p.Q = static_cast<const __nv_bfloat16*>(Q);
   p.O = static_cast<const __nv_bfloat16*>(O);
   p.dO = static_cast<const __nv_bfloat16*>(dO);
   p.LSE = LSE;

@@ -323,6 +323,50 @@ __device__ __forceinline__ void mma_ts_elect(uint32_t d_tmem, uint32_t a_tmem, u
       ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// Four MMAs into one accumulator from a single instruction block: one elect, then the four
+// tcgen05.mma back to back with ready-made 64-bit descriptors.  Per MMA the issuing warp
+// spends one instruction instead of an elect, two register-pair moves and a predicate set,
+// which matters for narrow MMAs (N = 64 runs 32 clocks on the tensor core, less than the
+// per-call overhead of the single-MMA helpers).  `accumulate` applies to the first MMA; the
+// other three always accumulate.
+__device__ __forceinline__ uint64_t desc64(uint32_t lo, uint32_t hi) {
+  return (static_cast<uint64_t>(hi) << 32) | lo;
+}
+__device__ __forceinline__ void mma_ss_elect_x4(uint32_t d_tmem, uint64_t a0, uint64_t a1, uint64_t a2, uint64_t a3,
+                                                uint64_t b0, uint64_t b1, uint64_t b2, uint64_t b3, uint32_t idesc,
+                                                uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p, t, e;\n\t"
+      "elect.sync _|e, 0xffffffff;\n\t"
+      "setp.ne.b32 p, %10, 0;\n\t"
+      "setp.eq.b32 t, 0, 0;\n\t"
+      "@e tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %5, %9, p;\n\t"
+      "@e tcgen05.mma.cta_group::1.kind::f16 [%0], %2, %6, %9, t;\n\t"
+      "@e tcgen05.mma.cta_group::1.kind::f16 [%0], %3, %7, %9, t;\n\t"
+      "@e tcgen05.mma.cta_group::1.kind::f16 [%0], %4, %8, %9, t;\n\t}"
+      ::"r"(d_tmem), "l"(a0), "l"(a1), "l"(a2), "l"(a3), "l"(b0), "l"(b1), "l"(b2), "l"(b3), "r"(idesc),
+        "r"(accumulate)
+      : "memory");
+}
+// Same with the A operand in tensor memory at a_tmem, a_tmem + 8, + 16, + 24 (16 K-elements =
+// 8 packed bf16 columns per MMA).
+__device__ __forceinline__ void mma_ts_elect_x4(uint32_t d_tmem, uint32_t a_tmem, uint64_t b0, uint64_t b1, uint64_t b2,
+                                                uint64_t b3, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p, t, e;\n\t.reg .b32 a1, a2, a3;\n\t"
+      "elect.sync _|e, 0xffffffff;\n\t"
+      "setp.ne.b32 p, %7, 0;\n\t"
+      "setp.eq.b32 t, 0, 0;\n\t"
+      "add.u32 a1, %1, 8;\n\t"
+      "add.u32 a2, %1, 16;\n\t"
+      "add.u32 a3, %1, 24;\n\t"
+      "@e tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %6, p;\n\t"
+      "@e tcgen05.mma.cta_group::1.kind::f16 [%0], [a1], %3, %6, t;\n\t"
+      "@e tcgen05.mma.cta_group::1.kind::f16 [%0], [a2], %4, %6, t;\n\t"
+      "@e tcgen05.mma.cta_group::1.kind::f16 [%0], [a3], %5, %6, t;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(b0), "l"(b1), "l"(b2), "l"(b3), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 __device__ __forceinline__ void mma_commit_elect(uint32_t bar) {
   asm volatile(
       "{\n\t.reg .pred e;\n\t"
