@@ -7,6 +7,7 @@
 #include "host_common.cuh"
 #include "attn_bwd_sm100.cuh"
 #include "attn_fwd_sm100.cuh"
+#include "attn_fwd_pair_sm100.cuh"
 #include "gemm_sm100.cuh"
 
 namespace wir {
@@ -267,6 +268,30 @@ int launch_attn_cfg(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensor
   return WARPIR_OK;
 }
 
+// Head dimension 128 on CTA pairs (attn_fwd_pair_sm100.cuh): clusters of two CTAs, four Q tiles each.
+template <bool CAUSAL>
+int launch_attn_pair_cfg(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const wir::AttnParams& p,
+                         cudaStream_t stream) {
+  auto kernel = wir::attn_fwd_pair_sm100<CAUSAL>;
+  constexpr int smem = wir::AttnPairSmem::kDynamicBytes;
+  static_assert(smem <= 232448, "shared memory limit per CTA");
+  static_assert(smem > 116 * 1024, "one CTA per SM is what keeps the tensor-memory allocation from blocking");
+  if (int rc = opt_in_smem(reinterpret_cast<const void*>(kernel), smem)) return rc;
+  const int clusters = (p.S + 4 * wir::kAttnBQ - 1) / (4 * wir::kAttnBQ);
+  dim3 grid(2 * clusters, p.H, p.B);
+  kernel<<<grid, wir::kAttnThreads, smem, stream>>>(tq, tk, tv, p);
+  WIR_CUDA(cudaGetLastError());
+  return WARPIR_OK;
+}
+
+// WARPIR_ATTN_PAIR=0|1 overrides the choice between the single-CTA and the CTA-pair forward.
+inline int env_attn_pair() {
+  static const int v = [] {
+    const char* e = getenv("WARPIR_ATTN_PAIR");
+    return e ? atoi(e) : -1;
+  }();
+  return v;
+}
 
 inline int attn_impl(const void* Q, const void* K, const void* V, void* O, float* LSE, int64_t B, int64_t Hq,
                      int64_t Hkv, int64_t S, int64_t D, float softmax_scale, int causal, int device,
@@ -317,6 +342,15 @@ inline int attn_impl(const void* Q, const void* K, const void* V, void* O, float
   p.status = dev->status;
   p.trace = g_trace;
   p.stagger_clocks = env_attn_stagger();
+  const bool pair = (D == 128) && (env_attn_pair() >= 0 ? env_attn_pair() != 0 : false);
+  if (pair) {
+    CUtensorMap tk_half;   // a CTA loads half the keys of a K block
+    const uint64_t dims[3] = {static_cast<uint64_t>(D), static_cast<uint64_t>(S), static_cast<uint64_t>(B * Hkv)};
+    const uint64_t strides[2] = {static_cast<uint64_t>(D) * 2, static_cast<uint64_t>(S) * D * 2};
+    const uint32_t box_k[3] = {64, 32, 1};
+    if (int rc = make_tmap(&tk_half, K, 3, dims, strides, box_k)) return rc;
+    return causal ? launch_attn_pair_cfg<true>(tq, tk_half, tv, p, stream) : launch_attn_pair_cfg<false>(tq, tk_half, tv, p, stream);
+  }
   if (D == 128) return causal ? launch_attn_cfg<128, true>(tq, tk, tv, p, stream) : launch_attn_cfg<128, false>(tq, tk, tv, p, stream);
   return causal ? launch_attn_cfg<64, true>(tq, tk, tv, p, stream) : launch_attn_cfg<64, false>(tq, tk, tv, p, stream);
 }

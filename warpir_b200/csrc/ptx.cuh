@@ -396,6 +396,94 @@ __device__ __forceinline__ void mma_commit(uint32_t bar) {
                : "memory");
 }
 
+// ---- CTA pairs (thread-block clusters of two, tcgen05 cta_group::2) ------------------------
+// One MMA instruction of the pair's leader (cluster rank 0) computes a 256-row tile: rows
+// 0-127 into the leader's tensor memory, rows 128-255 into the peer's, A from each CTA's own
+// shared or tensor memory (same offsets in both), B split along N between the two CTAs'
+// shared memories.  Nothing here names a cluster-wide TMA copy: every load lands in the
+// shared memory of the CTA that issues it; only the barrier it signals may live in the leader.
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// shared::cluster address of this CTA's shared address `addr` as seen in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t mapa_shared(uint32_t addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// TMA load into this CTA's shared memory whose bytes are counted on a barrier given by its
+// shared::cluster address (the leader's, for operands a pair's MMA reads from both CTAs)
+__device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const CUtensorMap* m, uint32_t bar_cluster, int x,
+                                                 int y, int z) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar_cluster), "r"(x), "r"(y), "r"(z)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t dst_smem, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+// Four pair-MMAs (see mma_ss_elect_x4); issued by the leader only.
+__device__ __forceinline__ void mma_ss_pair_x4(uint32_t d_tmem, uint64_t a0, uint64_t a1, uint64_t a2, uint64_t a3,
+                                               uint64_t b0, uint64_t b1, uint64_t b2, uint64_t b3, uint32_t idesc,
+                                               uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p, t, e;\n\t"
+      "elect.sync _|e, 0xffffffff;\n\t"
+      "setp.ne.b32 p, %10, 0;\n\t"
+      "setp.eq.b32 t, 0, 0;\n\t"
+      "@e tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %5, %9, p;\n\t"
+      "@e tcgen05.mma.cta_group::2.kind::f16 [%0], %2, %6, %9, t;\n\t"
+      "@e tcgen05.mma.cta_group::2.kind::f16 [%0], %3, %7, %9, t;\n\t"
+      "@e tcgen05.mma.cta_group::2.kind::f16 [%0], %4, %8, %9, t;\n\t}"
+      ::"r"(d_tmem), "l"(a0), "l"(a1), "l"(a2), "l"(a3), "l"(b0), "l"(b1), "l"(b2), "l"(b3), "r"(idesc),
+        "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void mma_ts_pair_x4(uint32_t d_tmem, uint32_t a_tmem, uint64_t b0, uint64_t b1, uint64_t b2,
+                                               uint64_t b3, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p, t, e;\n\t.reg .b32 a1, a2, a3;\n\t"
+      "elect.sync _|e, 0xffffffff;\n\t"
+      "setp.ne.b32 p, %7, 0;\n\t"
+      "setp.eq.b32 t, 0, 0;\n\t"
+      "add.u32 a1, %1, 8;\n\t"
+      "add.u32 a2, %1, 16;\n\t"
+      "add.u32 a3, %1, 24;\n\t"
+      "@e tcgen05.mma.cta_group::2.kind::f16 [%0], [%1], %2, %6, p;\n\t"
+      "@e tcgen05.mma.cta_group::2.kind::f16 [%0], [a1], %3, %6, t;\n\t"
+      "@e tcgen05.mma.cta_group::2.kind::f16 [%0], [a2], %4, %6, t;\n\t"
+      "@e tcgen05.mma.cta_group::2.kind::f16 [%0], [a3], %5, %6, t;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(b0), "l"(b1), "l"(b2), "l"(b3), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Arrive on the barrier at shared::cluster address `bar_cluster` (in either CTA of the pair)
+// once every pair-MMA issued so far by this thread has completed.
+__device__ __forceinline__ void mma_commit_pair_elect(uint32_t bar_cluster) {
+  asm volatile(
+      "{\n\t.reg .pred e;\n\t"
+      "elect.sync _|e, 0xffffffff;\n\t"
+      "@e tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}"
+      ::"r"(bar_cluster)
+      : "memory");
+}
+
 // ---- tensor memory <-> registers (shape 32x32b: lane = row, one column per register) ----
 #define WIR_R4(r, o) "=r"(r[o + 0]), "=r"(r[o + 1]), "=r"(r[o + 2]), "=r"(r[o + 3])
 #define WIR_R16(r, o) WIR_R4(r, o), WIR_R4(r, o + 4), WIR_R4(r, o + 8), WIR_R4(r, o + 12)
