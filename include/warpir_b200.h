@@ -138,6 +138,16 @@ int warpir_attn_fwd_bf16(const void* Q, const void* K, const void* V, void* O, f
                          float softmax_scale, int causal, int device, void* cuda_stream);
 
 /*
+ * Same with the kernel variant spelled out: 0 lets the library choose, 1 is the single-CTA
+ * kernel (two 128-row Q tiles per CTA), 2 the CTA-pair kernel (clusters of two CTAs whose
+ * tensor cores share 256-row MMAs; head dimension 128 only).  Results agree to rounding.
+ * No counterpart in the reference; exists for tests and tuning.
+ */
+int warpir_attn_fwd_bf16_ex(const void* Q, const void* K, const void* V, void* O, float* LSE,
+                            int64_t B, int64_t Hq, int64_t Hkv, int64_t S, int64_t D,
+                            float softmax_scale, int causal, int variant, int device, void* cuda_stream);
+
+/*
  * Attention backward: gradients of warpir_attn_fwd_bf16's O with respect to Q, K and V.
  *   Q, O, dO: [B, Hq, S, D] bf16;  K, V: [B, Hkv, S, D] bf16;  LSE: [B, Hq, S] fp32 as written
  *   by the forward (natural log);  dQ: [B, Hq, S, D] fp32;  dK, dV: [B, Hkv, S, D] fp32

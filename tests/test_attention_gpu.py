@@ -13,11 +13,11 @@ from warpir_b200 import runtime
 pytestmark = pytest.mark.gpu
 
 
-def run_attn(Q, K, V, causal, scale=None, want_lse=True):
+def run_attn(Q, K, V, causal, scale=None, want_lse=True, variant=0):
     Qd = Q.cuda()
     O = torch.full_like(Qd, float("nan"))
     L = torch.full(Q.shape[:-1], float("nan"), device="cuda") if want_lse else None
-    runtime.launch_attention(Qd, K.cuda(), V.cuda(), O, L, scale, causal)
+    runtime.launch_attention(Qd, K.cuda(), V.cuda(), O, L, scale, causal, variant)
     runtime.read_status()
     return O.cpu(), (L.cpu() if want_lse else None)
 
@@ -52,6 +52,35 @@ def test_ragged_lengths(S, D, causal, lib):
     Q, K, V = R.attention_inputs(2, 3, S, D, seed=S + D)
     O, L = run_attn(Q, K, V, causal)
     check(O, L, *R.attention_ref(Q, K, V, None, causal))
+
+
+@pytest.mark.parametrize("variant", [1, 2])
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("S", [1, 129, 512, 700, 1100, 2048])
+def test_both_kernel_variants_at_d128(S, causal, variant, lib):
+    """The single-CTA kernel (1) and the CTA-pair kernel (2) against the oracle, with grouped
+    K/V heads, across lengths that leave clusters partly or wholly past the end of the sequence."""
+    Q, K, V = R.attention_inputs(2, 4, S, 128, seed=S + variant, Hkv=2)
+    O, L = run_attn(Q, K, V, causal, variant=variant)
+    check(O, L, *R.attention_ref(Q, K, V, None, causal))
+
+
+@pytest.mark.parametrize("variant", [1, 2])
+def test_rescale_path_in_both_variants(variant, lib):
+    Q, K, V = R.attention_inputs(1, 2, 1024, 128, seed=2)
+    ramp = torch.linspace(0.2, 6.0, 1024).view(1, 1, 1024, 1)
+    K = (K.float() * ramp).bfloat16()
+    O, L = run_attn(Q, K, V, True, variant=variant)
+    check(O, L, *R.attention_ref(Q, K, V, None, True))
+
+
+def test_variant_rejections(lib):
+    Q, K, V = (t.cuda() for t in R.attention_inputs(1, 1, 64, 64, seed=1))
+    O = torch.empty_like(Q)
+    with pytest.raises(runtime.WarpirError):
+        runtime.launch_attention(Q, K, V, O, None, None, False, 2)     # pairs exist for D = 128 only
+    with pytest.raises(runtime.WarpirError):
+        runtime.launch_attention(Q, K, V, O, None, None, False, 3)
 
 
 def test_grouped_kv_heads_and_custom_scale(lib):

@@ -40,6 +40,12 @@ int warpir_attn_fwd_bf16(const void* Q, const void* K, const void* V, void* O, f
   return attn_impl(Q, K, V, O, LSE, B, Hq, Hkv, S, D, softmax_scale, causal, device, cuda_stream);
 }
 
+int warpir_attn_fwd_bf16_ex(const void* Q, const void* K, const void* V, void* O, float* LSE, int64_t B, int64_t Hq,
+                            int64_t Hkv, int64_t S, int64_t D, float softmax_scale, int causal, int variant,
+                            int device, void* cuda_stream) {
+  return attn_impl(Q, K, V, O, LSE, B, Hq, Hkv, S, D, softmax_scale, causal, device, cuda_stream, variant);
+}
+
 int warpir_attn_bwd_bf16(const void* Q, const void* K, const void* V, const void* O, const void* dO, const float* LSE,
                          float* dQ, float* dK, float* dV, float* delta_ws, int64_t B, int64_t Hq, int64_t Hkv,
                          int64_t S, int64_t D, float softmax_scale, int causal, int device, void* cuda_stream) {

@@ -295,10 +295,12 @@ inline int env_attn_pair() {
 
 inline int attn_impl(const void* Q, const void* K, const void* V, void* O, float* LSE, int64_t B, int64_t Hq,
                      int64_t Hkv, int64_t S, int64_t D, float softmax_scale, int causal, int device,
-                     void* cuda_stream) {
+                     void* cuda_stream, int variant = 0) {
   g_last_error[0] = 0;
   if (B < 0 || Hq < 0 || Hkv < 0 || S < 0) return fail(WARPIR_EINVAL, "negative size");
   if (D != 64 && D != 128) return fail(WARPIR_ESHAPE, "D = %lld: head dimension must be 64 or 128", (long long)D);
+  if (variant < 0 || variant > 2) return fail(WARPIR_EINVAL, "variant must be 0 (choose), 1 (single CTA) or 2 (CTA pairs)");
+  if (variant == 2 && D != 128) return fail(WARPIR_ESHAPE, "the CTA-pair kernel covers head dimension 128 only");
   if (B == 0 || Hq == 0 || S == 0) return WARPIR_OK;
   if (Hkv <= 0 || Hq % Hkv != 0) return fail(WARPIR_ESHAPE, "Hq = %lld must be a positive multiple of Hkv = %lld", (long long)Hq, (long long)Hkv);
   if (!(softmax_scale > 0.f) || !std::isfinite(softmax_scale)) return fail(WARPIR_EINVAL, "softmax_scale must be positive and finite");
@@ -342,7 +344,9 @@ inline int attn_impl(const void* Q, const void* K, const void* V, void* O, float
   p.status = dev->status;
   p.trace = g_trace;
   p.stagger_clocks = env_attn_stagger();
-  const bool pair = (D == 128) && (env_attn_pair() >= 0 ? env_attn_pair() != 0 : false);
+  bool pair = false;                                        // default: the single-CTA kernel
+  if (env_attn_pair() >= 0) pair = (D == 128) && env_attn_pair() != 0;
+  if (variant != 0) pair = (variant == 2);
   if (pair) {
     CUtensorMap tk_half;   // a CTA loads half the keys of a K block
     const uint64_t dims[3] = {static_cast<uint64_t>(D), static_cast<uint64_t>(S), static_cast<uint64_t>(B * Hkv)};

@@ -25,7 +25,8 @@ ABI_VERSION = 1
 
 EXPORTS = (
     "warpir_abi_version", "warpir_strerror", "warpir_last_error", "warpir_gemm_bf16",
-    "warpir_gemm_bf16_ex", "warpir_attn_fwd_bf16", "warpir_attn_bwd_bf16", "warpir_read_status",
+    "warpir_gemm_bf16_ex", "warpir_attn_fwd_bf16", "warpir_attn_fwd_bf16_ex", "warpir_attn_bwd_bf16",
+    "warpir_read_status",
     "warpir_gemm_bf16_splitk_noalloc", "warpir_selftest_bounded_wait",
 )
 
@@ -69,6 +70,8 @@ def load_library() -> ctypes.CDLL:
         lib.warpir_gemm_bf16_splitk_noalloc.argtypes = [vp, vp, vp, i64, i64, i64, ci, ci, ci, ci, vp]
         lib.warpir_attn_fwd_bf16.restype = ci
         lib.warpir_attn_fwd_bf16.argtypes = [vp, vp, vp, vp, vp, i64, i64, i64, i64, i64, cf, ci, ci, vp]
+        lib.warpir_attn_fwd_bf16_ex.restype = ci
+        lib.warpir_attn_fwd_bf16_ex.argtypes = [vp, vp, vp, vp, vp, i64, i64, i64, i64, i64, cf, ci, ci, ci, vp]
         lib.warpir_attn_bwd_bf16.restype = ci
         lib.warpir_attn_bwd_bf16.argtypes = [vp] * 10 + [i64] * 5 + [cf, ci, ci, vp]
         lib.warpir_selftest_bounded_wait.restype = ci
@@ -134,13 +137,15 @@ def launch_gemm(A, B, C, b_layout: int = 0, block_n: int = 0, splits: int = 0) -
 
 
 def launch_attention(Q, K, V, O, LSE=None, softmax_scale: Optional[float] = None,
-                     causal: bool = False) -> None:
+                     causal: bool = False, variant: int = 0) -> None:
     """Attention forward on torch's current stream.
 
     Accepts the reference's single-head call ``launch_attention(Q, K, V, O)``
     with ``[N, D]`` tensors (tests/test_modal_attention.py:25-39) as well as
     ``[B, H, S, D]`` tensors with grouped KV heads; ``LSE`` (fp32 ``[B, H, S]``
     or ``[N]``) is filled when given.  Scale defaults to ``1/sqrt(D)``.
+    ``variant``: 0 lets the library choose, 1 forces the single-CTA kernel, 2 the CTA-pair
+    kernel (head dimension 128 only).
     """
     import torch
     lib = load_library()
@@ -164,9 +169,9 @@ def launch_attention(Q, K, V, O, LSE=None, softmax_scale: Optional[float] = None
         lse_ptr = LSE.data_ptr()
     if softmax_scale is None:
         softmax_scale = 1.0 / math.sqrt(D)
-    _check(lib.warpir_attn_fwd_bf16(Q.data_ptr(), K.data_ptr(), V.data_ptr(), O.data_ptr(), lse_ptr,
-                                    Bz, Hq, Hkv, S, D, float(softmax_scale), int(bool(causal)),
-                                    Q.device.index, _stream_of(Q)))
+    _check(lib.warpir_attn_fwd_bf16_ex(Q.data_ptr(), K.data_ptr(), V.data_ptr(), O.data_ptr(), lse_ptr,
+                                       Bz, Hq, Hkv, S, D, float(softmax_scale), int(bool(causal)), int(variant),
+                                       Q.device.index, _stream_of(Q)))
 
 
 def launch_attention_backward(Q, K, V, O, dO, LSE, dQ, dK, dV, delta=None, softmax_scale: Optional[float] = None,
