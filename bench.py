@@ -52,10 +52,11 @@ def load_peaks():
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the workload's kernel, from one ncu
 # capture each (summaries and the exact commands: profiles/*.md); None where none was taken
 NCU_DRAM_BYTES_PER_LAUNCH = {
-    "gemm_8192": 940.8e6,
-    "gemm_skinny_m16": 139.3e6,
-    "attn_noncausal_b16_h16_s4096_d128": 1057.7e6,
-    "attn_causal_b4_h32_s8192_d128": 1061.6e6,
+    "gemm_8192": 941.9e6,
+    "gemm_skinny_m16": 138.3e6,
+    "attn_noncausal_b16_h16_s4096_d128": 1057.0e6,
+    "attn_causal_b4_h32_s8192_d128": 1058.8e6,
+    "attn_bwd_causal_b4_h32_s8192_d128": 3970.4e6,     # both launches of the backward together
 }
 
 # --------------------------------------------------------------------------- workloads
