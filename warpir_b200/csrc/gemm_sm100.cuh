@@ -91,32 +91,39 @@ struct TileCoord {
 };
 
 // Tile index -> block coordinates, walking the tile grid in bands of kGroupM row-blocks.
-__device__ __forceinline__ void decode_tile(int tile, const GemmParams& p, TileCoord& t) {
+// (The work decomposition below is plain integer arithmetic, callable from the host so that
+// it can be checked exhaustively without a GPU.)
+__host__ __device__ __forceinline__ void decode_tile(int tile, const GemmParams& p, TileCoord& t) {
   const int band = kGroupM * p.tiles_n;
   const int g = tile / band;
   const int first_m = g * kGroupM;
-  const int rows = min(p.tiles_m - first_m, kGroupM);
+  const int rest = p.tiles_m - first_m;
+  const int rows = rest < kGroupM ? rest : kGroupM;
   const int in_band = tile - g * band;
   t.m_blk = first_m + in_band % rows;
   t.n_blk = in_band / rows;
   t.tile = tile;
 }
 
-// The sequence of work items of this CTA; producer, MMA issuer and epilogue each walk their own copy.
+// The sequence of work items of CTA `cta` of `grid`; producer, MMA issuer and epilogue each walk their own copy.
 struct WorkIter {
   int w;          // next item (tile x K-split), static round-robin
   int g, g_end;   // stream-K: next k-block of this CTA's run, and its end
+  int cta, grid;
 };
 
-__device__ __forceinline__ WorkIter work_begin(const GemmParams& p) {
+__host__ __device__ __forceinline__ WorkIter work_begin(const GemmParams& p, int cta, int grid) {
   WorkIter it;
-  it.w = blockIdx.x;
-  it.g = blockIdx.x * p.sk_units;
-  it.g_end = min(p.tiles_m * p.tiles_n * p.num_kb, it.g + p.sk_units);
+  it.cta = cta;
+  it.grid = grid;
+  it.w = cta;
+  it.g = cta * p.sk_units;
+  const int total = p.tiles_m * p.tiles_n * p.num_kb;
+  it.g_end = (it.g + p.sk_units < total) ? it.g + p.sk_units : total;
   return it;
 }
 
-__device__ __forceinline__ bool work_next(WorkIter& it, const GemmParams& p, TileCoord& t) {
+__host__ __device__ __forceinline__ bool work_next(WorkIter& it, const GemmParams& p, TileCoord& t) {
   if (p.sk_units == 0) {
     if (it.w >= p.tiles_m * p.tiles_n * p.splits) return false;
     const int tile = it.w / p.splits;
@@ -124,18 +131,19 @@ __device__ __forceinline__ bool work_next(WorkIter& it, const GemmParams& p, Til
     t.split = it.w - tile * p.splits;
     t.nseg = p.splits;
     t.kb_begin = t.split * p.kb_per_split;
-    t.kb_end = min(p.num_kb, t.kb_begin + p.kb_per_split);
-    it.w += gridDim.x;
+    t.kb_end = (t.kb_begin + p.kb_per_split < p.num_kb) ? t.kb_begin + p.kb_per_split : p.num_kb;
+    it.w += it.grid;
     return true;
   }
   if (it.g >= it.g_end) return false;
   const int tile = it.g / p.num_kb;
   decode_tile(tile, p, t);
   t.kb_begin = it.g - tile * p.num_kb;
-  t.kb_end = min(p.num_kb, t.kb_begin + (it.g_end - it.g));
+  const int left = it.g_end - it.g;
+  t.kb_end = (t.kb_begin + left < p.num_kb) ? t.kb_begin + left : p.num_kb;
   const int first_cta = (tile * p.num_kb) / p.sk_units;
   const int last_cta = ((tile + 1) * p.num_kb - 1) / p.sk_units;
-  t.split = static_cast<int>(blockIdx.x) - first_cta;
+  t.split = it.cta - first_cta;
   t.nseg = last_cta - first_cta + 1;
   it.g += t.kb_end - t.kb_begin;
   return true;
@@ -177,7 +185,7 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
   // Producer state (thread 0 only).  The first ring-full of loads is issued right here, before the
   // rest of the CTA has allocated tensor memory and met at the barrier, so the start-up latency of
   // the first copies overlaps the rest of the prologue.
-  WorkIter p_work = work_begin(p);
+  WorkIter p_work = work_begin(p, blockIdx.x, gridDim.x);
   TileCoord p_tile;
   int p_kb = 0, p_kb_end = 0;
   uint32_t p_it = 0;
@@ -258,7 +266,7 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
     uint32_t it = 0, acc_it = 0;
     bool ok = true;
     WIR_TRACE_DECL;
-    WorkIter work = work_begin(p);
+    WorkIter work = work_begin(p, blockIdx.x, gridDim.x);
     TileCoord t;
     for (; ok && work_next(work, p, t); ++acc_it) {
       const int w = t.tile;
@@ -311,7 +319,7 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
     uint32_t acc_it = 0;
     bool ok = true;
     WIR_TRACE_DECL;
-    WorkIter work = work_begin(p);
+    WorkIter work = work_begin(p, blockIdx.x, gridDim.x);
     TileCoord t;
     for (; ok && work_next(work, p, t); ++acc_it) {
       const int w = t.tile;
