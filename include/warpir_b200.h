@@ -166,6 +166,19 @@ int warpir_attn_bwd_bf16(const void* Q, const void* K, const void* V, const void
                          float softmax_scale, int causal, int device, void* cuda_stream);
 
 /*
+ * Launches a tile program that was lowered and compiled into its own shared object
+ * (`Sm100Lowerer().lower(kernel)` -> nvcc -shared): looks `<kernel_name>_launch` up in
+ * `module_handle` (a dlopen handle) and calls it.  `tensor_ptrs`: device pointers of the
+ * program's global inputs then outputs, in signature order; `dims`: four extents (batch,
+ * depth, rows, cols) per tensor; `scalars`: the program's int inputs in signature order.
+ * Replaces the pybind module the reference builds per program with `load_inline` and its
+ * f-string launch wrapper (tests/test_gemm_baseline.py:20-74, tests/test_modal_attention.py:25-99).
+ */
+int warpir_launch_generated(void* module_handle, const char* kernel_name, const void* const* tensor_ptrs,
+                            const int64_t* dims, int n_tensors, const int64_t* scalars, int n_scalars,
+                            int device, void* cuda_stream);
+
+/*
  * Waits for `cuda_stream`, then reports and clears the device's status words:
  * *code is 0 when every kernel launched so far on this device ran to completion,
  * otherwise the kernel-side error (1 = a bounded wait ran out); *detail packs

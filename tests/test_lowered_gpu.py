@@ -58,3 +58,26 @@ def test_attention_program_d128_batched_causal_with_lse(lib):
     O_ref, L_ref = R.attention_ref(Q, K, V, None, True)
     e = R.attention_errors(O.cpu(), L.cpu(), O_ref, L_ref)
     assert e["o_max_abs"] <= R.ATTN_O_ABS_TOL and e["lse_max_abs"] <= R.ATTN_LSE_ABS_TOL
+
+
+def test_launch_by_name_through_the_c_abi(lib):
+    """`warpir_launch_generated`: the C-ABI way to launch a lowered program from its shared object."""
+    import ctypes
+    mod = runtime.load(kernel_pass(build_gemm_kernel(), REFERENCE_MODEL))
+    n = 256
+    A, B = R.gemm_inputs(n, n, n, seed=3, b_layout=0)
+    Ad, Bd = A.cuda(), B.cuda()
+    C = torch.zeros(n, n, device="cuda", dtype=torch.bfloat16)
+    vp, i64 = ctypes.c_void_p, ctypes.c_int64
+    ptrs = (vp * 3)(Ad.data_ptr(), Bd.data_ptr(), C.data_ptr())
+    dims = (i64 * 12)(1, 1, n, n, 1, 1, n, n, 1, 1, n, n)
+    scalars = (i64 * 1)(n)
+    handle = vp(mod._dll._handle)
+    stream = vp(torch.cuda.current_stream().cuda_stream)
+    rc = lib.warpir_launch_generated(handle, b"gemm", ptrs, dims, 3, scalars, 1, 0, stream)
+    assert rc == 0, lib.warpir_last_error()
+    runtime.read_status()
+    e = R.gemm_errors(C.cpu(), R.gemm_ref(A, B, 0))
+    assert e["normalised"] <= R.GEMM_REL_TOL and e["elementwise"] <= R.GEMM_REL_TOL, e
+    assert lib.warpir_launch_generated(handle, b"no_such_kernel", ptrs, dims, 3, scalars, 1, 0, stream) == -1
+    assert b"not found" in lib.warpir_last_error()

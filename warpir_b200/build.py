@@ -23,7 +23,7 @@ INCLUDE = PKG.parent / "include"
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-lineinfo", "-O3", "-std=c++17",
-    "-shared", "-Xcompiler", "-fPIC",
+    "-shared", "-Xcompiler", "-fPIC", "-ldl",
     "-Xptxas", "-v",
 ]
 

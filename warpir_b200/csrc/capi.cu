@@ -1,4 +1,6 @@
 // C-ABI entry points (see include/warpir_b200.h).  The work is in launch.cuh.
+#include <dlfcn.h>
+
 #include "launch.cuh"
 
 using namespace wir::host;
@@ -51,6 +53,43 @@ int warpir_attn_bwd_bf16(const void* Q, const void* K, const void* V, const void
                          int64_t S, int64_t D, float softmax_scale, int causal, int device, void* cuda_stream) {
   return attn_bwd_impl(Q, K, V, O, dO, LSE, dQ, dK, dV, delta_ws, B, Hq, Hkv, S, D, softmax_scale, causal, device,
                        cuda_stream);
+}
+
+int warpir_launch_generated(void* module_handle, const char* kernel_name, const void* const* tensor_ptrs,
+                            const int64_t* dims, int n_tensors, const int64_t* scalars, int n_scalars, int device,
+                            void* cuda_stream) {
+  g_last_error[0] = 0;
+  if (module_handle == nullptr || kernel_name == nullptr) return fail(WARPIR_EINVAL, "module handle or kernel name is NULL");
+  if (n_tensors < 0 || n_scalars < 0 || (n_tensors > 0 && (tensor_ptrs == nullptr || dims == nullptr)))
+    return fail(WARPIR_EINVAL, "tensor arrays missing");
+  char symbol[256];
+  const int len = snprintf(symbol, sizeof symbol, "%s_launch", kernel_name);
+  if (len < 0 || len >= static_cast<int>(sizeof symbol)) return fail(WARPIR_EINVAL, "kernel name too long");
+  using LaunchFn = int (*)(const void* const*, const int64_t*, const int64_t*, int, void*);
+  dlerror();
+  LaunchFn fn = reinterpret_cast<LaunchFn>(dlsym(module_handle, symbol));
+  if (fn == nullptr) return fail(WARPIR_EINVAL, "%s not found in the module: %s", symbol, dlerror());
+  // emitted launchers read a fixed number of entries; hand them zero-padded copies so that a short
+  // caller array can never be over-read (one optional trailing tensor, four trailing scalars)
+  constexpr int kMaxTensors = 16, kMaxScalars = 16;
+  if (n_tensors >= kMaxTensors || n_scalars > kMaxScalars - 4) return fail(WARPIR_EINVAL, "too many tensors or scalars");
+  const void* t[kMaxTensors] = {};
+  int64_t d[4 * kMaxTensors] = {};
+  int64_t sc[kMaxScalars] = {};
+  for (int i = 0; i < n_tensors; ++i) {
+    t[i] = tensor_ptrs[i];
+    for (int k = 0; k < 4; ++k) d[4 * i + k] = dims[4 * i + k];
+  }
+  for (int i = 0; i < n_scalars; ++i) sc[i] = scalars[i];
+  const int rc = fn(t, d, sc, device, cuda_stream);
+  if (rc != WARPIR_OK) {
+    // the text of the failure lives in the module's own copy of the error buffer
+    snprintf(symbol, sizeof symbol, "%s_last_error", kernel_name);
+    using ErrFn = const char* (*)(void);
+    ErrFn err = reinterpret_cast<ErrFn>(dlsym(module_handle, symbol));
+    return fail(rc, "%s", err ? err() : "launch failed");
+  }
+  return rc;
 }
 
 int warpir_read_status(int device, void* cuda_stream, int* code, int* detail) {

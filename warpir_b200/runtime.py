@@ -26,7 +26,7 @@ ABI_VERSION = 1
 EXPORTS = (
     "warpir_abi_version", "warpir_strerror", "warpir_last_error", "warpir_gemm_bf16",
     "warpir_gemm_bf16_ex", "warpir_attn_fwd_bf16", "warpir_attn_fwd_bf16_ex", "warpir_attn_bwd_bf16",
-    "warpir_read_status",
+    "warpir_launch_generated", "warpir_read_status",
     "warpir_gemm_bf16_splitk_noalloc", "warpir_selftest_bounded_wait",
 )
 
@@ -72,6 +72,9 @@ def load_library() -> ctypes.CDLL:
         lib.warpir_attn_fwd_bf16.argtypes = [vp, vp, vp, vp, vp, i64, i64, i64, i64, i64, cf, ci, ci, vp]
         lib.warpir_attn_fwd_bf16_ex.restype = ci
         lib.warpir_attn_fwd_bf16_ex.argtypes = [vp, vp, vp, vp, vp, i64, i64, i64, i64, i64, cf, ci, ci, ci, vp]
+        lib.warpir_launch_generated.restype = ci
+        lib.warpir_launch_generated.argtypes = [vp, ctypes.c_char_p, ctypes.POINTER(vp), ctypes.POINTER(i64), ci,
+                                                ctypes.POINTER(i64), ci, ci, vp]
         lib.warpir_attn_bwd_bf16.restype = ci
         lib.warpir_attn_bwd_bf16.argtypes = [vp] * 10 + [i64] * 5 + [cf, ci, ci, vp]
         lib.warpir_selftest_bounded_wait.restype = ci
