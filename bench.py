@@ -394,6 +394,44 @@ def measure_workload(name, w, steps, warmup, dist_on, device, world, peaks):
     return rec
 
 
+def measure_allgather(w, steps, device, world, rank):
+    """Row-sharded GEMM whose output every GPU needs whole: the fused epilogue all-gather
+    (`warpir_gemm_bf16_allgather`, stores to peers over NVLink from the GEMM itself) against the
+    same GEMM followed by NCCL's all-gather.  Times are device events, max over ranks."""
+    import torch
+    import torch.distributed as dist
+    from warpir_b200 import runtime, sharding
+    M, N, K = w["M"], w["N"], w["K"]
+    g = torch.Generator(device=device).manual_seed(77 + rank)
+    A = (torch.randn(M, K, generator=g, device=device) * w["std"]).bfloat16()
+    B = (torch.randn(N, K, generator=torch.Generator(device=device).manual_seed(78), device=device) * w["std"]).bfloat16()
+    out = sharding.GatheredOutput(world * M, N)
+    block = torch.empty(M, N, dtype=torch.bfloat16, device=device)
+    full = torch.empty(world * M, N, dtype=torch.bfloat16, device=device)
+
+    def fused():
+        sharding.gemm_allgather(A, B, out, rank * M)
+
+    def separate():
+        runtime.launch_gemm(A, B, block, 1)
+        dist.all_gather_into_tensor(full, block)
+
+    res = {}
+    for tag, fn in (("gemm_plus_nccl_allgather", separate), ("fused", fused)):
+        ms = time_steps(fn, steps, 3, True, device)
+        res[tag + "_ms_per_step"] = ms / steps
+    out.wait_all()
+    # same bytes everywhere, and equal to what NCCL gathered
+    same = bool(torch.equal(out.tensor.view(torch.int16), full.view(torch.int16)))
+    flag = torch.tensor([1 if same else 0], device=device)
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    runtime.read_status(device)
+    res.update({"matches_nccl_on_every_rank": bool(flag.item()), "rows_per_gpu": M, "N": N, "K": K,
+                "bytes_sent_per_gpu": 2.0 * M * N * (world - 1), "steps": steps,
+                "nvlink_gbs_per_gpu_fused": 2.0 * M * N * (world - 1) / (res["fused_ms_per_step"] * 1e6)})
+    return res
+
+
 def run_gpu_arm(args, w, name):
     import torch
     from warpir_b200 import runtime
@@ -460,6 +498,10 @@ def run_gpu_arm(args, w, name):
             others.append(measure_workload(oname, ow, k, 5, dist_on, device, world, peaks))
         runtime.read_status(device)
 
+    gathered = None
+    if args.allgather and dist_on and w["kind"] == "gemm":
+        gathered = measure_allgather(w, 20, device, world, rank)
+
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
         cpu = cpu_baseline_gemm(w if w["kind"] == "gemm" else workload_table()["gemm_8192"])
@@ -488,6 +530,8 @@ def run_gpu_arm(args, w, name):
         "frac_of_nominal_2250_per_gpu": value / world / NOMINAL_TFLOPS,
         "other_workloads": others,
     }
+    if gathered is not None:
+        line["fused_allgather"] = gathered
     emit(line)
 
 
@@ -522,6 +566,8 @@ def main():
     ap.add_argument("--no-others", dest="others", action="store_false", help="skip the secondary workloads")
     ap.add_argument("--no-e2e", dest="e2e", action="store_false", help="skip the host-buffer end-to-end leg")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--allgather", action="store_true",
+                    help="with --gpus > 1: also time the GEMM with its output all-gather fused into the epilogue")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl != "reference":
         args.warmup = 3

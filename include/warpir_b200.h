@@ -122,6 +122,21 @@ int warpir_gemm_bf16_splitk_noalloc(const void* A, const void* B, void* C, int64
                                     int b_layout, int block_n, int splits, int device, void* cuda_stream);
 
 /*
+ * GEMM with the all-gather of its output fused into the epilogue.  In a job that splits the rows
+ * of A (and of C) over GPUs, every GPU ends up with the whole C: each finished tile is stored to
+ * n_dst destinations, C_dst[d] being the address of THIS GPU's row block inside GPU d's full C
+ * (its own memory, or a peer's buffer mapped into this GPU's address space, e.g. through torch's
+ * symmetric memory or CUDA IPC / virtual memory mappings).  The stores to peers cross NVLink while
+ * the tensor cores work on the next tiles; nothing else is exchanged and nothing waits.  All
+ * destinations have row pitch N.  The caller orders consumers after the kernel (stream
+ * synchronisation plus a barrier between the processes).  n_dst is 1 .. 8.
+ * Arguments, size rules and return codes otherwise as warpir_gemm_bf16; K is never split here.
+ * No counterpart in the reference (which is single-GPU).
+ */
+int warpir_gemm_bf16_allgather(const void* A, const void* B, void* const* C_dst, int n_dst,
+                               int64_t M, int64_t N, int64_t K, int b_layout, int device, void* cuda_stream);
+
+/*
  * Attention forward: O[b,h] = softmax(softmax_scale * Q[b,h] K[b,hk]^T (+ causal mask)) V[b,hk],
  * LSE[b,h,i] = log sum_j exp(softmax_scale * q_i . k_j) (natural log), hk = h / (Hq / Hkv).
  *   Q, O: [B, Hq, S, D] bf16, contiguous;  K, V: [B, Hkv, S, D] bf16, contiguous;

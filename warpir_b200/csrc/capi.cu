@@ -36,6 +36,15 @@ int warpir_gemm_bf16_ex(const void* A, const void* B, void* C, int64_t M, int64_
   return gemm_impl(A, B, C, M, N, K, b_layout, block_n, splits, device, cuda_stream);
 }
 
+int warpir_gemm_bf16_allgather(const void* A, const void* B, void* const* C_dst, int n_dst, int64_t M, int64_t N,
+                               int64_t K, int b_layout, int device, void* cuda_stream) {
+  if (n_dst < 1) {
+    g_last_error[0] = 0;
+    return fail(WARPIR_EINVAL, "n_dst must be at least 1");
+  }
+  return gemm_impl(A, B, nullptr, M, N, K, b_layout, 0, 1, device, cuda_stream, nullptr, 1, C_dst, n_dst);
+}
+
 int warpir_attn_fwd_bf16(const void* Q, const void* K, const void* V, void* O, float* LSE, int64_t B, int64_t Hq,
                          int64_t Hkv, int64_t S, int64_t D, float softmax_scale, int causal, int device,
                          void* cuda_stream) {

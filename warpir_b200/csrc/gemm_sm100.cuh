@@ -58,6 +58,13 @@ struct GemmParams {
   int sk_max_seg = 0;     // slots reserved per tile
   int sk_rows = 0;        // rows of a slot (min(M, 128))
   int* sk_counters = nullptr;   // one arrival counter per tile; zero between launches
+  // Fused all-gather of the output (n_dst > 1): every finished tile is stored to each of the n_dst
+  // destinations, which are the places of this GPU's block of C in the full C of every GPU of the
+  // job (its own and its peers', mapped into this GPU's address space).  The stores to peers travel
+  // over NVLink while the tensor core works on the next tile.  C is dst[0] when n_dst == 0.
+  static constexpr int kMaxDst = 8;
+  int n_dst = 0;
+  __nv_bfloat16* dst[kMaxDst] = {};
   unsigned long long* trace;   // event trace buffer of debug builds (-DWIR_TRACE), else unused
 };
 
@@ -356,21 +363,25 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
         const int col0 = t.n_blk * BN + c * kChunk;
         if (row < p.M && col0 < p.N) {
           if (t.nseg == 1) {
-            __nv_bfloat16* dst = p.C + static_cast<size_t>(row) * p.ldc + col0;
-            if (vec_ok && col0 + kChunk <= p.N) {
+            uint4 q[kChunk / 8];
 #pragma unroll
-              for (int v = 0; v < kChunk / 8; ++v) {
-                uint4 q;
-                q.x = pack_bf16(__uint_as_float(r[8 * v + 0]), __uint_as_float(r[8 * v + 1]));
-                q.y = pack_bf16(__uint_as_float(r[8 * v + 2]), __uint_as_float(r[8 * v + 3]));
-                q.z = pack_bf16(__uint_as_float(r[8 * v + 4]), __uint_as_float(r[8 * v + 5]));
-                q.w = pack_bf16(__uint_as_float(r[8 * v + 6]), __uint_as_float(r[8 * v + 7]));
-                reinterpret_cast<uint4*>(dst)[v] = q;
+            for (int v = 0; v < kChunk / 8; ++v) {
+              q[v].x = pack_bf16(__uint_as_float(r[8 * v + 0]), __uint_as_float(r[8 * v + 1]));
+              q[v].y = pack_bf16(__uint_as_float(r[8 * v + 2]), __uint_as_float(r[8 * v + 3]));
+              q[v].z = pack_bf16(__uint_as_float(r[8 * v + 4]), __uint_as_float(r[8 * v + 5]));
+              q[v].w = pack_bf16(__uint_as_float(r[8 * v + 6]), __uint_as_float(r[8 * v + 7]));
+            }
+            const int n_out = p.n_dst > 0 ? p.n_dst : 1;
+            for (int d = 0; d < n_out; ++d) {   // one destination, or this block's place in every GPU's C
+              __nv_bfloat16* dst = (p.n_dst > 0 ? p.dst[d] : p.C) + static_cast<size_t>(row) * p.ldc + col0;
+              if (vec_ok && col0 + kChunk <= p.N) {
+#pragma unroll
+                for (int v = 0; v < kChunk / 8; ++v) reinterpret_cast<uint4*>(dst)[v] = q[v];
+              } else {
+#pragma unroll
+                for (int j = 0; j < kChunk; ++j)
+                  if (col0 + j < p.N) dst[j] = __float2bfloat16_rn(__uint_as_float(r[j]));
               }
-            } else {
-#pragma unroll
-              for (int j = 0; j < kChunk; ++j)
-                if (col0 + j < p.N) dst[j] = __float2bfloat16_rn(__uint_as_float(r[j]));
             }
           } else if (p.sk_units != 0) {
             // stream-K: slot [tile][segment] of sk_rows x BN floats, whole chunks (columns past N are never read)

@@ -99,9 +99,29 @@ inline GemmChoice choose_gemm(int64_t M, int64_t N, int64_t K, int sms) {
 // `fixed`: when not null, the instantiation to launch (with `block_n` its tile width and
 // `fixed_mt` its tile height in units of 128 rows); used by
 // the translation units the lowering emits, which pin tile width and ring depth.
+// `dsts` / `n_dst` (fused all-gather): instead of C, n_dst destinations for the finished tiles, each
+// the start of this problem's rows in one GPU's copy of the full output (memory of this GPU or peer
+// memory mapped into its address space).  K-splitting is off in that mode: a tile leaves the SM once.
 inline int gemm_impl(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K, int b_layout, int block_n,
-                     int splits, int device, void* cuda_stream, GemmLaunchFn fixed = nullptr, int fixed_mt = 1) {
+                     int splits, int device, void* cuda_stream, GemmLaunchFn fixed = nullptr, int fixed_mt = 1,
+                     void* const* dsts = nullptr, int n_dst = 0) {
   g_last_error[0] = 0;
+  if (n_dst < 0 || n_dst > wir::GemmParams::kMaxDst || (n_dst > 0 && dsts == nullptr))
+    return fail(WARPIR_EINVAL, "n_dst must be in [1, %d] with a destination array", wir::GemmParams::kMaxDst);
+  if (n_dst > 0) {
+    for (int d = 0; d < n_dst; ++d) {
+      if (dsts[d] == nullptr) return fail(WARPIR_EINVAL, "destination %d is NULL", d);
+      if (reinterpret_cast<uintptr_t>(dsts[d]) & 15) return fail(WARPIR_EALIGN, "destination %d is not 16-byte aligned", d);
+      cudaPointerAttributes attr;
+      if (cudaPointerGetAttributes(&attr, dsts[d]) != cudaSuccess || attr.type != cudaMemoryTypeDevice) {
+        cudaGetLastError();
+        return fail(WARPIR_EDEVICE, "destination %d is not device memory visible to this process", d);
+      }
+    }
+    if (N % 8 != 0) return fail(WARPIR_ESHAPE, "N = %lld: the gathered output needs a row pitch that is a multiple of 16 bytes", (long long)N);
+    C = dsts[0];
+    splits = 1;
+  }
   if (M < 0 || N < 0 || K < 0) return fail(WARPIR_EINVAL, "negative size");
   if (b_layout != 0 && b_layout != 1) return fail(WARPIR_EINVAL, "b_layout must be 0 or 1");
   if (block_n != 0 && block_n != 64 && block_n != 128 && block_n != 256)
@@ -111,12 +131,14 @@ inline int gemm_impl(const void* A, const void* B, void* C, int64_t M, int64_t N
   if (M == 0 || N == 0) return WARPIR_OK;
   DeviceState* dev = nullptr;
   if (int rc = get_device_state(device, &dev)) return rc;
-  if (int rc = check_device_ptr(C, "C", device)) return rc;
+  if (n_dst == 0)
+    if (int rc = check_device_ptr(C, "C", device)) return rc;
   cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
   DeviceGuard guard(device);
   if (guard.err != cudaSuccess) return fail(WARPIR_ECUDA, "cudaSetDevice(%d): %s", device, cudaGetErrorString(guard.err));
   if (K == 0) {
-    WIR_CUDA(cudaMemsetAsync(C, 0, static_cast<size_t>(M) * N * 2, stream));
+    for (int d = 0; d < (n_dst > 0 ? n_dst : 1); ++d)
+      WIR_CUDA(cudaMemsetAsync(n_dst > 0 ? dsts[d] : C, 0, static_cast<size_t>(M) * N * 2, stream));
     return WARPIR_OK;
   }
   if (int rc = check_device_ptr(A, "A", device)) return rc;
@@ -136,7 +158,7 @@ inline int gemm_impl(const void* A, const void* B, void* C, int64_t M, int64_t N
     ch.block_n = 64;
     ch.mt = 1;
     ch.a_rows = (M <= 16) ? 16 : 64;
-    const int want = env_skinny_bn() ? env_skinny_bn() : 128;
+    const int want = n_dst > 0 ? 64 : (env_skinny_bn() ? env_skinny_bn() : 128);   // no shared tiles when gathering
     // Shared tiles cost a round trip of fp32 partial sums through L2, which grows with the row
     // count: above 32 rows the static 64-wide tiling wins unless it leaves many SMs idle.
     const int64_t tiles64 = (N + 63) / 64;
@@ -174,6 +196,8 @@ inline int gemm_impl(const void* A, const void* B, void* C, int64_t M, int64_t N
   p.partial = nullptr;
   p.status = dev->status;
   p.trace = g_trace;
+  p.n_dst = n_dst;
+  for (int d = 0; d < n_dst; ++d) p.dst[d] = static_cast<__nv_bfloat16*>(dsts[d]);
 
   int64_t work = static_cast<int64_t>(p.tiles_m) * p.tiles_n * p.splits;
   int grid = static_cast<int>(work < dev->sm_count ? work : dev->sm_count);

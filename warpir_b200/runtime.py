@@ -25,7 +25,7 @@ ABI_VERSION = 1
 
 EXPORTS = (
     "warpir_abi_version", "warpir_strerror", "warpir_last_error", "warpir_gemm_bf16",
-    "warpir_gemm_bf16_ex", "warpir_attn_fwd_bf16", "warpir_attn_fwd_bf16_ex", "warpir_attn_bwd_bf16",
+    "warpir_gemm_bf16_ex", "warpir_gemm_bf16_allgather", "warpir_attn_fwd_bf16", "warpir_attn_fwd_bf16_ex", "warpir_attn_bwd_bf16",
     "warpir_launch_generated", "warpir_read_status",
     "warpir_gemm_bf16_splitk_noalloc", "warpir_selftest_bounded_wait",
 )
@@ -72,6 +72,8 @@ def load_library() -> ctypes.CDLL:
         lib.warpir_attn_fwd_bf16.argtypes = [vp, vp, vp, vp, vp, i64, i64, i64, i64, i64, cf, ci, ci, vp]
         lib.warpir_attn_fwd_bf16_ex.restype = ci
         lib.warpir_attn_fwd_bf16_ex.argtypes = [vp, vp, vp, vp, vp, i64, i64, i64, i64, i64, cf, ci, ci, ci, vp]
+        lib.warpir_gemm_bf16_allgather.restype = ci
+        lib.warpir_gemm_bf16_allgather.argtypes = [vp, vp, ctypes.POINTER(vp), ci, i64, i64, i64, ci, ci, vp]
         lib.warpir_launch_generated.restype = ci
         lib.warpir_launch_generated.argtypes = [vp, ctypes.c_char_p, ctypes.POINTER(vp), ctypes.POINTER(i64), ci,
                                                 ctypes.POINTER(i64), ci, ci, vp]
@@ -137,6 +139,25 @@ def launch_gemm(A, B, C, b_layout: int = 0, block_n: int = 0, splits: int = 0) -
         raise ValueError("A, B and C must be on one device")
     _check(lib.warpir_gemm_bf16_ex(A.data_ptr(), B.data_ptr(), C.data_ptr(), M, N, K, b_layout,
                                    block_n, splits, A.device.index, _stream_of(A)))
+
+
+def launch_gemm_allgather(A, B, dst_ptrs, N: int, b_layout: int = 1) -> None:
+    """``A @ B`` for this GPU's rows of A, every finished tile stored to each address in
+    ``dst_ptrs``: the place of this row block inside every GPU's copy of the full output (own
+    buffer and peers' buffers mapped into this GPU's address space; see
+    ``warpir_b200.sharding.GatheredOutput``).  Asynchronous on torch's current stream; the caller
+    synchronises the GPUs before reading the gathered output."""
+    import torch
+    lib = load_library()
+    _require(A, "A", torch.bfloat16, 2)
+    _require(B, "B", torch.bfloat16, 2)
+    M, K = A.shape
+    Nb, Kb = (B.shape if b_layout == 1 else B.shape[::-1])
+    if Kb != K or Nb != N:
+        raise ValueError(f"shape mismatch: A {tuple(A.shape)}, B {tuple(B.shape)}, N {N}")
+    ptrs = (ctypes.c_void_p * len(dst_ptrs))(*[int(p) for p in dst_ptrs])
+    _check(lib.warpir_gemm_bf16_allgather(A.data_ptr(), B.data_ptr(), ptrs, len(dst_ptrs), M, N, K, b_layout,
+                                          A.device.index, _stream_of(A)))
 
 
 def launch_attention(Q, K, V, O, LSE=None, softmax_scale: Optional[float] = None,

@@ -63,3 +63,55 @@ def all_gather_outputs(shard, sizes: List[int], dim: int = 0, group=None):
     parts = [torch.empty_like(padded) for _ in range(world)]
     dist.all_gather(parts, padded, group=group)
     return torch.cat([p.narrow(dim, 0, n) for p, n in zip(parts, sizes)], dim=dim)
+
+
+class GatheredOutput:
+    """The full output ``C [M_total, N]`` (bf16) of a row-sharded GEMM, one copy per GPU, that
+    every rank's GEMM writes into directly: the fused form of ``all_gather_outputs``.
+
+    The copies live in torch symmetric memory, which maps every rank's buffer into every
+    other rank's address space; ``runtime.launch_gemm_allgather`` then stores each finished
+    tile of this rank's row block to all of them from the GEMM epilogue, the peer stores
+    crossing NVLink while the next tiles are computed.  No NVLink multicast object is
+    involved (plain peer stores), and multicast binding is switched off for the allocation.
+    """
+
+    def __init__(self, m_total: int, n: int, group=None):
+        import os
+        # plain peer mappings only: on shared hosts a rank that dies while bound to a multicast
+        # object can disturb its peers
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        import torch
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm
+        self.group = group if group is not None else dist.group.WORLD
+        self.m_total, self.n = int(m_total), int(n)
+        self.tensor = symm.empty((self.m_total, self.n), dtype=torch.bfloat16,
+                                 device=torch.device("cuda", torch.cuda.current_device()))
+        handle = symm.rendezvous(self.tensor, self.group)
+        self.rank, self.world = handle.rank, handle.world_size
+        self.ptrs = [int(p) for p in handle.buffer_ptrs]
+        if self.ptrs[self.rank] != self.tensor.data_ptr():
+            raise RuntimeError("symmetric memory handle does not describe this tensor")
+
+    def dst_ptrs(self, row_start: int) -> List[int]:
+        """Addresses of row ``row_start`` in every rank's copy, this rank's own copy first."""
+        if not 0 <= row_start <= self.m_total:
+            raise ValueError("row_start outside the output")
+        order = [self.rank] + [r for r in range(self.world) if r != self.rank]
+        return [self.ptrs[r] + row_start * self.n * 2 for r in order]
+
+    def wait_all(self) -> None:
+        """Every rank's stores have landed in every copy once all ranks return from here."""
+        import torch
+        import torch.distributed as dist
+        torch.cuda.current_stream().synchronize()
+        dist.barrier(group=self.group)
+
+
+def gemm_allgather(A_block, B, out: GatheredOutput, row_start: int, b_layout: int = 1) -> None:
+    """This rank's rows of ``A @ B`` stored straight into every rank's copy of ``out``."""
+    from . import runtime
+    if row_start + A_block.shape[0] > out.m_total:
+        raise ValueError("row block does not fit the gathered output")
+    runtime.launch_gemm_allgather(A_block, B, out.dst_ptrs(row_start), out.n, b_layout)
