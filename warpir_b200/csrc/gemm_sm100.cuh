@@ -87,7 +87,10 @@ struct GemmSmem {
   static constexpr int kTmemPtrOffset = kBarOffset + kNumBars * 8;
   static constexpr int kAbortOffset = kTmemPtrOffset + 4;
   static constexpr int kTicketOffset = kAbortOffset + 4;
-  static constexpr int kBytes = kTicketOffset + 4;
+  // 4 KB per epilogue warp: 32 rows x 128 bytes of output, turned from one row per lane into
+  // whole 128-byte row segments per store when the tile also goes to peer GPUs
+  static constexpr int kStageOutOffset = (kTicketOffset + 4 + 127) & ~127;
+  static constexpr int kBytes = kStageOutOffset + 4 * MT * 4096;
   static constexpr int kDynamicBytes = kBytes + 1024;  // room to align the base to 1024 B
 };
 
@@ -354,6 +357,47 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
       const int row = t.m_blk * kTileM + mt * kGemmBM + quarter * 32 + lane;
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * (MT * BN) + mt * BN;
       constexpr int kChunk = (BN % 32 == 0) ? 32 : 16;
+      if constexpr (BN % 64 == 0 && MT == 1) {   // the host only gathers with 128-row tiles
+        if (p.n_dst > 0) {
+          // Gathered output.  A store instruction of a warp with one row per lane writes 32 separate
+          // 16-byte pieces, which is harmless in local memory (L2 merges them) but wastes most of an
+          // NVLink packet.  So the warp turns its 32 x 64 block around in shared memory (XOR-swizzled,
+          // conflict-free both ways) and stores 128 contiguous bytes per row, four rows per instruction.
+          uint8_t* stage = smem + L::kStageOutOffset + (warp - 2) * 4096;
+          const int row_base = t.m_blk * kTileM + mt * kGemmBM + quarter * 32;
+#pragma unroll 1
+          for (int c2 = 0; c2 < BN / 64; ++c2) {
+            uint32_t r[64];
+            tmem_ld32(t_row + c2 * 64, r);
+            tmem_ld32(t_row + c2 * 64 + 32, r + 32);
+            tmem_wait_ld();
+#pragma unroll
+            for (int v = 0; v < 8; ++v) {
+              uint4 q;
+              q.x = pack_bf16(__uint_as_float(r[8 * v + 0]), __uint_as_float(r[8 * v + 1]));
+              q.y = pack_bf16(__uint_as_float(r[8 * v + 2]), __uint_as_float(r[8 * v + 3]));
+              q.z = pack_bf16(__uint_as_float(r[8 * v + 4]), __uint_as_float(r[8 * v + 5]));
+              q.w = pack_bf16(__uint_as_float(r[8 * v + 6]), __uint_as_float(r[8 * v + 7]));
+              *reinterpret_cast<uint4*>(stage + lane * 128 + ((v ^ (lane & 7)) << 4)) = q;
+            }
+            __syncwarp();
+            const int gcol = t.n_blk * BN + c2 * 64 + (lane & 7) * 8;
+#pragma unroll
+            for (int rr = 0; rr < 8; ++rr) {
+              const int rl = rr * 4 + (lane >> 3);
+              const uint4 q = *reinterpret_cast<const uint4*>(stage + rl * 128 + (((lane & 7) ^ (rl & 7)) << 4));
+              const int grow = row_base + rl;
+              if (grow < p.M && gcol + 8 <= p.N)
+                for (int d = 0; d < p.n_dst; ++d)
+                  *reinterpret_cast<uint4*>(p.dst[d] + static_cast<size_t>(grow) * p.ldc + gcol) = q;
+            }
+            __syncwarp();
+          }
+          tc_fence_before();
+          mbar_arrive(acc_empty_bar(acc));
+          continue;
+        }
+      }
 #pragma unroll 1
       for (int c = 0; c < BN / kChunk; ++c) {
         uint32_t r[kChunk];
@@ -363,25 +407,21 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
         const int col0 = t.n_blk * BN + c * kChunk;
         if (row < p.M && col0 < p.N) {
           if (t.nseg == 1) {
-            uint4 q[kChunk / 8];
+            __nv_bfloat16* dst = p.C + static_cast<size_t>(row) * p.ldc + col0;
+            if (vec_ok && col0 + kChunk <= p.N) {
 #pragma unroll
-            for (int v = 0; v < kChunk / 8; ++v) {
-              q[v].x = pack_bf16(__uint_as_float(r[8 * v + 0]), __uint_as_float(r[8 * v + 1]));
-              q[v].y = pack_bf16(__uint_as_float(r[8 * v + 2]), __uint_as_float(r[8 * v + 3]));
-              q[v].z = pack_bf16(__uint_as_float(r[8 * v + 4]), __uint_as_float(r[8 * v + 5]));
-              q[v].w = pack_bf16(__uint_as_float(r[8 * v + 6]), __uint_as_float(r[8 * v + 7]));
-            }
-            const int n_out = p.n_dst > 0 ? p.n_dst : 1;
-            for (int d = 0; d < n_out; ++d) {   // one destination, or this block's place in every GPU's C
-              __nv_bfloat16* dst = (p.n_dst > 0 ? p.dst[d] : p.C) + static_cast<size_t>(row) * p.ldc + col0;
-              if (vec_ok && col0 + kChunk <= p.N) {
-#pragma unroll
-                for (int v = 0; v < kChunk / 8; ++v) reinterpret_cast<uint4*>(dst)[v] = q[v];
-              } else {
-#pragma unroll
-                for (int j = 0; j < kChunk; ++j)
-                  if (col0 + j < p.N) dst[j] = __float2bfloat16_rn(__uint_as_float(r[j]));
+              for (int v = 0; v < kChunk / 8; ++v) {
+                uint4 q;
+                q.x = pack_bf16(__uint_as_float(r[8 * v + 0]), __uint_as_float(r[8 * v + 1]));
+                q.y = pack_bf16(__uint_as_float(r[8 * v + 2]), __uint_as_float(r[8 * v + 3]));
+                q.z = pack_bf16(__uint_as_float(r[8 * v + 4]), __uint_as_float(r[8 * v + 5]));
+                q.w = pack_bf16(__uint_as_float(r[8 * v + 6]), __uint_as_float(r[8 * v + 7]));
+                reinterpret_cast<uint4*>(dst)[v] = q;
               }
+            } else {
+#pragma unroll
+              for (int j = 0; j < kChunk; ++j)
+                if (col0 + j < p.N) dst[j] = __float2bfloat16_rn(__uint_as_float(r[j]));
             }
           } else if (p.sk_units != 0) {
             // stream-K: slot [tile][segment] of sk_rows x BN floats, whole chunks (columns past N are never read)
@@ -407,7 +447,7 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
       tc_fence_before();
       mbar_arrive(acc_empty_bar(acc));
       if (warp == 2 && lane == 0) WIR_TRACE_EVENT(p.trace, 1, 12, w);
-      if (p.sk_units != 0 && t.nseg > 1) {
+      if (MT == 1 && p.sk_units != 0 && t.nseg > 1) {   // (the host deals k-blocks out only with 128-row tiles)
         // Whoever brings the last segment of a tile finishes it.  Nobody waits: each CTA publishes
         // its slot, takes a ticket, and only the holder of the last ticket reads the slots back
         // (in segment order, so the sum does not depend on who arrived when).

@@ -177,6 +177,9 @@ inline int gemm_impl(const void* A, const void* B, void* C, int64_t M, int64_t N
   if (env_gemm_mt() == 1 && fixed == nullptr) ch.mt = 1;
   if (env_gemm_mt() == 2 && ch.block_n == 256 && fixed == nullptr) ch.mt = 2;
   if (ch.splits > 1 && fixed == nullptr) ch.mt = 1;
+  // Gathering: the 128-row tile keeps two accumulators, so its epilogue (which now also feeds the
+  // slower stores to the peers) runs under the next tile's MMAs; the 256-row tile's does not.
+  if (n_dst > 0 && fixed == nullptr) ch.mt = 1;
   const int num_kb = static_cast<int>((K + wir::kGemmBK - 1) / wir::kGemmBK);
   if (ch.splits > num_kb) ch.splits = num_kb;
   if (ch.splits > 1 && N % 4 != 0) ch.splits = 1;  // the reduce pass works on groups of four columns
