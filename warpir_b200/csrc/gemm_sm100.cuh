@@ -192,9 +192,9 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
   { WIR_TRACE_DECL; if (threadIdx.x == 64) WIR_TRACE_EVENT(p.trace, 2, 20, 0); }
 #endif
 
-  // Producer state (thread 0 only).  The first ring-full of loads is issued right here, before the
-  // rest of the CTA has allocated tensor memory and met at the barrier, so the start-up latency of
-  // the first copies overlaps the rest of the prologue.
+  // Producer state (thread 0 only).  The first loads are issued right here, before the rest of the
+  // CTA has allocated tensor memory and met at the barrier, so the start-up latency of the first
+  // copies overlaps the rest of the prologue.
   WorkIter p_work = work_begin(p, blockIdx.x, gridDim.x);
   TileCoord p_tile;
   int p_kb = 0, p_kb_end = 0;
@@ -226,6 +226,8 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
   };
 
   if (threadIdx.x == 0) {
+    WIR_TRACE_DECL;
+    WIR_TRACE_EVENT(p.trace, 4, 30, 0);
     *abort_flag = 0;
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(full_bar(s), 1);
@@ -238,19 +240,26 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
     mbar_init(drain_bar, 1);
     fence_mbar_init();
     fence_proxy_async_smem();
-    for (int n = 0; n < STAGES; ++n)
+    WIR_TRACE_EVENT(p.trace, 4, 31, 0);
+    // two stages only: issuing a stage costs this thread ~280 clocks, and the rest of the CTA is
+    // waiting for it at the barrier below; the remaining slots are filled right after it
+    for (int n = 0; n < 2 && n < STAGES; ++n)
       if (producer_step(true) <= 0) break;
+    WIR_TRACE_EVENT(p.trace, 4, 32, 0);
   }
   if (warp == 1) {
+    WIR_TRACE_DECL;
+    if (lane == 0) WIR_TRACE_EVENT(p.trace, 5, 40, 0);
     tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_ptr_slot)), kTmemCols);
     tmem_relinquish();
+    if (lane == 0) WIR_TRACE_EVENT(p.trace, 5, 41, 0);
   }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_ptr_slot;
 #ifdef WIR_TRACE
-  { WIR_TRACE_DECL; if (threadIdx.x == 64) WIR_TRACE_EVENT(p.trace, 3, 21, 0); }
+  { WIR_TRACE_DECL; if (threadIdx.x == 64) WIR_TRACE_EVENT(p.trace, 6, 21, 0); }
 #endif
 
   if (warp == 0) {
@@ -521,7 +530,7 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
     tmem_dealloc(tmem_base, kTmemCols);
   }
 #ifdef WIR_TRACE
-  { WIR_TRACE_DECL; if (threadIdx.x == 32) WIR_TRACE_EVENT(p.trace, 3, 22, 0); }
+  { WIR_TRACE_DECL; if (threadIdx.x == 32) WIR_TRACE_EVENT(p.trace, 7, 22, 0); }
 #endif
 }
 
