@@ -133,6 +133,25 @@ attn_bwd_sm100(const __grid_constant__ CUtensorMap tmap_x0, const __grid_constan
     return DKV ? (batch * p.H + head * group + it / per_head) : (batch * p.Hkv + head / group);
   };
 
+  // Producer (thread 0, which also initialises the barriers): loads of the streamed tiles of step
+  // `it` into ring slot it % STAGES.  The resident tiles and the first step go out before the
+  // CTA-wide barrier below, so their latency overlaps the rest of the set-up.
+  auto load_y = [&](int it) -> bool {
+    const int s = it % STAGES;
+    const uint32_t ph = (it / STAGES) & 1;
+    if (!mbar_wait(y_empty(s), ph ^ 1, ctx, kRoleProducer, s, it)) return false;
+    mbar_arrive_expect_tx(y_full(s), 2 * L::kYTileBytes);
+    const uint32_t dst = smem_base + L::kYOffset + s * 2 * L::kYTileBytes;
+    const int row = y_tile_of(it) * kBwdBY, plane = y_plane_of(it);
+#pragma unroll
+    for (int c = 0; c < D / 64; ++c) {
+      tma_load_3d(dst + c * L::kYChunkBytes, &tmap_y0, y_full(s), c * 64, row, plane);
+      tma_load_3d(dst + L::kYTileBytes + c * L::kYChunkBytes, &tmap_y1, y_full(s), c * 64, row, plane);
+    }
+    return true;
+  };
+  bool p_ok = true;
+
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     mbar_init(x_full, DKV ? 1 : kBwdComputeThreads);
@@ -147,6 +166,18 @@ attn_bwd_sm100(const __grid_constant__ CUtensorMap tmap_x0, const __grid_constan
     mbar_init(acc_done, 1);
     mbar_init(drain_bar, 1);
     fence_mbar_init();
+    fence_proxy_async_smem();
+    if (n_it > 0) {
+      if constexpr (DKV) {
+        mbar_arrive_expect_tx(x_full, 2 * L::kXTileBytes);
+#pragma unroll
+        for (int c = 0; c < D / 64; ++c) {
+          tma_load_3d(smem_base + c * L::kXChunkBytes, &tmap_x0, x_full, c * 64, x_row0, x_plane);
+          tma_load_3d(smem_base + L::kXTileBytes + c * L::kXChunkBytes, &tmap_x1, x_full, c * 64, x_row0, x_plane);
+        }
+      }
+      p_ok = load_y(0);
+    }
   }
   if (warp == 1) {
     tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_ptr_slot)), kTmemCols);
@@ -160,29 +191,10 @@ attn_bwd_sm100(const __grid_constant__ CUtensorMap tmap_x0, const __grid_constan
   if (warp == 0) {
     // ------------------------------------------------------------------ producer
     if (lane == 0 && n_it > 0) {
-      if constexpr (DKV) {
-        mbar_arrive_expect_tx(x_full, 2 * L::kXTileBytes);
-#pragma unroll
-        for (int c = 0; c < D / 64; ++c) {
-          tma_load_3d(smem_base + c * L::kXChunkBytes, &tmap_x0, x_full, c * 64, x_row0, x_plane);
-          tma_load_3d(smem_base + L::kXTileBytes + c * L::kXChunkBytes, &tmap_x1, x_full, c * 64, x_row0, x_plane);
-        }
-      }
-      bool ok = true;
-      int it = 0;
-      for (; ok && it < n_it; ++it) {
-        const int s = it % STAGES;
-        const uint32_t ph = (it / STAGES) & 1;
-        if (!mbar_wait(y_empty(s), ph ^ 1, ctx, kRoleProducer, s, it)) { ok = false; break; }
-        mbar_arrive_expect_tx(y_full(s), 2 * L::kYTileBytes);
-        const uint32_t dst = smem_base + L::kYOffset + s * 2 * L::kYTileBytes;
-        const int row = y_tile_of(it) * kBwdBY, plane = y_plane_of(it);
-#pragma unroll
-        for (int c = 0; c < D / 64; ++c) {
-          tma_load_3d(dst + c * L::kYChunkBytes, &tmap_y0, y_full(s), c * 64, row, plane);
-          tma_load_3d(dst + L::kYTileBytes + c * L::kYChunkBytes, &tmap_y1, y_full(s), c * 64, row, plane);
-        }
-      }
+      bool ok = p_ok;
+      int it = 1;   // step 0 went out before the barrier
+      for (; ok && it < n_it; ++it) ok = load_y(it);
+      if (!ok) --it;   // the step whose wait ran out issued nothing
       if (!ok || *abort_flag) {
         if (DKV) mbar_wait_quiet(x_full, 0);
         const int n = it < STAGES ? it : STAGES;

@@ -113,7 +113,25 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
   auto k_index = [&](int j) -> uint32_t { return j == 0 ? 0u : static_cast<uint32_t>(2 * j - 1); };
   auto v_index = [&](int j) -> uint32_t { return static_cast<uint32_t>(j + 1 < n_max ? 2 * j + 2 : 2 * j + 1); };
 
-  if (threadIdx.x == 0) {
+  // Producer state (one lane of the producer warp).  That lane also initialises the barriers and
+  // issues the loads of Q and of the first K block before the CTA-wide barrier below, so their
+  // latency overlaps the tensor-memory allocation and the barrier itself.
+  uint32_t p_idx = 0;
+  auto load_tile = [&](const CUtensorMap* map, int j) -> bool {
+    const int s = p_idx % STAGES;
+    const uint32_t ph = (p_idx / STAGES) & 1;
+    if (!mbar_wait(kv_empty(s), ph ^ 1, ctx, kRoleProducer, s, j)) return false;
+    mbar_arrive_expect_tx(kv_full(s), L::kKVTileBytes);
+    const uint32_t dst = smem_base + L::kKVOffset + s * L::kKVTileBytes;
+#pragma unroll
+    for (int c = 0; c < D / 64; ++c)
+      tma_load_3d(dst + c * L::kKVChunkBytes, map, kv_full(s), c * 64, j * kAttnBKV, bh_kv);
+    ++p_idx;
+    return true;
+  };
+  bool p_ok = true;
+
+  if (threadIdx.x == (kAttnMmaWarp + 2) * 32) {
     *abort_flag = 0;
     mbar_init(q_full, 1);
     for (int s = 0; s < STAGES; ++s) {
@@ -129,9 +147,16 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
     mbar_init(drain_bar, 1);
     mbar_init(drain_bar + 8u, 1);
     fence_mbar_init();
-    prefetch_tensormap(&tmap_q);
-    prefetch_tensormap(&tmap_k);
-    prefetch_tensormap(&tmap_v);
+    fence_proxy_async_smem();
+    const int n_q = (n0 > 0) + (n1 > 0);
+    mbar_arrive_expect_tx(q_full, n_q * L::kQTileBytes);
+    for (int t = 0; t < 2; ++t)
+      if ((t == 0 ? n0 : n1) > 0)
+#pragma unroll
+        for (int c = 0; c < D / 64; ++c)
+          tma_load_3d(smem_base + L::kQOffset + t * L::kQTileBytes + c * L::kQChunkBytes, &tmap_q, q_full,
+                      c * 64, (2 * pair + t) * kAttnBQ, bh);
+    if (n_max > 0) p_ok = load_tile(&tmap_k, 0);
   }
   if (warp == kAttnMmaWarp) {
     tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_ptr_slot)), kTmemCols);
@@ -145,30 +170,9 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
   if (warp == kAttnMmaWarp + 2) {
     // ------------------------------------------------------------------ producer
     if (lane == 0) {
-      const int n_q = (n0 > 0) + (n1 > 0);
-      mbar_arrive_expect_tx(q_full, n_q * L::kQTileBytes);
-      for (int t = 0; t < 2; ++t)
-        if ((t == 0 ? n0 : n1) > 0)
-#pragma unroll
-          for (int c = 0; c < D / 64; ++c)
-            tma_load_3d(smem_base + L::kQOffset + t * L::kQTileBytes + c * L::kQChunkBytes, &tmap_q, q_full,
-                        c * 64, (2 * pair + t) * kAttnBQ, bh);
-      uint32_t idx = 0;
-      bool ok = true;
-      auto load_tile = [&](const CUtensorMap* map, int j) -> bool {
-        const int s = idx % STAGES;
-        const uint32_t ph = (idx / STAGES) & 1;
-        if (!mbar_wait(kv_empty(s), ph ^ 1, ctx, kRoleProducer, s, j)) return false;
-        mbar_arrive_expect_tx(kv_full(s), L::kKVTileBytes);
-        const uint32_t dst = smem_base + L::kKVOffset + s * L::kKVTileBytes;
-#pragma unroll
-        for (int c = 0; c < D / 64; ++c)
-          tma_load_3d(dst + c * L::kKVChunkBytes, map, kv_full(s), c * 64, j * kAttnBKV, bh_kv);
-        ++idx;
-        return true;
-      };
-      // K0, then K(j+1) ahead of V(j): the order in which the MMA warp consumes them
-      if (n_max > 0) ok = load_tile(&tmap_k, 0);
+      bool ok = p_ok;
+      uint32_t& idx = p_idx;
+      // K0 went out before the barrier; then K(j+1) ahead of V(j): the order in which the MMA warps consume them
       for (int j = 0; ok && j < n_max; ++j) {
         if (j + 1 < n_max) ok = load_tile(&tmap_k, j + 1);
         if (ok) ok = load_tile(&tmap_v, j);
