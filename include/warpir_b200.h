@@ -154,8 +154,10 @@ int warpir_attn_fwd_bf16(const void* Q, const void* K, const void* V, void* O, f
 
 /*
  * Same with the kernel variant spelled out: 0 lets the library choose, 1 is the single-CTA
- * kernel (two 128-row Q tiles per CTA), 2 the CTA-pair kernel (clusters of two CTAs whose
- * tensor cores share 256-row MMAs; head dimension 128 only).  Results agree to rounding.
+ * kernel with one softmax warpgroup per 128-row Q tile (the default), 2 the CTA-pair kernel
+ * (clusters of two CTAs whose tensor cores share 256-row MMAs; head dimension 128 only), 3 the
+ * single-CTA kernel with two softmax warpgroups per Q tile (each takes half of the score
+ * columns).  Results agree to rounding.
  * No counterpart in the reference; exists for tests and tuning.
  */
 int warpir_attn_fwd_bf16_ex(const void* Q, const void* K, const void* V, void* O, float* LSE,

@@ -54,24 +54,39 @@ def test_ragged_lengths(S, D, causal, lib):
     check(O, L, *R.attention_ref(Q, K, V, None, causal))
 
 
-@pytest.mark.parametrize("variant", [1, 2])
+@pytest.mark.parametrize("variant", [1, 2, 3])
 @pytest.mark.parametrize("causal", [False, True])
 @pytest.mark.parametrize("S", [1, 129, 512, 700, 1100, 2048])
-def test_both_kernel_variants_at_d128(S, causal, variant, lib):
-    """The single-CTA kernel (1) and the CTA-pair kernel (2) against the oracle, with grouped
-    K/V heads, across lengths that leave clusters partly or wholly past the end of the sequence."""
+def test_every_kernel_variant_at_d128(S, causal, variant, lib):
+    """One softmax warpgroup per tile (1), CTA pairs (2) and two softmax warpgroups per tile (3)
+    against the oracle, with grouped K/V heads, across lengths that leave tiles and clusters partly
+    or wholly past the end of the sequence."""
     Q, K, V = R.attention_inputs(2, 4, S, 128, seed=S + variant, Hkv=2)
     O, L = run_attn(Q, K, V, causal, variant=variant)
     check(O, L, *R.attention_ref(Q, K, V, None, causal))
 
 
-@pytest.mark.parametrize("variant", [1, 2])
-def test_rescale_path_in_both_variants(variant, lib):
+@pytest.mark.parametrize("variant", [1, 2, 3])
+def test_rescale_path_in_every_variant(variant, lib):
     Q, K, V = R.attention_inputs(1, 2, 1024, 128, seed=2)
     ramp = torch.linspace(0.2, 6.0, 1024).view(1, 1, 1024, 1)
     K = (K.float() * ramp).bfloat16()
     O, L = run_attn(Q, K, V, True, variant=variant)
     check(O, L, *R.attention_ref(Q, K, V, None, True))
+
+
+@pytest.mark.parametrize("variant", [1, 3])
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("S", [1, 100, 384, 1000, 2048])
+def test_kernel_variants_at_d64(S, causal, variant, lib):
+    Q, K, V = R.attention_inputs(2, 4, S, 64, seed=S + variant, Hkv=4)
+    O, L = run_attn(Q, K, V, causal, variant=variant)
+    check(O, L, *R.attention_ref(Q, K, V, None, causal))
+    if S == 1000:      # steep score growth: the lazy rescale fires in both column halves
+        ramp = torch.linspace(0.2, 6.0, S).view(1, 1, S, 1)
+        K2 = (K.float() * ramp).bfloat16()
+        O, L = run_attn(Q, K2, V, causal, variant=variant)
+        check(O, L, *R.attention_ref(Q, K2, V, None, causal))
 
 
 def test_variant_rejections(lib):
@@ -80,7 +95,7 @@ def test_variant_rejections(lib):
     with pytest.raises(runtime.WarpirError):
         runtime.launch_attention(Q, K, V, O, None, None, False, 2)     # pairs exist for D = 128 only
     with pytest.raises(runtime.WarpirError):
-        runtime.launch_attention(Q, K, V, O, None, None, False, 3)
+        runtime.launch_attention(Q, K, V, O, None, None, False, 4)
 
 
 def test_grouped_kv_heads_and_custom_scale(lib):

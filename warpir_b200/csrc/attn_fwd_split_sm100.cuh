@@ -1,0 +1,406 @@
+// Attention forward with the softmax of every Q tile split over two warpgroups.
+//
+// Same algorithm, tensor-memory layout, K/V ring and MMA schedule as attn_fwd_sm100.cuh.  There
+// one warpgroup per Q tile walks all 64 score columns of a block, and at head dimension 64,
+// where the MMAs are short, that chain of dependent loads, exponentials and stores is what a
+// block costs.  Here two warpgroups share a tile: both own all 128 rows (thread = row =
+// tensor-memory lane) and each takes 32 of the 64 columns and half of the O columns.  Four
+// softmax warps per scheduler instead of two hide each other's latencies; the price is one
+// exchange of partial row maxima through shared memory per block.  Row sums stay per half and
+// are added once at the end.  Warps 0-7 / 8-15: tile 0 / 1 (halves 0, 1 by groups of four
+// warps); warps 16, 17: MMA issuers; warp 18: producer.
+#pragma once
+
+#include "attn_fwd_sm100.cuh"
+
+namespace wir {
+
+constexpr int kSplitThreads = 608;   // 16 softmax warps, 2 MMA warps, 1 producer warp
+constexpr int kSplitMmaWarp = 16;
+
+template <int D>
+struct AttnSplitSmem {
+  static constexpr int kStages = (D == 128) ? 9 : 12;
+  static constexpr int kQChunkBytes = kAttnBQ * 128;        // 128 rows x 64 bf16
+  static constexpr int kQTileBytes = (D / 64) * kQChunkBytes;
+  static constexpr int kKVChunkBytes = kAttnBKV * 128;      // 64 rows x 64 bf16
+  static constexpr int kKVTileBytes = (D / 64) * kKVChunkBytes;
+  static constexpr int kQOffset = 0;
+  static constexpr int kKVOffset = 2 * kQTileBytes;
+  static constexpr int kBarOffset = kKVOffset + kStages * kKVTileBytes;
+  // q_full, kv_full[S], kv_empty[S], s_full[2][2], p_full[2][2], pv_done[2][2], drain[2]
+  static constexpr int kNumBars = 1 + 2 * kStages + 14;
+  static constexpr int kTmemPtrOffset = kBarOffset + kNumBars * 8;
+  static constexpr int kAbortOffset = kTmemPtrOffset + 4;
+  static constexpr int kExchangeOffset = (kAbortOffset + 4 + 15) & ~15;   // [parity][tile][half][row] floats
+  static constexpr int kBytes = kExchangeOffset + 2 * 2 * 2 * kAttnBQ * 4;
+  static constexpr int kDynamicBytes = kBytes + 1024;
+};
+
+template <int D, bool CAUSAL>
+__global__ void __launch_bounds__(kSplitThreads, 1)
+attn_fwd_split_sm100(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+               const __grid_constant__ CUtensorMap tmap_v, const AttnParams p) {
+  using L = AttnSplitSmem<D>;
+  constexpr int STAGES = L::kStages;
+  constexpr uint32_t kTmemCols = 512;
+  constexpr uint32_t kOCol = 256;        // O_t at columns 256 + t*D
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const uint32_t smem_base = smem_u32(smem);
+  const uint32_t bar_base = smem_base + L::kBarOffset;
+  const uint32_t q_full = bar_base;
+  auto kv_full = [&](int s) { return bar_base + 8u * (1 + s); };
+  auto kv_empty = [&](int s) { return bar_base + 8u * (1 + STAGES + s); };
+  auto s_full = [&](int t, int b) { return bar_base + 8u * (1 + 2 * STAGES + 2 * t + b); };
+  auto p_full = [&](int t, int b) { return bar_base + 8u * (5 + 2 * STAGES + 2 * t + b); };
+  auto pv_done = [&](int t, int b) { return bar_base + 8u * (9 + 2 * STAGES + 2 * t + b); };
+  const uint32_t drain_bar = bar_base + 8u * (13 + 2 * STAGES);
+  volatile uint32_t* tmem_ptr_slot = reinterpret_cast<volatile uint32_t*>(smem + L::kTmemPtrOffset);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kAbortOffset);
+  const AbortCtx ctx{abort_flag, p.status};
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  // ---- which rows / how many KV tiles -----------------------------------------
+  const int pair = CAUSAL ? (gridDim.x - 1 - blockIdx.x) : blockIdx.x;  // heaviest causal tiles first
+  const int head = blockIdx.y, batch = blockIdx.z;
+  const int bh = batch * p.H + head;
+  const int bh_kv = batch * p.Hkv + head / (p.H / p.Hkv);
+  const int nkv = (p.S + kAttnBKV - 1) / kAttnBKV;
+  // KV tiles each Q tile visits (0: the tile lies beyond the sequence)
+  const int qt0 = 2 * pair, qt1 = 2 * pair + 1;
+  const int n0 = (qt0 * kAttnBQ >= p.S) ? 0 : (CAUSAL ? min(nkv, 2 * qt0 + 2) : nkv);
+  const int n1 = (qt1 * kAttnBQ >= p.S) ? 0 : (CAUSAL ? min(nkv, 2 * qt1 + 2) : nkv);
+  const int n_max = max(n0, n1);
+  // position of K(j) / V(j) in the load sequence K0, K1, V0, K2, V1, K3, ...
+  auto k_index = [&](int j) -> uint32_t { return j == 0 ? 0u : static_cast<uint32_t>(2 * j - 1); };
+  auto v_index = [&](int j) -> uint32_t { return static_cast<uint32_t>(j + 1 < n_max ? 2 * j + 2 : 2 * j + 1); };
+
+  // Producer state (one lane of the producer warp).  That lane also initialises the barriers and
+  // issues the loads of Q and of the first K block before the CTA-wide barrier below, so their
+  // latency overlaps the tensor-memory allocation and the barrier itself.
+  uint32_t p_idx = 0;
+  auto load_tile = [&](const CUtensorMap* map, int j) -> bool {
+    const int s = p_idx % STAGES;
+    const uint32_t ph = (p_idx / STAGES) & 1;
+    if (!mbar_wait(kv_empty(s), ph ^ 1, ctx, kRoleProducer, s, j)) return false;
+    mbar_arrive_expect_tx(kv_full(s), L::kKVTileBytes);
+    const uint32_t dst = smem_base + L::kKVOffset + s * L::kKVTileBytes;
+#pragma unroll
+    for (int c = 0; c < D / 64; ++c)
+      tma_load_3d(dst + c * L::kKVChunkBytes, map, kv_full(s), c * 64, j * kAttnBKV, bh_kv);
+    ++p_idx;
+    return true;
+  };
+  bool p_ok = true;
+
+  if (threadIdx.x == (kSplitMmaWarp + 2) * 32) {
+    *abort_flag = 0;
+    mbar_init(q_full, 1);
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(kv_full(s), 1);
+      mbar_init(kv_empty(s), 2);   // one arrival per MMA issuer
+    }
+    for (int t = 0; t < 2; ++t)
+      for (int b = 0; b < 2; ++b) {
+        mbar_init(s_full(t, b), 1);
+        mbar_init(p_full(t, b), 256);   // both column halves of the tile
+        mbar_init(pv_done(t, b), 1);
+      }
+    mbar_init(drain_bar, 1);
+    mbar_init(drain_bar + 8u, 1);
+    fence_mbar_init();
+    fence_proxy_async_smem();
+    const int n_q = (n0 > 0) + (n1 > 0);
+    mbar_arrive_expect_tx(q_full, n_q * L::kQTileBytes);
+    for (int t = 0; t < 2; ++t)
+      if ((t == 0 ? n0 : n1) > 0)
+#pragma unroll
+        for (int c = 0; c < D / 64; ++c)
+          tma_load_3d(smem_base + L::kQOffset + t * L::kQTileBytes + c * L::kQChunkBytes, &tmap_q, q_full,
+                      c * 64, (2 * pair + t) * kAttnBQ, bh);
+    if (n_max > 0) p_ok = load_tile(&tmap_k, 0);
+  }
+  if (warp == kSplitMmaWarp) {
+    tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_ptr_slot)), kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_ptr_slot;
+
+  if (warp == kSplitMmaWarp + 2) {
+    // ------------------------------------------------------------------ producer
+    if (lane == 0) {
+      bool ok = p_ok;
+      uint32_t& idx = p_idx;
+      // K0 went out before the barrier; then K(j+1) ahead of V(j): the order in which the MMA warps consume them
+      for (int j = 0; ok && j < n_max; ++j) {
+        if (j + 1 < n_max) ok = load_tile(&tmap_k, j + 1);
+        if (ok) ok = load_tile(&tmap_v, j);
+      }
+      if (!ok || *abort_flag) {
+        mbar_wait_quiet(q_full, 0);
+        const uint32_t n = idx < STAGES ? idx : STAGES;
+        for (uint32_t back = 1; back <= n; ++back) {
+          const uint32_t i = idx - back;
+          mbar_wait_quiet(kv_full(i % STAGES), (i / STAGES) & 1);
+        }
+      }
+    }
+  } else if (warp == kSplitMmaWarp || warp == kSplitMmaWarp + 1) {
+    // ------------------------------------------------------------------ MMA issuer of one Q tile
+    // One issuing warp per Q tile.  The whole warp runs the loop (warp-uniform operands), one
+    // elected lane issues; a single issuer for both tiles cannot hide the waits, fences and
+    // commits that surround each group of MMAs.
+    const int t = warp - kSplitMmaWarp;
+    const int n = (t == 0) ? n0 : n1;
+    constexpr uint32_t idesc_qk = idesc_bf16_f32(kAttnBQ, kAttnBKV, 0, 0);
+    constexpr uint32_t idesc_pv = idesc_bf16_f32(kAttnBQ, D, 0, 1);
+    constexpr uint32_t desc_hi = smem_desc_hi_sw128(1024);
+    const uint32_t q_lo = smem_desc_lo(smem_base + L::kQOffset + t * L::kQTileBytes, 16);
+    const uint32_t o_tmem = tmem_base + kOCol + t * D;
+    bool ok = true;
+    auto kv_addr = [&](uint32_t idx) { return smem_base + L::kKVOffset + (idx % STAGES) * L::kKVTileBytes; };
+    auto wait_kv = [&](uint32_t idx, int tag) {
+      return mbar_wait_warp(kv_full(idx % STAGES), (idx / STAGES) & 1, ctx, kRoleMma, tag, idx);
+    };
+    // every K/V slot is released by BOTH issuers (its empty barrier counts two arrivals); the
+    // issuer whose tile does not visit a block releases it once the block has landed
+    auto skip_tile = [&](uint32_t idx) -> bool {
+      if (!wait_kv(idx, 40 + t)) return false;
+      mbar_arrive_elect(kv_empty(idx % STAGES));
+      return true;
+    };
+    // S_t[j & 1] = Q_t K(j)^T
+    auto issue_qk = [&](int j) -> bool {
+      const uint32_t idx = k_index(j);
+      if (!wait_kv(idx, 10 + t)) return false;
+      tc_fence_after();
+      const uint32_t k_lo = smem_desc_lo(kv_addr(idx), 16);
+      const uint32_t d_tmem = tmem_base + t * 128 + (j & 1) * 64;
+#pragma unroll
+      for (int k = 0; k < D / 16; ++k) {
+        // 16 elements of the head dimension further: 32 bytes inside a 64-element chunk, then the next chunk
+        const uint32_t q_off = ((k / 4) * L::kQChunkBytes + (k % 4) * 32) >> 4;
+        const uint32_t k_off = ((k / 4) * L::kKVChunkBytes + (k % 4) * 32) >> 4;
+        mma_ss_elect(d_tmem, q_lo + q_off, desc_hi, k_lo + k_off, desc_hi, idesc_qk, k > 0 ? 1u : 0u);
+      }
+      mma_commit_elect(s_full(t, j & 1));
+      mma_commit_elect(kv_empty(idx % STAGES));
+      return true;
+    };
+
+    if (n > 0) ok = mbar_wait_warp(q_full, 0, ctx, kRoleMma, 1, 0);
+    for (int j = 0; ok && j < 2 && j < n_max; ++j) ok = (j < n) ? issue_qk(j) : skip_tile(k_index(j));
+
+    for (int j = 0; ok && j < n_max; ++j) {
+      const uint32_t idx = v_index(j);
+      if (j < n) {
+        // O_t += P_t(j) V(j)
+        if (!mbar_wait_warp(p_full(t, j & 1), (j >> 1) & 1, ctx, kRoleMma, 20 + t, j)) { ok = false; break; }
+        if (!wait_kv(idx, 30 + t)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t v_lo = smem_desc_lo(kv_addr(idx), L::kKVChunkBytes);
+        const uint32_t p_tmem = tmem_base + t * 128 + (j & 1) * 64 + 16;   // packed P sits at columns 16..47
+#pragma unroll
+        for (int k = 0; k < kAttnBKV / 16; ++k) {
+          // 16 keys further: 8 packed-bf16 columns of P, 16 rows (2048 B) of V
+          mma_ts_elect(o_tmem, p_tmem + k * 8, v_lo + ((k * 2048) >> 4), desc_hi, idesc_pv,
+                       (j > 0 || k > 0) ? 1u : 0u);
+        }
+        mma_commit_elect(pv_done(t, j & 1));
+        mma_commit_elect(kv_empty(idx % STAGES));
+      } else {
+        ok = skip_tile(idx);
+      }
+      if (ok && j + 2 < n_max) ok = (j + 2 < n) ? issue_qk(j + 2) : skip_tile(k_index(j + 2));
+    }
+    if (!ok || *abort_flag) {
+      mma_commit_elect(drain_bar + 8u * t);
+      mbar_wait_quiet(drain_bar + 8u * t, 0);
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------------------------------------------ softmax + epilogue
+    // Two warpgroups per Q tile: both own all 128 rows (one row per thread) and each takes 32 of
+    // the 64 score columns of a block.  The row max is the only thing the halves must agree on;
+    // they swap their partial maxima through shared memory at one named barrier per block.
+    const int t = warp >> 3;                 // which Q tile
+    const int half = (warp >> 2) & 1;        // which 32 of the 64 columns
+    const int quarter = warp & 3;            // tensor-memory lanes 32*quarter .. +31
+    const int r_in = quarter * 32 + lane;    // row inside the tile
+    const int qt = 2 * pair + t;
+    const int q_row = qt * kAttnBQ + r_in;
+    const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+    const uint32_t o_addr = lane_base + kOCol + t * D + half * (D / 2);   // this half's columns of O_t
+    const float c = p.scale_log2;
+    const int n = (t == 0) ? n0 : n1;
+    const int first_masked = CAUSAL ? 2 * qt : (p.S % kAttnBKV != 0 ? nkv - 1 : nkv);
+    float* xch = reinterpret_cast<float*>(smem + L::kExchangeOffset);   // [parity][tile][half][row]
+    auto xslot = [&](int par, int h) { return xch + ((par * 2 + t) * 2 + h) * kAttnBQ + r_in; };
+
+    float m = -INFINITY;  // running (possibly stale) max of the raw scores, identical in both halves
+    float l = 0.f;        // this half's share of the running sum of 2^(s c - m c)
+    bool ok = true;
+    bool bad = false;     // a wait inside a per-warp branch ran out: carried to the next tile-wide vote
+
+    for (int j = 0; j < n; ++j) {
+      const int b = j & 1;
+      const uint32_t s_addr = lane_base + t * 128 + b * 64;
+      const bool got = mbar_wait(s_full(t, b), (j >> 1) & 1, ctx, kRoleSoftmax, t, j) && !bad;
+      {
+        // the 256 threads of a tile meet at named barriers, so they must agree on going on
+        uint32_t all;
+        asm volatile(
+            "{\n\t.reg .pred a, q;\n\t"
+            "setp.ne.u32 q, %1, 0;\n\t"
+            "bar.red.and.pred a, %2, 256, q;\n\t"
+            "selp.u32 %0, 1, 0, a;\n\t}"
+            : "=r"(all)
+            : "r"(got ? 1u : 0u), "r"(1 + t)
+            : "memory");
+        if (all == 0) { ok = false; break; }
+      }
+      tc_fence_after();
+      if (j == 0 && t == 1 && p.stagger_clocks > 0) {
+        const long long t0 = clock64();
+        while (clock64() - t0 < p.stagger_clocks) {
+        }
+      }
+
+      uint32_t sb[32];  // this thread's 32 raw scores, as fp32 bit patterns
+      tmem_ld32(s_addr + half * 32, sb);
+      tmem_wait_ld();
+#define WIR_S(i) __uint_as_float(sb[i])
+
+      if (j >= first_masked || (j == nkv - 1 && p.S % kAttnBKV != 0)) {
+        const int k0 = j * kAttnBKV + half * 32;
+        const int limit = CAUSAL ? min(q_row, p.S - 1) : (p.S - 1);  // last visible key
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+          if (k0 + i > limit) sb[i] = 0xff800000u;  // -inf
+      }
+
+      float mx0 = WIR_S(0), mx1 = WIR_S(1), mx2 = WIR_S(2), mx3 = WIR_S(3);
+#pragma unroll
+      for (int i = 4; i < 32; i += 4) {
+        mx0 = fmaxf(mx0, WIR_S(i));
+        mx1 = fmaxf(mx1, WIR_S(i + 1));
+        mx2 = fmaxf(mx2, WIR_S(i + 2));
+        mx3 = fmaxf(mx3, WIR_S(i + 3));
+      }
+      const float mine = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+      *xslot(b, half) = mine;
+      asm volatile("bar.sync %0, 256;" ::"r"(3 + t) : "memory");
+      const float m_new = fmaxf(m, fmaxf(mine, *xslot(b, half ^ 1)));
+      // identical in the partner warp (same rows, same combined max), so both halves rescale together
+      const bool grow = (m_new - m) * c > kRescaleThreshold;
+      if (__any_sync(0xffffffffu, grow)) {
+        if (j > 0) {
+          const bool done = mbar_wait(pv_done(t, (j - 1) & 1), ((j - 1) >> 1) & 1, ctx, kRoleSoftmax, 8 + t, j);
+          if (!__all_sync(0xffffffffu, done)) {
+            bad = true;   // no early exit here: the other warps of the tile are heading for a barrier
+          } else {
+            tc_fence_after();
+            const float alpha = ex2_approx((m - m_new) * c);
+            l *= alpha;
+#pragma unroll 1
+            for (int cidx = 0; cidx < D / 64; ++cidx) {   // this half's D/2 columns of O
+              uint32_t o[32];
+              tmem_ld32(o_addr + cidx * 32, o);
+              tmem_wait_ld();
+#pragma unroll
+              for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+              tmem_st32(o_addr + cidx * 32, o);
+            }
+          }
+        }
+        m = m_new;
+      }
+
+      const float neg_mc = -m * c;
+      const float2 c2 = make_float2(c, c), neg_mc2 = make_float2(neg_mc, neg_mc);
+      float2 la = make_float2(0.f, 0.f), lb = make_float2(0.f, 0.f);
+      uint32_t pk[16];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        const float2 x = __ffma2_rn(make_float2(WIR_S(2 * i), WIR_S(2 * i + 1)), c2, neg_mc2);
+        float2 e;
+        if ((i & 3) == 3) {
+          e = ex2_fma2(x);
+        } else {
+          e.x = ex2_approx(x.x);
+          e.y = ex2_approx(x.y);
+        }
+        if (i & 1) lb = __fadd2_rn(lb, e);
+        else la = __fadd2_rn(la, e);
+        pk[i] = pack_bf16(e.x, e.y);
+      }
+#undef WIR_S
+      // Packed P (32 columns) sits at columns 16..47 of the score buffer: half 0 read columns 0..31
+      // and writes 16..31, half 1 read 32..63 and writes 32..47, so neither overwrites what the
+      // other may still be reading.
+      tmem_st16(s_addr + 16 + half * 16, pk);
+      l += (la.x + lb.x) + (la.y + lb.y);
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(p_full(t, b));
+    }
+
+    if (ok && n > 0) {
+      const bool got = mbar_wait(pv_done(t, (n - 1) & 1), ((n - 1) >> 1) & 1, ctx, kRoleEpilogue, t, n) && !bad;
+      uint32_t all;
+      asm volatile(
+          "{\n\t.reg .pred a, q;\n\t"
+          "setp.ne.u32 q, %1, 0;\n\t"
+          "bar.red.and.pred a, %2, 256, q;\n\t"
+          "selp.u32 %0, 1, 0, a;\n\t}"
+          : "=r"(all)
+          : "r"(got ? 1u : 0u), "r"(1 + t)
+          : "memory");
+      if (all != 0) {
+        tc_fence_after();
+        // the two halves' shares of the row sum
+        *xslot(n & 1, half) = l;
+        asm volatile("bar.sync %0, 256;" ::"r"(3 + t) : "memory");
+        const float l_all = l + *xslot(n & 1, half ^ 1);
+        const float inv_l = 1.0f / l_all;
+        const bool live = q_row < p.S;
+        __nv_bfloat16* dst = p.O + (static_cast<size_t>(bh) * p.S + (live ? q_row : 0)) * D + half * (D / 2);
+#pragma unroll 1
+        for (int cidx = 0; cidx < D / 64; ++cidx) {
+          uint32_t o[32];
+          tmem_ld32(o_addr + cidx * 32, o);
+          tmem_wait_ld();
+          if (live) {
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              uint4 q;
+              q.x = pack_bf16(__uint_as_float(o[8 * v + 0]) * inv_l, __uint_as_float(o[8 * v + 1]) * inv_l);
+              q.y = pack_bf16(__uint_as_float(o[8 * v + 2]) * inv_l, __uint_as_float(o[8 * v + 3]) * inv_l);
+              q.z = pack_bf16(__uint_as_float(o[8 * v + 4]) * inv_l, __uint_as_float(o[8 * v + 5]) * inv_l);
+              q.w = pack_bf16(__uint_as_float(o[8 * v + 6]) * inv_l, __uint_as_float(o[8 * v + 7]) * inv_l);
+              reinterpret_cast<uint4*>(dst + cidx * 32)[v] = q;
+            }
+          }
+        }
+        if (live && half == 0 && p.LSE != nullptr)
+          p.LSE[static_cast<size_t>(bh) * p.S + q_row] = m * c * 0.6931471805599453f + logf(l_all);
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == kSplitMmaWarp) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+}  // namespace wir
