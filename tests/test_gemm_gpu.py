@@ -96,6 +96,31 @@ def test_few_rows_stream_k(shape, b_layout, lib):
     check(run_gemm(A, B, b_layout, 64, 1), ref)
 
 
+def test_k_split_paths_on_two_streams_at_once(lib):
+    """The K-splitting paths keep fp32 partial sums and arrival counters in library scratch; every
+    CUDA stream has its own, so launches that overlap on different streams do not disturb each other."""
+    shapes = [(16, 8192, 4096), (8, 4096, 8192)]
+    streams = [torch.cuda.Stream() for _ in shapes]
+    data = []
+    for (M, N, K), st in zip(shapes, streams):
+        A, B = R.gemm_inputs(M, N, K, seed=M, std=0.05)
+        with torch.cuda.stream(st):
+            Ad, Bd = A.cuda(), B.cuda()
+            C = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+        data.append((A, B, Ad, Bd, C))
+    torch.cuda.synchronize()
+    for _ in range(20):                      # interleaved launches, both streams busy
+        for (A, B, Ad, Bd, C), st in zip(data, streams):
+            with torch.cuda.stream(st):
+                runtime.launch_gemm(Ad, Bd, C, 1)             # stream-K
+                runtime.launch_gemm(Ad, Bd, C, 1, 64, 4)      # split-K with the reduce pass
+                runtime.launch_gemm(Ad, Bd, C, 1)
+    torch.cuda.synchronize()
+    runtime.read_status()
+    for A, B, Ad, Bd, C in data:
+        check(C.cpu(), R.gemm_ref(A, B))
+
+
 def test_config2_2048_against_oracle(lib):
     A, B = R.gemm_inputs(2048, 2048, 2048, seed=1)
     check(run_gemm(A, B, 1), R.gemm_ref(A, B))

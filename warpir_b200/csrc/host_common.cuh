@@ -15,6 +15,7 @@
 #include <cstdlib>
 #include <cstring>
 #include <mutex>
+#include <unordered_map>
 
 #include "../../include/warpir_b200.h"
 
@@ -44,9 +45,15 @@ struct DeviceState {
   bool ready = false;
   int sm_count = 0;
   int* status = nullptr;        // 4 ints
-  float* splitk = nullptr;      // grown on demand
-  size_t splitk_bytes = 0;
-  int* sk_counters = nullptr;   // kSkMaxTiles arrival counters of the stream-K GEMM, zero between launches
+  // Scratch of the K-splitting GEMM paths (fp32 partial sums; stream-K arrival counters, zero
+  // between launches), one set per CUDA stream: launches on one stream run one after the other,
+  // launches on different streams may overlap and must not share it.  Grown on demand.
+  struct Scratch {
+    float* partial = nullptr;
+    size_t partial_bytes = 0;
+    int* counters = nullptr;    // kSkMaxTiles ints
+  };
+  std::unordered_map<void*, Scratch> scratch;   // keyed by stream handle
 };
 constexpr int kSkMaxTiles = 8192;
 
@@ -86,8 +93,6 @@ inline int get_device_state(int device, DeviceState** out) {
     WIR_CUDA(cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, device));
     WIR_CUDA(cudaMalloc(&d.status, 4 * sizeof(int)));
     WIR_CUDA(cudaMemset(d.status, 0, 4 * sizeof(int)));
-    WIR_CUDA(cudaMalloc(&d.sk_counters, kSkMaxTiles * sizeof(int)));
-    WIR_CUDA(cudaMemset(d.sk_counters, 0, kSkMaxTiles * sizeof(int)));
     d.ready = true;
   }
   if (g_encode == nullptr) {
@@ -99,6 +104,35 @@ inline int get_device_state(int device, DeviceState** out) {
     g_encode = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(fn);
   }
   *out = &d;
+  return WARPIR_OK;
+}
+
+// The calling stream's scratch with at least `bytes` of partial-sum space (and the counters).
+// May allocate, which synchronises: the first call of a given size on a stream does, later ones do not.
+inline int stream_scratch(DeviceState* dev, cudaStream_t stream, size_t bytes, DeviceState::Scratch** out) {
+  std::lock_guard<std::mutex> lock(g_mutex);
+  DeviceState::Scratch& sc = dev->scratch[static_cast<void*>(stream)];
+  if (sc.counters == nullptr) {
+    if (cudaMalloc(&sc.counters, kSkMaxTiles * sizeof(int)) != cudaSuccess) {
+      cudaGetLastError();
+      return fail(WARPIR_ENOMEM, "stream-K counters");
+    }
+    WIR_CUDA(cudaMemset(sc.counters, 0, kSkMaxTiles * sizeof(int)));
+  }
+  if (sc.partial_bytes < bytes) {
+    if (sc.partial) {
+      WIR_CUDA(cudaStreamSynchronize(stream));   // the buffer being replaced may still be in use there
+      WIR_CUDA(cudaFree(sc.partial));
+      sc.partial = nullptr;
+      sc.partial_bytes = 0;
+    }
+    if (cudaMalloc(&sc.partial, bytes) != cudaSuccess) {
+      cudaGetLastError();
+      return fail(WARPIR_ENOMEM, "K-split scratch of %zu bytes", bytes);
+    }
+    sc.partial_bytes = bytes;
+  }
+  *out = &sc;
   return WARPIR_OK;
 }
 
@@ -225,7 +259,9 @@ inline int read_status_impl(int device, void* cuda_stream, int* code, int* detai
   if (host[0] != 0) {
     WIR_CUDA(cudaMemset(dev->status, 0, sizeof host));
     // a kernel that gave up may have left stream-K tickets behind
-    WIR_CUDA(cudaMemset(dev->sk_counters, 0, kSkMaxTiles * sizeof(int)));
+    std::lock_guard<std::mutex> lock(g_mutex);
+    for (auto& kv : dev->scratch)
+      if (kv.second.counters) WIR_CUDA(cudaMemset(kv.second.counters, 0, kSkMaxTiles * sizeof(int)));
   }
   if (code) *code = host[0];
   if (detail) *detail = host[2];

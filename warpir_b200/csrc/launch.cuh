@@ -212,27 +212,15 @@ inline int gemm_impl(const void* A, const void* B, void* C, int64_t M, int64_t N
     grid = static_cast<int>((units + p.sk_units - 1) / p.sk_units);
     p.sk_max_seg = (num_kb + p.sk_units - 2) / p.sk_units + 1;
     p.sk_rows = static_cast<int>(M < wir::kGemmBM ? M : wir::kGemmBM);
-    p.sk_counters = dev->sk_counters;
     sk_bytes = static_cast<size_t>(p.tiles_m) * p.tiles_n * p.sk_max_seg * p.sk_rows * ch.block_n * sizeof(float);
   }
 
   if (p.splits > 1 || ch.stream_k) {
     const size_t need = ch.stream_k ? sk_bytes : static_cast<size_t>(p.splits) * M * N * sizeof(float);
-    std::lock_guard<std::mutex> lock(g_mutex);
-    if (dev->splitk_bytes < need) {
-      if (dev->splitk) {
-        WIR_CUDA(cudaDeviceSynchronize());
-        WIR_CUDA(cudaFree(dev->splitk));
-        dev->splitk = nullptr;
-        dev->splitk_bytes = 0;
-      }
-      if (cudaMalloc(&dev->splitk, need) != cudaSuccess) {
-        cudaGetLastError();
-        return fail(WARPIR_ENOMEM, "split-K scratch of %zu bytes", need);
-      }
-      dev->splitk_bytes = need;
-    }
-    p.partial = dev->splitk;
+    DeviceState::Scratch* sc = nullptr;
+    if (int rc = stream_scratch(dev, stream, need, &sc)) return rc;
+    p.partial = sc->partial;
+    p.sk_counters = sc->counters;
   }
 
   CUtensorMap ta, tb;
