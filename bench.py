@@ -455,6 +455,13 @@ def run_gpu_arm(args, w, name):
     for _ in range(args.warmup):
         step()
     sampler.start()
+    # nvidia-smi needs a moment to come up: keep the GPU under the same load (extra untimed steps)
+    # until its first sample is in, so that the samples cover the timed region from its start
+    t_wait = time.perf_counter()
+    while not sampler.lines and time.perf_counter() - t_wait < 2.0:
+        step()
+        torch.cuda.synchronize()
+    del sampler.lines[:]
     ms = time_steps(step, args.steps, 0, dist_on, device)
     clocks = sampler.stop()
     runtime.read_status(device)
