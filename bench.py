@@ -458,7 +458,7 @@ def run_gpu_arm(args, w, name):
     # nvidia-smi needs a moment to come up: keep the GPU under the same load (extra untimed steps)
     # until its first sample is in, so that the samples cover the timed region from its start
     t_wait = time.perf_counter()
-    while not sampler.lines and time.perf_counter() - t_wait < 2.0:
+    while sampler.proc is not None and not sampler.lines and time.perf_counter() - t_wait < 2.0:
         step()
         torch.cuda.synchronize()
     del sampler.lines[:]
