@@ -164,7 +164,13 @@ attn_fwd_pair_sm100(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         if (j + 1 < n_max) ok = load_k(j + 1);
         if (ok) ok = load_v(j);
       }
-      (void)ok;   // copies in flight are waited for by the cluster-wide barrier protocol below
+      if (!ok || *abort_flag) {
+        // The copies in flight are counted on the leader's barriers, which the peer cannot wait on.
+        // After a failure give them time to land (they take microseconds) before the CTA may exit
+        // and its shared memory go to another CTA.
+        const uint64_t t0 = global_timer_ns();
+        while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
+      }
     }
   } else if ((warp == kAttnMmaWarp || warp == kAttnMmaWarp + 1) && rank == 0) {
     // ------------------------------------------------------------------ MMA issuer of stream t (leader only)
