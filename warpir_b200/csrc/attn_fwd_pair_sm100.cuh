@@ -3,14 +3,15 @@
 // Same algorithm, roles and tensor-memory layout as attn_fwd_sm100.cuh (two 128-row Q tiles
 // per CTA, one softmax warpgroup per tile, 64-key K/V blocks, double-buffered scores, P fed
 // to the second MMA from tensor memory, lazy rescale).  What changes is who issues the MMAs
-// and what one instruction covers.  The tensor core retires one 128 x 64 x 16 MMA per ~70
-// clocks and one 128 x 128 x 16 MMA per ~100, whatever else the SM does, which caps the
-// single-CTA kernel near half of peak.  Here the two CTAs of a cluster form a pair
-// (tcgen05 cta_group::2): tile t of the leader and tile t of its peer are the two halves of
-// ONE 256-row MMA stream, issued by the leader's MMA warp t for both.  Each SM thus retires
-// half as many instructions per block of keys, and each CTA loads only half of every K/V
-// block (the B operand of a pair-MMA is split between the two shared memories: 32 of the
-// 64 keys of a K block, 64 of the 128 columns of a V block).
+// and what one instruction covers: the two CTAs of a cluster form a pair (tcgen05
+// cta_group::2), tile t of the leader and tile t of its peer are the two halves of ONE
+// 256-row MMA stream issued by the leader's MMA warp t for both, and each CTA loads only
+// half of every K/V block (the B operand of a pair-MMA is split between the two shared
+// memories: 32 of the 64 keys of a K block, 64 of the 128 columns of a V block).
+// Measured, this is slower than the single-CTA kernel (830 vs 1137 TFLOP/s on the non-causal
+// benchmark shape): shared-memory traffic was not the limit, each SM's tensor core still
+// works through as many instructions per block, and every completion is committed twice.
+// The kernel is kept, selectable and tested, as the worked example of the pair protocol.
 //
 // Q tiles of a cluster c: CTA r holds tiles 4c + r and 4c + 2 + r; stream t = tiles
 // (4c + 2t, 4c + 2t + 1).  With a causal mask a stream runs as many K/V blocks as its later
