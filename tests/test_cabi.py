@@ -52,3 +52,20 @@ def test_runtime_wrappers_refuse_cpu_tensors():
         runtime.launch_gemm(a, a, a)
     with pytest.raises(ValueError, match="CUDA"):
         runtime.launch_attention(a, a, a, a)
+
+
+def test_header_and_library_from_plain_c(tmp_path):
+    """`include/warpir_b200.h` compiles as C, the library links from a C program, and argument
+    checks answer without a GPU (`tests/host/cabi_c_check.c`)."""
+    import subprocess
+    from pathlib import Path
+    from warpir_b200 import build as wb
+    root = Path(__file__).resolve().parent.parent
+    lib = wb.build_library()
+    exe = tmp_path / "cabi_c_check"
+    cmd = ["gcc", "-std=c99", "-Wall", "-Werror", "-I", str(root / "include"), str(root / "tests" / "host" / "cabi_c_check.c"),
+           "-o", str(exe), "-L", str(lib.parent), "-lwarpir_b200", f"-Wl,-rpath,{lib.parent}"]
+    proc = subprocess.run(cmd, capture_output=True, text=True)
+    assert proc.returncode == 0, proc.stdout + proc.stderr
+    run = subprocess.run([str(exe)], capture_output=True, text=True)
+    assert run.returncode == 0 and run.stdout.strip().endswith("ok"), run.stdout + run.stderr
