@@ -157,7 +157,8 @@ int warpir_attn_fwd_bf16(const void* Q, const void* K, const void* V, void* O, f
  * kernel with one softmax warpgroup per 128-row Q tile (the default), 2 the CTA-pair kernel
  * (clusters of two CTAs whose tensor cores share 256-row MMAs; head dimension 128 only), 3 the
  * single-CTA kernel with two softmax warpgroups per Q tile (each takes half of the score
- * columns).  Results agree to rounding.
+ * columns), 4 the single-CTA kernel with 128-key blocks (one score tile per Q tile, the two
+ * Q tiles of a CTA taking turns on the tensor core).  Results agree to rounding.
  * No counterpart in the reference; exists for tests and tuning.
  */
 int warpir_attn_fwd_bf16_ex(const void* Q, const void* K, const void* V, void* O, float* LSE,

@@ -54,7 +54,7 @@ def test_ragged_lengths(S, D, causal, lib):
     check(O, L, *R.attention_ref(Q, K, V, None, causal))
 
 
-@pytest.mark.parametrize("variant", [1, 2, 3])
+@pytest.mark.parametrize("variant", [1, 2, 3, 4])
 @pytest.mark.parametrize("causal", [False, True])
 @pytest.mark.parametrize("S", [1, 129, 512, 700, 1100, 2048])
 def test_every_kernel_variant_at_d128(S, causal, variant, lib):
@@ -66,7 +66,7 @@ def test_every_kernel_variant_at_d128(S, causal, variant, lib):
     check(O, L, *R.attention_ref(Q, K, V, None, causal))
 
 
-@pytest.mark.parametrize("variant", [1, 2, 3])
+@pytest.mark.parametrize("variant", [1, 2, 3, 4])
 def test_rescale_path_in_every_variant(variant, lib):
     Q, K, V = R.attention_inputs(1, 2, 1024, 128, seed=2)
     ramp = torch.linspace(0.2, 6.0, 1024).view(1, 1, 1024, 1)
@@ -75,7 +75,7 @@ def test_rescale_path_in_every_variant(variant, lib):
     check(O, L, *R.attention_ref(Q, K, V, None, True))
 
 
-@pytest.mark.parametrize("variant", [1, 3])
+@pytest.mark.parametrize("variant", [1, 3, 4])
 @pytest.mark.parametrize("causal", [False, True])
 @pytest.mark.parametrize("S", [1, 100, 384, 1000, 2048])
 def test_kernel_variants_at_d64(S, causal, variant, lib):
@@ -95,7 +95,7 @@ def test_variant_rejections(lib):
     with pytest.raises(runtime.WarpirError):
         runtime.launch_attention(Q, K, V, O, None, None, False, 2)     # pairs exist for D = 128 only
     with pytest.raises(runtime.WarpirError):
-        runtime.launch_attention(Q, K, V, O, None, None, False, 4)
+        runtime.launch_attention(Q, K, V, O, None, None, False, 5)
 
 
 def test_grouped_kv_heads_and_custom_scale(lib):

@@ -1,0 +1,417 @@
+// Attention forward with 128-key blocks: variant 4 of warpir_attn_fwd_bf16_ex.
+//
+// The default kernel (attn_fwd_sm100.cuh) works in 64-key blocks with double-buffered scores.
+// Measured there: at head dimension 128 a step is the time the tensor core needs to retire
+// its MMAs, and a 128 x 64 x 16 MMA costs ~71 clocks against ~100 for a 128 x 128 x 16 one;
+// at head dimension 64 a step is ~1900 clocks of fixed round trips of the softmax warps per
+// block, whatever their arithmetic.  Both halve per key with 128-key blocks.  Tensor memory
+// then holds exactly one score tile and one accumulator per Q tile (2 x 128 + 2 x D columns),
+// so Q K^T of the next block cannot run ahead of the softmax of this one; the overlap comes
+// from the two Q tiles of the CTA taking turns on the tensor core (while tile 0 is in its
+// softmax, tile 1's P V and next Q K^T run) and from two softmax warpgroups per tile, each
+// with 64 of the 128 score columns and half of the O columns.
+//
+//   warps 0-7 / 8-15   softmax of tile 0 / 1; within a tile warps 0-3 take columns 0-63,
+//                      warps 4-7 columns 64-127 (thread = row = tensor-memory lane)
+//   warps 16, 17       MMA issuers of tile 0 / 1
+//   warp 18            producer (Q once, then K(j), V(j) tiles of 128 keys into a ring)
+//
+// P (bf16, two values per column) overwrites the scores it came from: a thread reloads its 64
+// scores in two chunks of 32 for the exponentials and writes each packed chunk over columns
+// it has already consumed (columns 0-31 for the first half, 64-95 for the second), so neither
+// half touches columns the other still reads.  MMAs execute in issue order, so the next
+// Q K^T, issued right after P V, overwrites S only once P has been read.
+//
+// Measured on a B200 (bf16, TFLOP/s, this kernel against the default): B16 H16 S4096 D128
+// 1049 vs 1144; causal B4 H32 S8192 D128 897 vs 1134 (a 128-key diagonal block masks twice as
+// many scores); D64 554 vs 582 and 511 vs 562.  A step of both tiles takes ~4330 clocks against
+// 3200 of tensor-core work: with one score buffer per tile a tile's chain softmax -> P V ->
+// next Q K^T -> softmax is serial, and the softmax leg (~2100 clocks with its round trips) is
+// longer than the other tile's 1600 clocks of MMAs that should hide it.  So the default kernel
+// stays the default; this one is kept as a checked alternative.
+#pragma once
+
+#include "attn_fwd_sm100.cuh"
+
+namespace wir {
+
+constexpr int kWideThreads = 608;   // 16 softmax warps, 2 MMA warps, 1 producer warp
+constexpr int kWideMmaWarp = 16;
+constexpr int kWideBKV = 128;       // keys per block
+
+template <int D>
+struct AttnWideSmem {
+  static constexpr int kChunkBytes = 128 * 128;                  // 128 rows x 64 bf16 (Q, K and V tiles alike)
+  static constexpr int kTileBytes = (D / 64) * kChunkBytes;
+  static constexpr int kStages = (D == 128) ? 4 : 8;             // K and V tiles alternate in the ring
+  static constexpr int kQOffset = 0;
+  static constexpr int kKVOffset = 2 * kTileBytes;
+  static constexpr int kBarOffset = kKVOffset + kStages * kTileBytes;
+  // q_full, kv_full[S], kv_empty[S], s_full[2], p_full[2], pv_done[2], drain[2]
+  static constexpr int kNumBars = 1 + 2 * kStages + 8;
+  static constexpr int kTmemPtrOffset = kBarOffset + kNumBars * 8;
+  static constexpr int kAbortOffset = kTmemPtrOffset + 4;
+  static constexpr int kExchangeOffset = (kAbortOffset + 4 + 15) & ~15;   // [parity][tile][half][row] floats
+  static constexpr int kBytes = kExchangeOffset + 2 * 2 * 2 * kAttnBQ * 4;
+  static constexpr int kDynamicBytes = kBytes + 1024;
+};
+
+template <int D, bool CAUSAL>
+__global__ void __launch_bounds__(kWideThreads, 1)
+attn_fwd_wide_sm100(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                    const __grid_constant__ CUtensorMap tmap_v, const AttnParams p) {
+  using L = AttnWideSmem<D>;
+  constexpr int STAGES = L::kStages;
+  constexpr uint32_t kTmemCols = 512;
+  constexpr uint32_t kOCol = 256;        // O_t at columns 256 + t*D; S_t at t*128
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const uint32_t smem_base = smem_u32(smem);
+  const uint32_t bar_base = smem_base + L::kBarOffset;
+  const uint32_t q_full = bar_base;
+  auto kv_full = [&](int s) { return bar_base + 8u * (1 + s); };
+  auto kv_empty = [&](int s) { return bar_base + 8u * (1 + STAGES + s); };
+  auto s_full = [&](int t) { return bar_base + 8u * (1 + 2 * STAGES + t); };
+  auto p_full = [&](int t) { return bar_base + 8u * (3 + 2 * STAGES + t); };
+  auto pv_done = [&](int t) { return bar_base + 8u * (5 + 2 * STAGES + t); };
+  const uint32_t drain_bar = bar_base + 8u * (7 + 2 * STAGES);
+  volatile uint32_t* tmem_ptr_slot = reinterpret_cast<volatile uint32_t*>(smem + L::kTmemPtrOffset);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kAbortOffset);
+  const AbortCtx ctx{abort_flag, p.status};
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  // ---- which rows / how many K/V blocks ------------------------------------------------
+  const int pair = CAUSAL ? (gridDim.x - 1 - blockIdx.x) : blockIdx.x;  // heaviest causal tiles first
+  const int head = blockIdx.y, batch = blockIdx.z;
+  const int bh = batch * p.H + head;
+  const int bh_kv = batch * p.Hkv + head / (p.H / p.Hkv);
+  const int nkv = (p.S + kWideBKV - 1) / kWideBKV;
+  const int qt0 = 2 * pair, qt1 = 2 * pair + 1;
+  const int n0 = (qt0 * kAttnBQ >= p.S) ? 0 : (CAUSAL ? min(nkv, qt0 + 1) : nkv);
+  const int n1 = (qt1 * kAttnBQ >= p.S) ? 0 : (CAUSAL ? min(nkv, qt1 + 1) : nkv);
+  const int n_max = max(n0, n1);
+  // ring positions: K(j) at 2j, V(j) at 2j + 1
+
+  // Producer state (one lane of the producer warp, which also initialises the barriers and issues
+  // Q and K(0) before the CTA-wide barrier).
+  uint32_t p_idx = 0;
+  auto load_tile = [&](const CUtensorMap* map, int j) -> bool {
+    const int s = p_idx % STAGES;
+    const uint32_t ph = (p_idx / STAGES) & 1;
+    if (!mbar_wait(kv_empty(s), ph ^ 1, ctx, kRoleProducer, s, j)) return false;
+    mbar_arrive_expect_tx(kv_full(s), L::kTileBytes);
+    const uint32_t dst = smem_base + L::kKVOffset + s * L::kTileBytes;
+#pragma unroll
+    for (int c = 0; c < D / 64; ++c)
+      tma_load_3d(dst + c * L::kChunkBytes, map, kv_full(s), c * 64, j * kWideBKV, bh_kv);
+    ++p_idx;
+    return true;
+  };
+  bool p_ok = true;
+
+  if (threadIdx.x == (kWideMmaWarp + 2) * 32) {
+    *abort_flag = 0;
+    mbar_init(q_full, 1);
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(kv_full(s), 1);
+      mbar_init(kv_empty(s), 2);   // one arrival per MMA issuer
+    }
+    for (int t = 0; t < 2; ++t) {
+      mbar_init(s_full(t), 1);
+      mbar_init(p_full(t), 256);   // both column halves of the tile
+      mbar_init(pv_done(t), 1);
+    }
+    mbar_init(drain_bar, 1);
+    mbar_init(drain_bar + 8u, 1);
+    fence_mbar_init();
+    fence_proxy_async_smem();
+    const int n_q = (n0 > 0) + (n1 > 0);
+    mbar_arrive_expect_tx(q_full, n_q * L::kTileBytes);
+    for (int t = 0; t < 2; ++t)
+      if ((t == 0 ? n0 : n1) > 0)
+#pragma unroll
+        for (int c = 0; c < D / 64; ++c)
+          tma_load_3d(smem_base + L::kQOffset + t * L::kTileBytes + c * L::kChunkBytes, &tmap_q, q_full, c * 64,
+                      (2 * pair + t) * kAttnBQ, bh);
+    if (n_max > 0) p_ok = load_tile(&tmap_k, 0);
+  }
+  if (warp == kWideMmaWarp) {
+    tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_ptr_slot)), kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_ptr_slot;
+
+  if (warp == kWideMmaWarp + 2) {
+    // ------------------------------------------------------------------ producer
+    if (lane == 0) {
+      bool ok = p_ok;
+      // K(0) went out before the barrier; then V(j), K(j+1): the order in which the MMA warps consume them
+      for (int j = 0; ok && j < n_max; ++j) {
+        ok = load_tile(&tmap_v, j);
+        if (ok && j + 1 < n_max) ok = load_tile(&tmap_k, j + 1);
+      }
+      if (!ok || *abort_flag) {
+        mbar_wait_quiet(q_full, 0);
+        const uint32_t n = p_idx < STAGES ? p_idx : STAGES;
+        for (uint32_t back = 1; back <= n; ++back) {
+          const uint32_t i = p_idx - back;
+          mbar_wait_quiet(kv_full(i % STAGES), (i / STAGES) & 1);
+        }
+      }
+    }
+  } else if (warp == kWideMmaWarp || warp == kWideMmaWarp + 1) {
+    // ------------------------------------------------------------------ MMA issuer of one Q tile
+    // The whole warp runs the loop (warp-uniform operands), one elected lane issues.
+    const int t = warp - kWideMmaWarp;
+    const int n = (t == 0) ? n0 : n1;
+    constexpr uint32_t idesc_qk = idesc_bf16_f32(kAttnBQ, kWideBKV, 0, 0);
+    constexpr uint32_t idesc_pv = idesc_bf16_f32(kAttnBQ, D, 0, 1);
+    constexpr uint32_t desc_hi = smem_desc_hi_sw128(1024);
+    const uint32_t q_lo = smem_desc_lo(smem_base + L::kQOffset + t * L::kTileBytes, 16);
+    const uint32_t s_tmem = tmem_base + t * 128;
+    const uint32_t o_tmem = tmem_base + kOCol + t * D;
+    bool ok = true;
+    auto kv_addr = [&](uint32_t idx) { return smem_base + L::kKVOffset + (idx % STAGES) * L::kTileBytes; };
+    auto wait_kv = [&](uint32_t idx, int tag) {
+      return mbar_wait_warp(kv_full(idx % STAGES), (idx / STAGES) & 1, ctx, kRoleMma, tag, idx);
+    };
+    // every ring slot is released by BOTH issuers; the one whose tile does not visit a block
+    // releases it once the block has landed
+    auto skip_tile = [&](uint32_t idx) -> bool {
+      if (!wait_kv(idx, 40 + t)) return false;
+      mbar_arrive_elect(kv_empty(idx % STAGES));
+      return true;
+    };
+    // S_t = Q_t K(j)^T: D/16 MMAs of 128 x 128 x 16
+    auto issue_qk = [&](int j) -> bool {
+      const uint32_t idx = 2u * j;
+      if (!wait_kv(idx, 10 + t)) return false;
+      tc_fence_after();
+      const uint32_t k_lo = smem_desc_lo(kv_addr(idx), 16);
+#pragma unroll
+      for (int k = 0; k < D / 16; ++k) {
+        // 16 elements of the head dimension further: 32 bytes inside a 64-element chunk, then the next chunk
+        const uint32_t off = ((k / 4) * L::kChunkBytes + (k % 4) * 32) >> 4;
+        mma_ss_elect(s_tmem, q_lo + off, desc_hi, k_lo + off, desc_hi, idesc_qk, k > 0 ? 1u : 0u);
+      }
+      mma_commit_elect(s_full(t));
+      mma_commit_elect(kv_empty(idx % STAGES));
+      return true;
+    };
+
+    if (n > 0) ok = mbar_wait_warp(q_full, 0, ctx, kRoleMma, 1, 0);
+    if (ok && n_max > 0) ok = (0 < n) ? issue_qk(0) : skip_tile(0);
+
+    for (int j = 0; ok && j < n_max; ++j) {
+      const uint32_t idx = 2u * j + 1;
+      if (j < n) {
+        // O_t += P_t(j) V(j): 8 MMAs of 128 x D x 16, P from tensor memory
+        if (!mbar_wait_warp(p_full(t), j & 1, ctx, kRoleMma, 20 + t, j)) { ok = false; break; }
+        if (!wait_kv(idx, 30 + t)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t v_lo = smem_desc_lo(kv_addr(idx), L::kChunkBytes);
+#pragma unroll
+        for (int k = 0; k < kWideBKV / 16; ++k) {
+          // 16 keys further: 8 packed columns of P (the two halves' P sit at columns 0-31 and 64-95
+          // of the score tile), 16 rows (2048 bytes) of V
+          const uint32_t p_tmem = s_tmem + (k < 4 ? k * 8 : 64 + (k - 4) * 8);
+          mma_ts_elect(o_tmem, p_tmem, v_lo + ((k * 2048) >> 4), desc_hi, idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
+        }
+        mma_commit_elect(pv_done(t));
+        mma_commit_elect(kv_empty(idx % STAGES));
+      } else {
+        ok = skip_tile(idx);
+      }
+      // the next scores overwrite S_t (and P inside it): in issue order behind P V, which reads P
+      if (ok && j + 1 < n_max) ok = (j + 1 < n) ? issue_qk(j + 1) : skip_tile(2u * (j + 1));
+    }
+    if (!ok || *abort_flag) {
+      mma_commit_elect(drain_bar + 8u * t);
+      mbar_wait_quiet(drain_bar + 8u * t, 0);
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------------------------------------------ softmax + epilogue
+    const int t = warp >> 3;                 // which Q tile
+    const int half = (warp >> 2) & 1;        // which 64 of the 128 columns
+    const int quarter = warp & 3;            // tensor-memory lanes 32*quarter .. +31
+    const int r_in = quarter * 32 + lane;    // row inside the tile
+    const int qt = 2 * pair + t;
+    const int q_row = qt * kAttnBQ + r_in;
+    const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+    const uint32_t s_addr = lane_base + t * 128 + half * 64;                 // this half's 64 score columns
+    const uint32_t o_addr = lane_base + kOCol + t * D + half * (D / 2);      // this half's columns of O_t
+    const float c = p.scale_log2;
+    const int n = (t == 0) ? n0 : n1;
+    const int first_masked = CAUSAL ? qt : (p.S % kWideBKV != 0 ? nkv - 1 : nkv);
+    float* xch = reinterpret_cast<float*>(smem + L::kExchangeOffset);
+    auto xslot = [&](int par, int h) { return xch + ((par * 2 + t) * 2 + h) * kAttnBQ + r_in; };
+    // tile-wide vote (the 256 threads of a tile meet at named barriers, so they must agree on going on)
+    auto vote = [&](bool mine) -> bool {
+      uint32_t all;
+      asm volatile(
+          "{\n\t.reg .pred a, q;\n\t"
+          "setp.ne.u32 q, %1, 0;\n\t"
+          "bar.red.and.pred a, %2, 256, q;\n\t"
+          "selp.u32 %0, 1, 0, a;\n\t}"
+          : "=r"(all)
+          : "r"(mine ? 1u : 0u), "r"(1 + t)
+          : "memory");
+      return all != 0;
+    };
+
+    float m = -INFINITY;  // running (possibly stale) max of the raw scores, identical in both halves
+    float l = 0.f;        // this half's share of the running sum of 2^(s c - m c)
+    bool ok = true;
+    bool bad = false;     // a wait inside a per-warp branch ran out: carried to the next tile-wide vote
+
+    for (int j = 0; j < n; ++j) {
+      const bool got = mbar_wait(s_full(t), j & 1, ctx, kRoleSoftmax, t, j) && !bad;
+      if (!vote(got)) { ok = false; break; }
+      tc_fence_after();
+      if (j == 0 && t == 1 && p.stagger_clocks > 0) {
+        const long long t0 = clock64();
+        while (clock64() - t0 < p.stagger_clocks) {
+        }
+      }
+      const bool masked = (j >= first_masked) || (j == nkv - 1 && p.S % kWideBKV != 0);
+      const int limit = CAUSAL ? min(q_row, p.S - 1) : (p.S - 1);   // last visible key
+      const int k_first = j * kWideBKV + half * 64;
+
+      // pass 1: row max over this half's 64 columns, 32 at a time
+      float mine = -INFINITY;
+#pragma unroll
+      for (int ch = 0; ch < 2; ++ch) {
+        uint32_t sb[32];
+        tmem_ld32(s_addr + ch * 32, sb);
+        tmem_wait_ld();
+        if (masked) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (k_first + ch * 32 + i > limit) sb[i] = 0xff800000u;  // -inf
+        }
+        float mx0 = __uint_as_float(sb[0]), mx1 = __uint_as_float(sb[1]);
+        float mx2 = __uint_as_float(sb[2]), mx3 = __uint_as_float(sb[3]);
+#pragma unroll
+        for (int i = 4; i < 32; i += 4) {
+          mx0 = fmaxf(mx0, __uint_as_float(sb[i]));
+          mx1 = fmaxf(mx1, __uint_as_float(sb[i + 1]));
+          mx2 = fmaxf(mx2, __uint_as_float(sb[i + 2]));
+          mx3 = fmaxf(mx3, __uint_as_float(sb[i + 3]));
+        }
+        mine = fmaxf(mine, fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)));
+      }
+      *xslot(j & 1, half) = mine;
+      asm volatile("bar.sync %0, 256;" ::"r"(3 + t) : "memory");
+      const float m_new = fmaxf(m, fmaxf(mine, *xslot(j & 1, half ^ 1)));
+      // identical in the partner warp (same rows, same combined max), so both halves rescale together
+      const bool grow = (m_new - m) * c > kRescaleThreshold;
+      if (__any_sync(0xffffffffu, grow)) {
+        if (j > 0) {
+          const bool done = mbar_wait(pv_done(t), (j - 1) & 1, ctx, kRoleSoftmax, 8 + t, j);
+          if (!__all_sync(0xffffffffu, done)) {
+            bad = true;   // no early exit here: the other warps of the tile are heading for a barrier
+          } else {
+            tc_fence_after();
+            const float alpha = ex2_approx((m - m_new) * c);
+            l *= alpha;
+#pragma unroll 1
+            for (int cidx = 0; cidx < D / 64; ++cidx) {   // this half's D/2 columns of O
+              uint32_t o[32];
+              tmem_ld32(o_addr + cidx * 32, o);
+              tmem_wait_ld();
+#pragma unroll
+              for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+              tmem_st32(o_addr + cidx * 32, o);
+            }
+          }
+        }
+        m = m_new;
+      }
+
+      // pass 2: exponentials, 32 columns at a time; each packed chunk (16 columns) goes over score
+      // columns this thread has already consumed
+      const float neg_mc = -m * c;
+      const float2 c2 = make_float2(c, c), neg_mc2 = make_float2(neg_mc, neg_mc);
+      float2 la = make_float2(0.f, 0.f), lb = make_float2(0.f, 0.f);
+#pragma unroll
+      for (int ch = 0; ch < 2; ++ch) {
+        uint32_t sb[32];
+        tmem_ld32(s_addr + ch * 32, sb);
+        tmem_wait_ld();
+        if (masked) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (k_first + ch * 32 + i > limit) sb[i] = 0xff800000u;
+        }
+        uint32_t pk[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const float2 x = __ffma2_rn(make_float2(__uint_as_float(sb[2 * i]), __uint_as_float(sb[2 * i + 1])), c2, neg_mc2);
+          float2 e;
+          if ((i & 3) == 3) {
+            e = ex2_fma2(x);
+          } else {
+            e.x = ex2_approx(x.x);
+            e.y = ex2_approx(x.y);
+          }
+          if (i & 1) lb = __fadd2_rn(lb, e);
+          else la = __fadd2_rn(la, e);
+          pk[i] = pack_bf16(e.x, e.y);
+        }
+        tmem_st16(s_addr + ch * 16, pk);   // half 0: columns 0-31 of S_t, half 1: columns 64-95
+      }
+      l += (la.x + lb.x) + (la.y + lb.y);
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(p_full(t));
+    }
+
+    if (ok && n > 0) {
+      const bool got = mbar_wait(pv_done(t), (n - 1) & 1, ctx, kRoleEpilogue, t, n) && !bad;
+      if (vote(got)) {
+        tc_fence_after();
+        *xslot(n & 1, half) = l;   // the two halves' shares of the row sum
+        asm volatile("bar.sync %0, 256;" ::"r"(3 + t) : "memory");
+        const float l_all = l + *xslot(n & 1, half ^ 1);
+        const float inv_l = 1.0f / l_all;
+        const bool live = q_row < p.S;
+        __nv_bfloat16* dst = p.O + (static_cast<size_t>(bh) * p.S + (live ? q_row : 0)) * D + half * (D / 2);
+#pragma unroll 1
+        for (int cidx = 0; cidx < D / 64; ++cidx) {
+          uint32_t o[32];
+          tmem_ld32(o_addr + cidx * 32, o);
+          tmem_wait_ld();
+          if (live) {
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              uint4 q;
+              q.x = pack_bf16(__uint_as_float(o[8 * v + 0]) * inv_l, __uint_as_float(o[8 * v + 1]) * inv_l);
+              q.y = pack_bf16(__uint_as_float(o[8 * v + 2]) * inv_l, __uint_as_float(o[8 * v + 3]) * inv_l);
+              q.z = pack_bf16(__uint_as_float(o[8 * v + 4]) * inv_l, __uint_as_float(o[8 * v + 5]) * inv_l);
+              q.w = pack_bf16(__uint_as_float(o[8 * v + 6]) * inv_l, __uint_as_float(o[8 * v + 7]) * inv_l);
+              reinterpret_cast<uint4*>(dst + cidx * 32)[v] = q;
+            }
+          }
+        }
+        if (live && half == 0 && p.LSE != nullptr)
+          p.LSE[static_cast<size_t>(bh) * p.S + q_row] = m * c * 0.6931471805599453f + logf(l_all);
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == kWideMmaWarp) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+}  // namespace wir

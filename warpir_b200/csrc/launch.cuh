@@ -9,6 +9,7 @@
 #include "attn_fwd_sm100.cuh"
 #include "attn_fwd_pair_sm100.cuh"
 #include "attn_fwd_split_sm100.cuh"
+#include "attn_fwd_wide_sm100.cuh"
 #include "gemm_sm100.cuh"
 
 namespace wir {
@@ -300,6 +301,22 @@ int launch_attn_split_cfg(const CUtensorMap& tq, const CUtensorMap& tk, const CU
   return WARPIR_OK;
 }
 
+// 128-key blocks, two Q tiles taking turns on the tensor core (attn_fwd_wide_sm100.cuh).
+template <int D, bool CAUSAL>
+int launch_attn_wide_cfg(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const wir::AttnParams& p,
+                         cudaStream_t stream) {
+  auto kernel = wir::attn_fwd_wide_sm100<D, CAUSAL>;
+  constexpr int smem = wir::AttnWideSmem<D>::kDynamicBytes;
+  static_assert(smem <= 232448, "shared memory limit per CTA");
+  static_assert(smem > 116 * 1024, "one CTA per SM is what keeps the tensor-memory allocation from blocking");
+  if (int rc = opt_in_smem(reinterpret_cast<const void*>(kernel), smem)) return rc;
+  const int pairs = (p.S + 2 * wir::kAttnBQ - 1) / (2 * wir::kAttnBQ);
+  dim3 grid(pairs, p.H, p.B);
+  kernel<<<grid, wir::kWideThreads, smem, stream>>>(tq, tk, tv, p);
+  WIR_CUDA(cudaGetLastError());
+  return WARPIR_OK;
+}
+
 // Head dimension 128 on CTA pairs (attn_fwd_pair_sm100.cuh): clusters of two CTAs, four Q tiles each.
 template <bool CAUSAL>
 int launch_attn_pair_cfg(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const wir::AttnParams& p,
@@ -331,8 +348,8 @@ inline int attn_impl(const void* Q, const void* K, const void* V, void* O, float
   g_last_error[0] = 0;
   if (B < 0 || Hq < 0 || Hkv < 0 || S < 0) return fail(WARPIR_EINVAL, "negative size");
   if (D != 64 && D != 128) return fail(WARPIR_ESHAPE, "D = %lld: head dimension must be 64 or 128", (long long)D);
-  if (variant < 0 || variant > 3)
-    return fail(WARPIR_EINVAL, "variant must be 0 (choose), 1 (one softmax warpgroup per tile), 2 (CTA pairs) or 3 (two softmax warpgroups per tile)");
+  if (variant < 0 || variant > 4)
+    return fail(WARPIR_EINVAL, "variant must be 0 (choose), 1 (one softmax warpgroup per tile), 2 (CTA pairs), 3 (two softmax warpgroups per tile) or 4 (128-key blocks)");
   if (variant == 2 && D != 128) return fail(WARPIR_ESHAPE, "the CTA-pair kernel covers head dimension 128 only");
   if (B == 0 || Hq == 0 || S == 0) return WARPIR_OK;
   if (Hkv <= 0 || Hq % Hkv != 0) return fail(WARPIR_ESHAPE, "Hq = %lld must be a positive multiple of Hkv = %lld", (long long)Hq, (long long)Hkv);
@@ -387,6 +404,18 @@ inline int attn_impl(const void* Q, const void* K, const void* V, void* O, float
     const uint32_t box_k[3] = {64, 32, 1};
     if (int rc = make_tmap(&tk_half, K, 3, dims, strides, box_k)) return rc;
     return causal ? launch_attn_pair_cfg<true>(tq, tk_half, tv, p, stream) : launch_attn_pair_cfg<false>(tq, tk_half, tv, p, stream);
+  }
+  bool wide = false;
+  if (const char* e = getenv("WARPIR_ATTN_WIDE")) wide = atoi(e) != 0;
+  if (variant != 0) wide = (variant == 4);
+  if (wide) {
+    CUtensorMap tk128, tv128;   // K and V in tiles of 128 keys
+    const uint64_t dims[3] = {static_cast<uint64_t>(D), static_cast<uint64_t>(S), static_cast<uint64_t>(B * Hkv)};
+    const uint64_t strides[2] = {static_cast<uint64_t>(D) * 2, static_cast<uint64_t>(S) * D * 2};
+    if (int rc = make_tmap(&tk128, K, 3, dims, strides, box)) return rc;
+    if (int rc = make_tmap(&tv128, V, 3, dims, strides, box)) return rc;
+    if (D == 128) return causal ? launch_attn_wide_cfg<128, true>(tq, tk128, tv128, p, stream) : launch_attn_wide_cfg<128, false>(tq, tk128, tv128, p, stream);
+    return causal ? launch_attn_wide_cfg<64, true>(tq, tk128, tv128, p, stream) : launch_attn_wide_cfg<64, false>(tq, tk128, tv128, p, stream);
   }
   bool split = false;
   if (const char* e = getenv("WARPIR_ATTN_SPLIT")) split = atoi(e) != 0;
