@@ -35,9 +35,11 @@
 
 namespace wir {
 
-constexpr int kWideThreads = 608;   // 16 softmax warps, 2 MMA warps, 1 producer warp
-constexpr int kWideMmaWarp = 16;
+constexpr int kWideThreads = 384;   // 8 softmax warps, 2 MMA warps, 1 producer warp, 1 idle warp (whole warpgroups)
+constexpr int kWideMmaWarp = 8;
 constexpr int kWideBKV = 128;       // keys per block
+constexpr float kRoundUpLog2 = 0.00281502f;    // log2(1 + 2^-9)
+constexpr float kRoundUpInv = 0.99805068f;     // 1 / (1 + 2^-9)
 
 template <int D>
 struct AttnWideSmem {
@@ -47,12 +49,11 @@ struct AttnWideSmem {
   static constexpr int kQOffset = 0;
   static constexpr int kKVOffset = 2 * kTileBytes;
   static constexpr int kBarOffset = kKVOffset + kStages * kTileBytes;
-  // q_full, kv_full[S], kv_empty[S], s_full[2], p_full[2], pv_done[2], drain[2]
-  static constexpr int kNumBars = 1 + 2 * kStages + 8;
+  // q_full, kv_full[S], kv_empty[S], s_full[2], p_half[2][2], pv_done[2], drain
+  static constexpr int kNumBars = 1 + 2 * kStages + 9;
   static constexpr int kTmemPtrOffset = kBarOffset + kNumBars * 8;
   static constexpr int kAbortOffset = kTmemPtrOffset + 4;
-  static constexpr int kExchangeOffset = (kAbortOffset + 4 + 15) & ~15;   // [parity][tile][half][row] floats
-  static constexpr int kBytes = kExchangeOffset + 2 * 2 * 2 * kAttnBQ * 4;
+  static constexpr int kBytes = kAbortOffset + 4;
   static constexpr int kDynamicBytes = kBytes + 1024;
 };
 
@@ -73,9 +74,9 @@ attn_fwd_wide_sm100(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
   auto kv_full = [&](int s) { return bar_base + 8u * (1 + s); };
   auto kv_empty = [&](int s) { return bar_base + 8u * (1 + STAGES + s); };
   auto s_full = [&](int t) { return bar_base + 8u * (1 + 2 * STAGES + t); };
-  auto p_full = [&](int t) { return bar_base + 8u * (3 + 2 * STAGES + t); };
-  auto pv_done = [&](int t) { return bar_base + 8u * (5 + 2 * STAGES + t); };
-  const uint32_t drain_bar = bar_base + 8u * (7 + 2 * STAGES);
+  auto p_half = [&](int t, int h) { return bar_base + 8u * (3 + 2 * STAGES + 2 * t + h); };   // P of keys 64h .. 64h+63
+  auto pv_done = [&](int t) { return bar_base + 8u * (7 + 2 * STAGES + t); };
+  const uint32_t drain_bar = bar_base + 8u * (9 + 2 * STAGES);
   volatile uint32_t* tmem_ptr_slot = reinterpret_cast<volatile uint32_t*>(smem + L::kTmemPtrOffset);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kAbortOffset);
   const AbortCtx ctx{abort_flag, p.status};
@@ -117,15 +118,15 @@ attn_fwd_wide_sm100(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
     mbar_init(q_full, 1);
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(kv_full(s), 1);
-      mbar_init(kv_empty(s), 2);   // one arrival per MMA issuer
+      mbar_init(kv_empty(s), 1);
     }
     for (int t = 0; t < 2; ++t) {
       mbar_init(s_full(t), 1);
-      mbar_init(p_full(t), 256);   // both column halves of the tile
+      mbar_init(p_half(t, 0), 128);   // one arrival per row
+      mbar_init(p_half(t, 1), 128);
       mbar_init(pv_done(t), 1);
     }
     mbar_init(drain_bar, 1);
-    mbar_init(drain_bar + 8u, 1);
     fence_mbar_init();
     fence_proxy_async_smem();
     const int n_q = (n0 > 0) + (n1 > 0);
@@ -147,6 +148,10 @@ attn_fwd_wide_sm100(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
   tc_fence_after();
   const uint32_t tmem_base = *tmem_ptr_slot;
 
+  // Registers move from the warpgroup of the issuers and the producer to the softmax warpgroups,
+  // whose threads hold a whole row of 128 scores (168 each at launch: 3 x 128 x 168 = 2 x 128 x 200 + 128 x 104).
+  if (warp >= kWideMmaWarp) {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 104;");
   if (warp == kWideMmaWarp + 2) {
     // ------------------------------------------------------------------ producer
     if (lane == 0) {
@@ -165,35 +170,33 @@ attn_fwd_wide_sm100(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         }
       }
     }
-  } else if (warp == kWideMmaWarp || warp == kWideMmaWarp + 1) {
-    // ------------------------------------------------------------------ MMA issuer of one Q tile
-    // The whole warp runs the loop (warp-uniform operands), one elected lane issues.
-    const int t = warp - kWideMmaWarp;
-    const int n = (t == 0) ? n0 : n1;
+  } else if (warp == kWideMmaWarp) {
+    // ------------------------------------------------------------------ MMA issuer of both Q tiles
+    // The whole warp runs the loop (warp-uniform operands), one elected lane issues.  The tiles
+    // are served in strict alternation, each with its P V of this block and its Q K^T of the next
+    // as one batch: the tensor core then works through one tile's batch while the other tile is
+    // in its softmax, and the two settle half a period apart.  (Two independent issuers let the
+    // batches interleave in the tensor core's queue, which pulled the tiles into lockstep: both
+    // softmaxes ran at once at half speed, then both batches queued.)
     constexpr uint32_t idesc_qk = idesc_bf16_f32(kAttnBQ, kWideBKV, 0, 0);
     constexpr uint32_t idesc_pv = idesc_bf16_f32(kAttnBQ, D, 0, 1);
     constexpr uint32_t desc_hi = smem_desc_hi_sw128(1024);
-    const uint32_t q_lo = smem_desc_lo(smem_base + L::kQOffset + t * L::kTileBytes, 16);
-    const uint32_t s_tmem = tmem_base + t * 128;
-    const uint32_t o_tmem = tmem_base + kOCol + t * D;
     bool ok = true;
+    WIR_TRACE_DECL;
     auto kv_addr = [&](uint32_t idx) { return smem_base + L::kKVOffset + (idx % STAGES) * L::kTileBytes; };
     auto wait_kv = [&](uint32_t idx, int tag) {
       return mbar_wait_warp(kv_full(idx % STAGES), (idx / STAGES) & 1, ctx, kRoleMma, tag, idx);
     };
-    // every ring slot is released by BOTH issuers; the one whose tile does not visit a block
-    // releases it once the block has landed
-    auto skip_tile = [&](uint32_t idx) -> bool {
-      if (!wait_kv(idx, 40 + t)) return false;
-      mbar_arrive_elect(kv_empty(idx % STAGES));
-      return true;
-    };
+    // a ring slot goes back to the producer behind the MMAs of the last tile that reads it
+    auto last_user = [&](int j) { return j < n1 ? 1 : 0; };
     // S_t = Q_t K(j)^T: D/16 MMAs of 128 x 128 x 16
-    auto issue_qk = [&](int j) -> bool {
+    auto issue_qk = [&](int t, int j) -> bool {
       const uint32_t idx = 2u * j;
       if (!wait_kv(idx, 10 + t)) return false;
       tc_fence_after();
+      const uint32_t q_lo = smem_desc_lo(smem_base + L::kQOffset + t * L::kTileBytes, 16);
       const uint32_t k_lo = smem_desc_lo(kv_addr(idx), 16);
+      const uint32_t s_tmem = tmem_base + t * 128;
 #pragma unroll
       for (int k = 0; k < D / 16; ++k) {
         // 16 elements of the head dimension further: 32 bytes inside a 64-element chunk, then the next chunk
@@ -201,190 +204,176 @@ attn_fwd_wide_sm100(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         mma_ss_elect(s_tmem, q_lo + off, desc_hi, k_lo + off, desc_hi, idesc_qk, k > 0 ? 1u : 0u);
       }
       mma_commit_elect(s_full(t));
-      mma_commit_elect(kv_empty(idx % STAGES));
+      if (t == last_user(j)) mma_commit_elect(kv_empty(idx % STAGES));
+      return true;
+    };
+    // O_t += P_t(j) V(j): 8 MMAs of 128 x D x 16, P from tensor memory (columns 0-63 of the score tile)
+    auto issue_pv = [&](int t, int j) -> bool {
+      const uint32_t idx = 2u * j + 1;
+      if (lane == 0) WIR_TRACE_EVENT(p.trace, 0, 1 + 10 * t, j);
+      if (!mbar_wait_warp(p_half(t, 0), j & 1, ctx, kRoleMma, 20 + t, j)) return false;
+      if (lane == 0) WIR_TRACE_EVENT(p.trace, 0, 2 + 10 * t, j);
+      if (!wait_kv(idx, 30 + t)) return false;
+      tc_fence_after();
+      const uint32_t v_lo = smem_desc_lo(kv_addr(idx), L::kChunkBytes);
+      const uint32_t s_tmem = tmem_base + t * 128;
+      const uint32_t o_tmem = tmem_base + kOCol + t * D;
+#pragma unroll
+      for (int k = 0; k < kWideBKV / 16; ++k) {
+        // the second half of P arrives while the MMAs of the first run
+        if (k == kWideBKV / 32) {
+          if (!mbar_wait_warp(p_half(t, 1), j & 1, ctx, kRoleMma, 22 + t, j)) return false;
+          tc_fence_after();
+        }
+        // 16 keys further: 8 packed columns of P, 16 rows (2048 bytes) of V
+        mma_ts_elect(o_tmem, s_tmem + k * 8, v_lo + ((k * 2048) >> 4), desc_hi, idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
+      }
+      mma_commit_elect(pv_done(t));
+      if (t == last_user(j)) mma_commit_elect(kv_empty(idx % STAGES));
+      if (lane == 0) WIR_TRACE_EVENT(p.trace, 0, 3 + 10 * t, j);
       return true;
     };
 
-    if (n > 0) ok = mbar_wait_warp(q_full, 0, ctx, kRoleMma, 1, 0);
-    if (ok && n_max > 0) ok = (0 < n) ? issue_qk(0) : skip_tile(0);
-
+    if (n_max > 0) ok = mbar_wait_warp(q_full, 0, ctx, kRoleMma, 1, 0);
+    if (ok && n0 > 0) ok = issue_qk(0, 0);
+    if (ok && n1 > 0) ok = issue_qk(1, 0);
     for (int j = 0; ok && j < n_max; ++j) {
-      const uint32_t idx = 2u * j + 1;
-      if (j < n) {
-        // O_t += P_t(j) V(j): 8 MMAs of 128 x D x 16, P from tensor memory
-        if (!mbar_wait_warp(p_full(t), j & 1, ctx, kRoleMma, 20 + t, j)) { ok = false; break; }
-        if (!wait_kv(idx, 30 + t)) { ok = false; break; }
-        tc_fence_after();
-        const uint32_t v_lo = smem_desc_lo(kv_addr(idx), L::kChunkBytes);
 #pragma unroll
-        for (int k = 0; k < kWideBKV / 16; ++k) {
-          // 16 keys further: 8 packed columns of P (the two halves' P sit at columns 0-31 and 64-95
-          // of the score tile), 16 rows (2048 bytes) of V
-          const uint32_t p_tmem = s_tmem + (k < 4 ? k * 8 : 64 + (k - 4) * 8);
-          mma_ts_elect(o_tmem, p_tmem, v_lo + ((k * 2048) >> 4), desc_hi, idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
+      for (int t = 0; t < 2; ++t) {
+        const int n = (t == 0) ? n0 : n1;
+        if (ok && j < n) {
+          ok = issue_pv(t, j);
+          // the next scores overwrite S_t (and P inside it): in issue order behind P V, which reads P
+          if (ok && j + 1 < n) ok = issue_qk(t, j + 1);
+          if (lane == 0) WIR_TRACE_EVENT(p.trace, 0, 4 + 10 * t, j);
         }
-        mma_commit_elect(pv_done(t));
-        mma_commit_elect(kv_empty(idx % STAGES));
-      } else {
-        ok = skip_tile(idx);
       }
-      // the next scores overwrite S_t (and P inside it): in issue order behind P V, which reads P
-      if (ok && j + 1 < n_max) ok = (j + 1 < n) ? issue_qk(j + 1) : skip_tile(2u * (j + 1));
     }
     if (!ok || *abort_flag) {
-      mma_commit_elect(drain_bar + 8u * t);
-      mbar_wait_quiet(drain_bar + 8u * t, 0);
+      mma_commit_elect(drain_bar);
+      mbar_wait_quiet(drain_bar, 0);
     }
     __syncwarp();
+  }
   } else {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 200;");
     // ------------------------------------------------------------------ softmax + epilogue
-    const int t = warp >> 3;                 // which Q tile
-    const int half = (warp >> 2) & 1;        // which 64 of the 128 columns
-    const int quarter = warp & 3;            // tensor-memory lanes 32*quarter .. +31
-    const int r_in = quarter * 32 + lane;    // row inside the tile
+    const int t = warp >> 2;            // which Q tile
+    const int quarter = warp & 3;       // tensor-memory lanes 32*quarter .. +31
     const int qt = 2 * pair + t;
-    const int q_row = qt * kAttnBQ + r_in;
+    const int q_row = qt * kAttnBQ + quarter * 32 + lane;
     const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
-    const uint32_t s_addr = lane_base + t * 128 + half * 64;                 // this half's 64 score columns
-    const uint32_t o_addr = lane_base + kOCol + t * D + half * (D / 2);      // this half's columns of O_t
+    const uint32_t s_addr = lane_base + t * 128;
+    const uint32_t o_addr = lane_base + kOCol + t * D;
     const float c = p.scale_log2;
     const int n = (t == 0) ? n0 : n1;
     const int first_masked = CAUSAL ? qt : (p.S % kWideBKV != 0 ? nkv - 1 : nkv);
-    float* xch = reinterpret_cast<float*>(smem + L::kExchangeOffset);
-    auto xslot = [&](int par, int h) { return xch + ((par * 2 + t) * 2 + h) * kAttnBQ + r_in; };
-    // tile-wide vote (the 256 threads of a tile meet at named barriers, so they must agree on going on)
-    auto vote = [&](bool mine) -> bool {
-      uint32_t all;
-      asm volatile(
-          "{\n\t.reg .pred a, q;\n\t"
-          "setp.ne.u32 q, %1, 0;\n\t"
-          "bar.red.and.pred a, %2, 256, q;\n\t"
-          "selp.u32 %0, 1, 0, a;\n\t}"
-          : "=r"(all)
-          : "r"(mine ? 1u : 0u), "r"(1 + t)
-          : "memory");
-      return all != 0;
-    };
 
-    float m = -INFINITY;  // running (possibly stale) max of the raw scores, identical in both halves
-    float l = 0.f;        // this half's share of the running sum of 2^(s c - m c)
+    WIR_TRACE_DECL;
+    float m = -INFINITY;  // running (possibly stale) max of the raw scores
+    float l = 0.f;        // running sum of 2^(s c - m c)
     bool ok = true;
-    bool bad = false;     // a wait inside a per-warp branch ran out: carried to the next tile-wide vote
 
     for (int j = 0; j < n; ++j) {
-      const bool got = mbar_wait(s_full(t), j & 1, ctx, kRoleSoftmax, t, j) && !bad;
-      if (!vote(got)) { ok = false; break; }
+      if (quarter == 0 && lane == 0) WIR_TRACE_EVENT(p.trace, 1 + t, 100, j);
+      if (!mbar_wait_warp(s_full(t), j & 1, ctx, kRoleSoftmax, t, j)) { ok = false; break; }
       tc_fence_after();
-      if (j == 0 && t == 1 && p.stagger_clocks > 0) {
-        const long long t0 = clock64();
-        while (clock64() - t0 < p.stagger_clocks) {
-        }
-      }
-      const bool masked = (j >= first_masked) || (j == nkv - 1 && p.S % kWideBKV != 0);
-      const int limit = CAUSAL ? min(q_row, p.S - 1) : (p.S - 1);   // last visible key
-      const int k_first = j * kWideBKV + half * 64;
+      if (quarter == 0 && lane == 0) WIR_TRACE_EVENT(p.trace, 1 + t, 101, j);
 
-      // pass 1: row max over this half's 64 columns, 32 at a time
-      float mine = -INFINITY;
+      uint32_t sb[128];  // this thread's row of raw scores, as fp32 bit patterns
+      tmem_ld32(s_addr, sb);
+      tmem_ld32(s_addr + 32, sb + 32);
+      tmem_ld32(s_addr + 64, sb + 64);
+      tmem_ld32(s_addr + 96, sb + 96);
+      tmem_wait_ld();
+      if (quarter == 0 && lane == 0) WIR_TRACE_EVENT(p.trace, 1 + t, 102, j);
+#define WIR_S(i) __uint_as_float(sb[i])
+
+      if (j >= first_masked || (j == nkv - 1 && p.S % kWideBKV != 0)) {
+        const int k0 = j * kWideBKV;
+        const int limit = CAUSAL ? min(q_row, p.S - 1) : (p.S - 1);  // last visible key
 #pragma unroll
-      for (int ch = 0; ch < 2; ++ch) {
-        uint32_t sb[32];
-        tmem_ld32(s_addr + ch * 32, sb);
-        tmem_wait_ld();
-        if (masked) {
-#pragma unroll
-          for (int i = 0; i < 32; ++i)
-            if (k_first + ch * 32 + i > limit) sb[i] = 0xff800000u;  // -inf
-        }
-        float mx0 = __uint_as_float(sb[0]), mx1 = __uint_as_float(sb[1]);
-        float mx2 = __uint_as_float(sb[2]), mx3 = __uint_as_float(sb[3]);
-#pragma unroll
-        for (int i = 4; i < 32; i += 4) {
-          mx0 = fmaxf(mx0, __uint_as_float(sb[i]));
-          mx1 = fmaxf(mx1, __uint_as_float(sb[i + 1]));
-          mx2 = fmaxf(mx2, __uint_as_float(sb[i + 2]));
-          mx3 = fmaxf(mx3, __uint_as_float(sb[i + 3]));
-        }
-        mine = fmaxf(mine, fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)));
+        for (int i = 0; i < 128; ++i)
+          if (k0 + i > limit) sb[i] = 0xff800000u;  // -inf
       }
-      *xslot(j & 1, half) = mine;
-      asm volatile("bar.sync %0, 256;" ::"r"(3 + t) : "memory");
-      const float m_new = fmaxf(m, fmaxf(mine, *xslot(j & 1, half ^ 1)));
-      // identical in the partner warp (same rows, same combined max), so both halves rescale together
-      const bool grow = (m_new - m) * c > kRescaleThreshold;
+
+      // three-input max: 64 instructions for 128 scores, in four independent chains
+      float mx0 = fmaxf(WIR_S(0), WIR_S(1)), mx1 = fmaxf(WIR_S(2), WIR_S(3));
+      float mx2 = fmaxf(WIR_S(4), WIR_S(5)), mx3 = fmaxf(WIR_S(6), WIR_S(7));
+#pragma unroll
+      for (int i = 8; i < 128; i += 8) {
+        mx0 = fmax3(mx0, WIR_S(i), WIR_S(i + 1));
+        mx1 = fmax3(mx1, WIR_S(i + 2), WIR_S(i + 3));
+        mx2 = fmax3(mx2, WIR_S(i + 4), WIR_S(i + 5));
+        mx3 = fmax3(mx3, WIR_S(i + 6), WIR_S(i + 7));
+      }
+      const float m_new = fmax3(m, fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+      const bool grow = (m_new - m) * c > kRescaleThreshold;  // true on the first block (m = -inf)
       if (__any_sync(0xffffffffu, grow)) {
         if (j > 0) {
-          const bool done = mbar_wait(pv_done(t), (j - 1) & 1, ctx, kRoleSoftmax, 8 + t, j);
-          if (!__all_sync(0xffffffffu, done)) {
-            bad = true;   // no early exit here: the other warps of the tile are heading for a barrier
-          } else {
-            tc_fence_after();
-            const float alpha = ex2_approx((m - m_new) * c);
-            l *= alpha;
+          // O_t was accumulated into by P V(j-1), which ran ahead of the Q K^T these scores came from
+          if (!mbar_wait_warp(pv_done(t), (j - 1) & 1, ctx, kRoleSoftmax, 8 + t, j)) { ok = false; break; }
+          tc_fence_after();
+          const float alpha = ex2_approx((m - m_new) * c);
+          l *= alpha;
 #pragma unroll 1
-            for (int cidx = 0; cidx < D / 64; ++cidx) {   // this half's D/2 columns of O
-              uint32_t o[32];
-              tmem_ld32(o_addr + cidx * 32, o);
-              tmem_wait_ld();
+          for (int cidx = 0; cidx < D / 16; ++cidx) {   // 16 columns at a time: the scores stay in registers
+            uint32_t o[16];
+            tmem_ld16(o_addr + cidx * 16, o);
+            tmem_wait_ld();
 #pragma unroll
-              for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-              tmem_st32(o_addr + cidx * 32, o);
-            }
+            for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+            tmem_st16(o_addr + cidx * 16, o);
           }
         }
         m = m_new;
       }
 
-      // pass 2: exponentials, 32 columns at a time; each packed chunk (16 columns) goes over score
-      // columns this thread has already consumed
-      const float neg_mc = -m * c;
+      // P = 2^(s c - m c) is rounded to bf16 without the conversion unit: the exponent carries an
+      // extra log2(1 + 2^-9), after which keeping the high 16 bits (one byte permute per pair)
+      // rounds the true value to within half a unit in the last place, unbiased.  The row sum is taken
+      // over the same scaled values and divided by 1 + 2^-9 once at the end.
+      const float neg_mc = kRoundUpLog2 - m * c;
+      // packed f32x2 arithmetic; all exponentials on the exponential unit (a polynomial share on the
+      // FMA pipe, which pays in the 64-key kernel, measured slower here: one warp per scheduler is
+      // short of issue slots, not of exponential throughput).
+      // P goes over score columns 0-63, 16 packed columns per store; all scores are in registers by now.
       const float2 c2 = make_float2(c, c), neg_mc2 = make_float2(neg_mc, neg_mc);
       float2 la = make_float2(0.f, 0.f), lb = make_float2(0.f, 0.f);
 #pragma unroll
-      for (int ch = 0; ch < 2; ++ch) {
-        uint32_t sb[32];
-        tmem_ld32(s_addr + ch * 32, sb);
-        tmem_wait_ld();
-        if (masked) {
-#pragma unroll
-          for (int i = 0; i < 32; ++i)
-            if (k_first + ch * 32 + i > limit) sb[i] = 0xff800000u;
-        }
+      for (int ch = 0; ch < 4; ++ch) {
         uint32_t pk[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
-          const float2 x = __ffma2_rn(make_float2(__uint_as_float(sb[2 * i]), __uint_as_float(sb[2 * i + 1])), c2, neg_mc2);
+          const float2 x = __ffma2_rn(make_float2(WIR_S(ch * 32 + 2 * i), WIR_S(ch * 32 + 2 * i + 1)), c2, neg_mc2);
           float2 e;
-          if ((i & 3) == 3) {
-            e = ex2_fma2(x);
-          } else {
-            e.x = ex2_approx(x.x);
-            e.y = ex2_approx(x.y);
-          }
+          e.x = ex2_approx(x.x);
+          e.y = ex2_approx(x.y);
           if (i & 1) lb = __fadd2_rn(lb, e);
           else la = __fadd2_rn(la, e);
-          pk[i] = pack_bf16(e.x, e.y);
+          pk[i] = __byte_perm(__float_as_uint(e.x), __float_as_uint(e.y), 0x7632);
         }
-        tmem_st16(s_addr + ch * 16, pk);   // half 0: columns 0-31 of S_t, half 1: columns 64-95
+        tmem_st16(s_addr + ch * 16, pk);
+        if (ch & 1) {   // 64 keys of P are out: P V can start on them
+          tmem_wait_st();
+          tc_fence_before();
+          mbar_arrive(p_half(t, ch >> 1));
+          if (quarter == 0 && lane == 0) WIR_TRACE_EVENT(p.trace, 1 + t, 103 + (ch >> 1), j);
+        }
       }
+#undef WIR_S
       l += (la.x + lb.x) + (la.y + lb.y);
-      tmem_wait_st();
-      tc_fence_before();
-      mbar_arrive(p_full(t));
     }
 
     if (ok && n > 0) {
-      const bool got = mbar_wait(pv_done(t), (n - 1) & 1, ctx, kRoleEpilogue, t, n) && !bad;
-      if (vote(got)) {
+      if (mbar_wait_warp(pv_done(t), (n - 1) & 1, ctx, kRoleEpilogue, t, n)) {
         tc_fence_after();
-        *xslot(n & 1, half) = l;   // the two halves' shares of the row sum
-        asm volatile("bar.sync %0, 256;" ::"r"(3 + t) : "memory");
-        const float l_all = l + *xslot(n & 1, half ^ 1);
-        const float inv_l = 1.0f / l_all;
+        l *= kRoundUpInv;
+        const float inv_l = 1.0f / l;
         const bool live = q_row < p.S;
-        __nv_bfloat16* dst = p.O + (static_cast<size_t>(bh) * p.S + (live ? q_row : 0)) * D + half * (D / 2);
+        __nv_bfloat16* dst = p.O + (static_cast<size_t>(bh) * p.S + (live ? q_row : 0)) * D;
 #pragma unroll 1
-        for (int cidx = 0; cidx < D / 64; ++cidx) {
+        for (int cidx = 0; cidx < D / 32; ++cidx) {
           uint32_t o[32];
           tmem_ld32(o_addr + cidx * 32, o);
           tmem_wait_ld();
@@ -400,8 +389,8 @@ attn_fwd_wide_sm100(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
             }
           }
         }
-        if (live && half == 0 && p.LSE != nullptr)
-          p.LSE[static_cast<size_t>(bh) * p.S + q_row] = m * c * 0.6931471805599453f + logf(l_all);
+        if (live && p.LSE != nullptr)
+          p.LSE[static_cast<size_t>(bh) * p.S + q_row] = m * c * 0.6931471805599453f + logf(l);
       }
     }
   }
