@@ -54,7 +54,7 @@ def load_peaks():
 NCU_DRAM_BYTES_PER_LAUNCH = {
     "gemm_8192": 941.9e6,
     "gemm_skinny_m16": 138.3e6,
-    "attn_noncausal_b16_h16_s4096_d128": 1057.0e6,
+    "attn_noncausal_b16_h16_s4096_d128": 1059.3e6,
     "attn_causal_b4_h32_s8192_d128": 1058.8e6,
     "attn_bwd_causal_b4_h32_s8192_d128": 3970.4e6,     # both launches of the backward together
 }
@@ -492,7 +492,8 @@ def run_gpu_arm(args, w, name):
     roof["traffic"] = NCU_DRAM_BYTES_PER_LAUNCH.get(name)
     roof["traffic_unit"] = "bytes per launch (ncu dram read + write)"
     roof["algorithmic_bytes_per_launch"] = bytes_of(w)
-    roof["kernel"] = {"gemm": "gemm_bf16_sm100", "attn": "attn_fwd_sm100", "attn_bwd": "attn_bwd_sm100"}[w["kind"]]
+    roof["kernel"] = {"gemm": "gemm_bf16_sm100", "attn": "attn_fwd_sm100" if w.get("causal") else "attn_fwd_wide_sm100",
+                      "attn_bwd": "attn_bwd_sm100"}[w["kind"]]
     roof["algorithmic_per_launch"] = flops_of(w) if tensor_bound else bytes_of(w)
 
     others = []

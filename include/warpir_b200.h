@@ -154,11 +154,12 @@ int warpir_attn_fwd_bf16(const void* Q, const void* K, const void* V, void* O, f
 
 /*
  * Same with the kernel variant spelled out: 0 lets the library choose, 1 is the single-CTA
- * kernel with one softmax warpgroup per 128-row Q tile (the default), 2 the CTA-pair kernel
+ * kernel with 64-key blocks and one softmax warpgroup per 128-row Q tile, 2 the CTA-pair kernel
  * (clusters of two CTAs whose tensor cores share 256-row MMAs; head dimension 128 only), 3 the
  * single-CTA kernel with two softmax warpgroups per Q tile (each takes half of the score
  * columns), 4 the single-CTA kernel with 128-key blocks (one score tile per Q tile, the two
- * Q tiles of a CTA taking turns on the tensor core).  Results agree to rounding.
+ * Q tiles of a CTA taking turns on the tensor core).  Results agree to rounding.  The library's
+ * own choice (0) is 4 without a causal mask and 1 with one.
  * No counterpart in the reference; exists for tests and tuning.
  */
 int warpir_attn_fwd_bf16_ex(const void* Q, const void* K, const void* V, void* O, float* LSE,

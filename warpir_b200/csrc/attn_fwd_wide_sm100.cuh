@@ -1,34 +1,40 @@
-// Attention forward with 128-key blocks: variant 4 of warpir_attn_fwd_bf16_ex.
+// Attention forward with 128-key blocks: variant 4 of warpir_attn_fwd_bf16_ex, and what the
+// library picks when there is no causal mask.
 //
-// The default kernel (attn_fwd_sm100.cuh) works in 64-key blocks with double-buffered scores.
-// Measured there: at head dimension 128 a step is the time the tensor core needs to retire
-// its MMAs, and a 128 x 64 x 16 MMA costs ~71 clocks against ~100 for a 128 x 128 x 16 one;
-// at head dimension 64 a step is ~1900 clocks of fixed round trips of the softmax warps per
-// block, whatever their arithmetic.  Both halve per key with 128-key blocks.  Tensor memory
-// then holds exactly one score tile and one accumulator per Q tile (2 x 128 + 2 x D columns),
-// so Q K^T of the next block cannot run ahead of the softmax of this one; the overlap comes
-// from the two Q tiles of the CTA taking turns on the tensor core (while tile 0 is in its
-// softmax, tile 1's P V and next Q K^T run) and from two softmax warpgroups per tile, each
-// with 64 of the 128 score columns and half of the O columns.
+// The 64-key kernel (attn_fwd_sm100.cuh) double-buffers its scores and is bound by the rate at
+// which the tensor core retires 128 x 64 x 16 MMAs (~71 clocks each, against ~100 for a
+// 128 x 128 x 16 one, so twice the work for 1.4x the time).  With 128-key blocks tensor memory
+// holds exactly one score tile and one accumulator per Q tile (2 x 128 + 2 x D columns), so the
+// Q K^T of a tile's next block cannot run ahead of its softmax; the overlap comes from the two
+// Q tiles of the CTA taking turns: while one is in its softmax, the tensor core works through
+// the other's batch (P V of this block, then Q K^T of the next).
 //
-//   warps 0-7 / 8-15   softmax of tile 0 / 1; within a tile warps 0-3 take columns 0-63,
-//                      warps 4-7 columns 64-127 (thread = row = tensor-memory lane)
-//   warps 16, 17       MMA issuers of tile 0 / 1
-//   warp 18            producer (Q once, then K(j), V(j) tiles of 128 keys into a ring)
+//   warps 0-3 / 4-7    softmax of tile 0 / 1: thread = row = tensor-memory lane, the whole row
+//                      of 128 scores in registers (one pass: max, exponentials, P written over
+//                      score columns 0-63 as packed bf16)
+//   warp 8             MMA issuer of both tiles, strictly alternating between them
+//   warp 10            producer (Q once, then K(j), V(j) tiles of 128 keys into a ring)
+//   warps 9, 11        idle: they only complete the warpgroup whose registers move to the
+//                      softmax warps (setmaxnreg 168 -> 104 / 200)
 //
-// P (bf16, two values per column) overwrites the scores it came from: a thread reloads its 64
-// scores in two chunks of 32 for the exponentials and writes each packed chunk over columns
-// it has already consumed (columns 0-31 for the first half, 64-95 for the second), so neither
-// half touches columns the other still reads.  MMAs execute in issue order, so the next
-// Q K^T, issued right after P V, overwrites S only once P has been read.
+// Why one issuer: with an issuer per tile the two batches interleaved in the tensor core's
+// queue, which pulled the tiles into lockstep (both softmaxes at once at half speed, then both
+// batches queued; 1049 TFLOP/s).  Alternating batches make the tiles settle half a period apart.
+// MMAs execute in issue order, so the next Q K^T, issued right after P V, overwrites S only once
+// P has been read.
 //
-// Measured on a B200 (bf16, TFLOP/s, this kernel against the default): B16 H16 S4096 D128
-// 1049 vs 1144; causal B4 H32 S8192 D128 897 vs 1134 (a 128-key diagonal block masks twice as
-// many scores); D64 554 vs 582 and 511 vs 562.  A step of both tiles takes ~4330 clocks against
-// 3200 of tensor-core work: with one score buffer per tile a tile's chain softmax -> P V ->
-// next Q K^T -> softmax is serial, and the softmax leg (~2100 clocks with its round trips) is
-// longer than the other tile's 1600 clocks of MMAs that should hide it.  So the default kernel
-// stays the default; this one is kept as a checked alternative.
+// Measured on a B200 (bf16, TFLOP/s, this kernel against the 64-key one): B16 H16 S4096 D128
+// 1177 vs 1134, D64 635 vs 581-616; causal B4 H32 S8192 D128 1052-1104 vs 1123, D64 550 vs 607.
+// A step of both tiles takes ~3690 clocks for 3218 clocks of MMAs (87 %): a tile's chain is its
+// softmax (~2050 clocks: tensor-memory load 220, row max ~300, 128 exponentials at the
+// exponential unit's 8 clocks per warp instruction ~1150 with the arithmetic around them,
+// store and signalling ~250) followed by its batch (1609), and only the other tile's batch
+// hides under the softmax.  Tried and not kept: two softmax warpgroups per tile (64 columns
+// each; the halves run in lockstep, so max and exponentials still add up: 1140), P V starting
+// on the first half or quarters of P (the issuer trails the tensor core's queue, so the early
+// start is not used: 1170 and 1039), a polynomial share of the exponentials on the FMA pipe
+// (one warp per scheduler is short of issue slots, not of exponential throughput: 1144-1190),
+// three-input max and rounding P by byte permute (no change).
 #pragma once
 
 #include "attn_fwd_sm100.cuh"
@@ -38,8 +44,6 @@ namespace wir {
 constexpr int kWideThreads = 384;   // 8 softmax warps, 2 MMA warps, 1 producer warp, 1 idle warp (whole warpgroups)
 constexpr int kWideMmaWarp = 8;
 constexpr int kWideBKV = 128;       // keys per block
-constexpr float kRoundUpLog2 = 0.00281502f;    // log2(1 + 2^-9)
-constexpr float kRoundUpInv = 0.99805068f;     // 1 / (1 + 2^-9)
 
 template <int D>
 struct AttnWideSmem {
@@ -49,8 +53,8 @@ struct AttnWideSmem {
   static constexpr int kQOffset = 0;
   static constexpr int kKVOffset = 2 * kTileBytes;
   static constexpr int kBarOffset = kKVOffset + kStages * kTileBytes;
-  // q_full, kv_full[S], kv_empty[S], s_full[2], p_half[2][2], pv_done[2], drain
-  static constexpr int kNumBars = 1 + 2 * kStages + 9;
+  // q_full, kv_full[S], kv_empty[S], s_full[2], p_full[2], pv_done[2], drain
+  static constexpr int kNumBars = 1 + 2 * kStages + 7;
   static constexpr int kTmemPtrOffset = kBarOffset + kNumBars * 8;
   static constexpr int kAbortOffset = kTmemPtrOffset + 4;
   static constexpr int kBytes = kAbortOffset + 4;
@@ -74,9 +78,9 @@ attn_fwd_wide_sm100(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
   auto kv_full = [&](int s) { return bar_base + 8u * (1 + s); };
   auto kv_empty = [&](int s) { return bar_base + 8u * (1 + STAGES + s); };
   auto s_full = [&](int t) { return bar_base + 8u * (1 + 2 * STAGES + t); };
-  auto p_half = [&](int t, int h) { return bar_base + 8u * (3 + 2 * STAGES + 2 * t + h); };   // P of keys 64h .. 64h+63
-  auto pv_done = [&](int t) { return bar_base + 8u * (7 + 2 * STAGES + t); };
-  const uint32_t drain_bar = bar_base + 8u * (9 + 2 * STAGES);
+  auto p_full = [&](int t) { return bar_base + 8u * (3 + 2 * STAGES + t); };
+  auto pv_done = [&](int t) { return bar_base + 8u * (5 + 2 * STAGES + t); };
+  const uint32_t drain_bar = bar_base + 8u * (7 + 2 * STAGES);
   volatile uint32_t* tmem_ptr_slot = reinterpret_cast<volatile uint32_t*>(smem + L::kTmemPtrOffset);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kAbortOffset);
   const AbortCtx ctx{abort_flag, p.status};
@@ -122,8 +126,7 @@ attn_fwd_wide_sm100(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
     }
     for (int t = 0; t < 2; ++t) {
       mbar_init(s_full(t), 1);
-      mbar_init(p_half(t, 0), 128);   // one arrival per row
-      mbar_init(p_half(t, 1), 128);
+      mbar_init(p_full(t), 128);   // one arrival per row
       mbar_init(pv_done(t), 1);
     }
     mbar_init(drain_bar, 1);
@@ -211,7 +214,7 @@ attn_fwd_wide_sm100(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
     auto issue_pv = [&](int t, int j) -> bool {
       const uint32_t idx = 2u * j + 1;
       if (lane == 0) WIR_TRACE_EVENT(p.trace, 0, 1 + 10 * t, j);
-      if (!mbar_wait_warp(p_half(t, 0), j & 1, ctx, kRoleMma, 20 + t, j)) return false;
+      if (!mbar_wait_warp(p_full(t), j & 1, ctx, kRoleMma, 20 + t, j)) return false;
       if (lane == 0) WIR_TRACE_EVENT(p.trace, 0, 2 + 10 * t, j);
       if (!wait_kv(idx, 30 + t)) return false;
       tc_fence_after();
@@ -220,11 +223,6 @@ attn_fwd_wide_sm100(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       const uint32_t o_tmem = tmem_base + kOCol + t * D;
 #pragma unroll
       for (int k = 0; k < kWideBKV / 16; ++k) {
-        // the second half of P arrives while the MMAs of the first run
-        if (k == kWideBKV / 32) {
-          if (!mbar_wait_warp(p_half(t, 1), j & 1, ctx, kRoleMma, 22 + t, j)) return false;
-          tc_fence_after();
-        }
         // 16 keys further: 8 packed columns of P, 16 rows (2048 bytes) of V
         mma_ts_elect(o_tmem, s_tmem + k * 8, v_lo + ((k * 2048) >> 4), desc_hi, idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
       }
@@ -297,17 +295,20 @@ attn_fwd_wide_sm100(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
           if (k0 + i > limit) sb[i] = 0xff800000u;  // -inf
       }
 
-      // three-input max: 64 instructions for 128 scores, in four independent chains
-      float mx0 = fmaxf(WIR_S(0), WIR_S(1)), mx1 = fmaxf(WIR_S(2), WIR_S(3));
-      float mx2 = fmaxf(WIR_S(4), WIR_S(5)), mx3 = fmaxf(WIR_S(6), WIR_S(7));
+      float mx0 = WIR_S(0), mx1 = WIR_S(1), mx2 = WIR_S(2), mx3 = WIR_S(3);
+      float mx4 = WIR_S(4), mx5 = WIR_S(5), mx6 = WIR_S(6), mx7 = WIR_S(7);
 #pragma unroll
       for (int i = 8; i < 128; i += 8) {
-        mx0 = fmax3(mx0, WIR_S(i), WIR_S(i + 1));
-        mx1 = fmax3(mx1, WIR_S(i + 2), WIR_S(i + 3));
-        mx2 = fmax3(mx2, WIR_S(i + 4), WIR_S(i + 5));
-        mx3 = fmax3(mx3, WIR_S(i + 6), WIR_S(i + 7));
+        mx0 = fmaxf(mx0, WIR_S(i));
+        mx1 = fmaxf(mx1, WIR_S(i + 1));
+        mx2 = fmaxf(mx2, WIR_S(i + 2));
+        mx3 = fmaxf(mx3, WIR_S(i + 3));
+        mx4 = fmaxf(mx4, WIR_S(i + 4));
+        mx5 = fmaxf(mx5, WIR_S(i + 5));
+        mx6 = fmaxf(mx6, WIR_S(i + 6));
+        mx7 = fmaxf(mx7, WIR_S(i + 7));
       }
-      const float m_new = fmax3(m, fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+      const float m_new = fmaxf(fmaxf(m, fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3))), fmaxf(fmaxf(mx4, mx5), fmaxf(mx6, mx7)));
       const bool grow = (m_new - m) * c > kRescaleThreshold;  // true on the first block (m = -inf)
       if (__any_sync(0xffffffffu, grow)) {
         if (j > 0) {
@@ -329,11 +330,7 @@ attn_fwd_wide_sm100(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         m = m_new;
       }
 
-      // P = 2^(s c - m c) is rounded to bf16 without the conversion unit: the exponent carries an
-      // extra log2(1 + 2^-9), after which keeping the high 16 bits (one byte permute per pair)
-      // rounds the true value to within half a unit in the last place, unbiased.  The row sum is taken
-      // over the same scaled values and divided by 1 + 2^-9 once at the end.
-      const float neg_mc = kRoundUpLog2 - m * c;
+      const float neg_mc = -m * c;
       // packed f32x2 arithmetic; all exponentials on the exponential unit (a polynomial share on the
       // FMA pipe, which pays in the 64-key kernel, measured slower here: one warp per scheduler is
       // short of issue slots, not of exponential throughput).
@@ -351,24 +348,21 @@ attn_fwd_wide_sm100(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
           e.y = ex2_approx(x.y);
           if (i & 1) lb = __fadd2_rn(lb, e);
           else la = __fadd2_rn(la, e);
-          pk[i] = __byte_perm(__float_as_uint(e.x), __float_as_uint(e.y), 0x7632);
+          pk[i] = pack_bf16(e.x, e.y);
         }
         tmem_st16(s_addr + ch * 16, pk);
-        if (ch & 1) {   // 64 keys of P are out: P V can start on them
-          tmem_wait_st();
-          tc_fence_before();
-          mbar_arrive(p_half(t, ch >> 1));
-          if (quarter == 0 && lane == 0) WIR_TRACE_EVENT(p.trace, 1 + t, 103 + (ch >> 1), j);
-        }
       }
 #undef WIR_S
       l += (la.x + lb.x) + (la.y + lb.y);
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(p_full(t));
+      if (quarter == 0 && lane == 0) WIR_TRACE_EVENT(p.trace, 1 + t, 103, j);
     }
 
     if (ok && n > 0) {
       if (mbar_wait_warp(pv_done(t), (n - 1) & 1, ctx, kRoleEpilogue, t, n)) {
         tc_fence_after();
-        l *= kRoundUpInv;
         const float inv_l = 1.0f / l;
         const bool live = q_row < p.S;
         __nv_bfloat16* dst = p.O + (static_cast<size_t>(bh) * p.S + (live ? q_row : 0)) * D;

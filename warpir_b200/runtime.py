@@ -169,7 +169,8 @@ def launch_attention(Q, K, V, O, LSE=None, softmax_scale: Optional[float] = None
     ``[B, H, S, D]`` tensors with grouped KV heads; ``LSE`` (fp32 ``[B, H, S]``
     or ``[N]``) is filled when given.  Scale defaults to ``1/sqrt(D)``.
     ``variant``: 0 lets the library choose, 1 forces the single-CTA kernel, 2 the CTA-pair
-    kernel (head dimension 128 only), 3 the kernel with two softmax warpgroups per Q tile, 4 the kernel with 128-key blocks.
+    kernel (head dimension 128 only), 3 the kernel with two softmax warpgroups per Q tile, 4 the kernel with 128-key blocks
+    (the library's own choice without a causal mask; with one it is 1).
     """
     import torch
     lib = load_library()
