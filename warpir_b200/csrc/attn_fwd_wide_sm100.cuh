@@ -34,7 +34,10 @@
 // on the first half or quarters of P (the issuer trails the tensor core's queue, so the early
 // start is not used: 1170 and 1039), a polynomial share of the exponentials on the FMA pipe
 // (one warp per scheduler is short of issue slots, not of exponential throughput: 1144-1190),
-// three-input max and rounding P by byte permute (no change).
+// three-input max and rounding P by byte permute (no change), exponentials against the stale max
+// with the row max taken alongside (softmax 1900 clocks, but the batches stretch to 1715-1833 and
+// the step stays at 3700: the tensor core is then ~96 % busy, so this is the instruction-rate
+// bound of 128-wide MMAs).
 #pragma once
 
 #include "attn_fwd_sm100.cuh"
