@@ -58,8 +58,8 @@ def test_ragged_lengths(S, D, causal, lib):
 @pytest.mark.parametrize("causal", [False, True])
 @pytest.mark.parametrize("S", [1, 129, 512, 700, 1100, 2048])
 def test_every_kernel_variant_at_d128(S, causal, variant, lib):
-    """One softmax warpgroup per tile (1), CTA pairs (2) and two softmax warpgroups per tile (3)
-    against the oracle, with grouped K/V heads, across lengths that leave tiles and clusters partly
+    """One softmax warpgroup per tile (1), CTA pairs (2), two softmax warpgroups per tile (3) and
+    128-key blocks (4) against the oracle, with grouped K/V heads, across lengths that leave tiles and clusters partly
     or wholly past the end of the sequence."""
     Q, K, V = R.attention_inputs(2, 4, S, 128, seed=S + variant, Hkv=2)
     O, L = run_attn(Q, K, V, causal, variant=variant)
