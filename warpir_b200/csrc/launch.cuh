@@ -333,6 +333,22 @@ int launch_attn_pair_cfg(const CUtensorMap& tq, const CUtensorMap& tk, const CUt
   return WARPIR_OK;
 }
 
+// WARPIR_ATTN_WIDE=0|1 and WARPIR_ATTN_SPLIT=0|1 override the choice of the 128-key forward and of the
+// forward with two softmax warpgroups per tile (read once per process).
+inline int env_attn_wide() {
+  static const int v = [] {
+    const char* e = getenv("WARPIR_ATTN_WIDE");
+    return e ? (atoi(e) != 0 ? 1 : 0) : -1;
+  }();
+  return v;
+}
+inline int env_attn_split() {
+  static const int v = [] {
+    const char* e = getenv("WARPIR_ATTN_SPLIT");
+    return e ? (atoi(e) != 0 ? 1 : 0) : -1;
+  }();
+  return v;
+}
 // WARPIR_ATTN_PAIR=0|1 overrides the choice between the single-CTA and the CTA-pair forward.
 inline int env_attn_pair() {
   static const int v = [] {
@@ -409,7 +425,7 @@ inline int attn_impl(const void* Q, const void* K, const void* V, void* O, float
   // dimension 128 and 635 vs 581-616 at 64; with one 1052-1104 vs 1123 and 550 vs 607 (the tiles of a
   // CTA end a block apart and a 128-key diagonal block is masked whole).  So the mask decides.
   bool wide = !causal;
-  if (const char* e = getenv("WARPIR_ATTN_WIDE")) wide = atoi(e) != 0;
+  if (env_attn_wide() >= 0) wide = env_attn_wide() != 0;
   if (variant != 0) wide = (variant == 4);
   if (wide) {
     CUtensorMap tk128, tv128;   // K and V in tiles of 128 keys
@@ -421,7 +437,7 @@ inline int attn_impl(const void* Q, const void* K, const void* V, void* O, float
     return causal ? launch_attn_wide_cfg<64, true>(tq, tk128, tv128, p, stream) : launch_attn_wide_cfg<64, false>(tq, tk128, tv128, p, stream);
   }
   bool split = false;
-  if (const char* e = getenv("WARPIR_ATTN_SPLIT")) split = atoi(e) != 0;
+  if (env_attn_split() >= 0) split = env_attn_split() != 0;
   if (variant != 0) split = (variant == 3);
   if (split) {
     if (D == 128) return causal ? launch_attn_split_cfg<128, true>(tq, tk, tv, p, stream) : launch_attn_split_cfg<128, false>(tq, tk, tv, p, stream);
