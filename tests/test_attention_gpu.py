@@ -149,6 +149,24 @@ def test_full_size_property_v_linearity(lib):
     assert (O3.float() - 1).abs().max().item() <= 8e-3
 
 
+@pytest.mark.parametrize("cfg", [(1, 4, 16384, 128), (1, 2, 20000, 128), (1, 2, 32768, 64)])
+def test_long_sequences_on_sampled_rows(cfg, lib):
+    """Hundreds of K/V blocks per Q tile (every barrier parity wraps many times) and a ragged
+    last block.  Without a causal mask a query row's output depends on that row of Q only, so
+    sampled rows are checked with the oracle's expression (softmax(q K^T / sqrt(D)) V in fp32 on
+    the CPU) instead of the full S x S problem."""
+    B, H, S, D = cfg
+    Q, K, V = R.attention_inputs(B, H, S, D, seed=S)
+    O, L = run_attn(Q, K, V, False)
+    assert not torch.isnan(O.float()).any() and not torch.isnan(L).any()   # every row was written
+    rows = torch.randint(0, S, (96,), generator=torch.Generator().manual_seed(S))
+    scores = Q[:, :, rows].float() @ K.float().transpose(-1, -2) / D ** 0.5
+    O_ref = torch.softmax(scores, -1) @ V.float()
+    L_ref = torch.logsumexp(scores, -1)
+    assert (O[:, :, rows].float() - O_ref).abs().max().item() <= R.ATTN_O_ABS_TOL
+    assert (L[:, :, rows] - L_ref).abs().max().item() <= R.ATTN_LSE_ABS_TOL
+
+
 def test_rejections(lib):
     Q = torch.zeros(1, 1, 128, 96, dtype=torch.bfloat16, device="cuda")
     with pytest.raises(runtime.WarpirError) as ei:
