@@ -69,6 +69,24 @@ def build_library(force: bool = False, verbose: bool = False) -> Path:
     return LIB_PATH
 
 
+PROBE_PATH = LIB_DIR / "libwarpir_probe.so"
+
+
+def build_probe(force: bool = False) -> Path:
+    """The tensor-core instruction-rate probe (csrc/probe_mma_rate.cu), a library of its own."""
+    stamp = LIB_DIR / "probe.stamp"
+    if not force and PROBE_PATH.exists() and stamp.exists() and stamp.read_text().strip() == source_digest():
+        return PROBE_PATH
+    LIB_DIR.mkdir(exist_ok=True)
+    cmd = [find_nvcc(), *NVCC_FLAGS, "-I", str(INCLUDE), "-o", str(PROBE_PATH), str(CSRC / "probe_mma_rate.cu")]
+    proc = subprocess.run(cmd, capture_output=True, text=True)
+    if proc.returncode != 0:
+        sys.stderr.write(proc.stdout + proc.stderr)
+        raise RuntimeError(f"nvcc failed ({proc.returncode}): {' '.join(cmd)}")
+    stamp.write_text(source_digest() + "\n")
+    return PROBE_PATH
+
+
 if __name__ == "__main__":
     path = build_library(force="--force" in sys.argv, verbose="-v" in sys.argv)
     print(path)

@@ -66,6 +66,11 @@ struct GemmParams {
   int n_dst = 0;
   __nv_bfloat16* dst[kMaxDst] = {};
   unsigned long long* trace;   // event trace buffer of debug builds (-DWIR_TRACE), else unused
+  // Rasterisation: tiles are walked in bands of group_m row-blocks (column by column inside a band).
+  int group_m = kGroupM;
+  // 1: every other tile of a CTA walks K backwards, so that a wave starts on the K end the
+  // previous wave finished on, which is what an LRU cache still holds of the shared panel
+  int k_serpentine = 0;
 };
 
 // Shared memory: the A tiles of all stages first, then the B tiles, then barriers.  A_ROWS < 128
@@ -104,11 +109,11 @@ struct TileCoord {
 // (The work decomposition below is plain integer arithmetic, callable from the host so that
 // it can be checked exhaustively without a GPU.)
 __host__ __device__ __forceinline__ void decode_tile(int tile, const GemmParams& p, TileCoord& t) {
-  const int band = kGroupM * p.tiles_n;
+  const int band = p.group_m * p.tiles_n;
   const int g = tile / band;
-  const int first_m = g * kGroupM;
+  const int first_m = g * p.group_m;
   const int rest = p.tiles_m - first_m;
-  const int rows = rest < kGroupM ? rest : kGroupM;
+  const int rows = rest < p.group_m ? rest : p.group_m;
   const int in_band = tile - g * band;
   t.m_blk = first_m + in_band % rows;
   t.n_blk = in_band / rows;
@@ -199,26 +204,30 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
   TileCoord p_tile;
   int p_kb = 0, p_kb_end = 0;
   uint32_t p_it = 0;
+  bool p_rev = true;   // flipped before the first tile
   // 1: one stage issued, 0: no work left, -1: a wait ran out
   auto producer_step = [&](bool slot_known_free) -> int {
     if (p_kb >= p_kb_end) {
       if (!work_next(p_work, p, p_tile)) return 0;
       p_kb = p_tile.kb_begin;
       p_kb_end = p_tile.kb_end;
+      p_rev = !p_rev;
     }
+    // K coordinate of this step (the MMA warp only counts stages, so the order is the producer's choice)
+    const int kc = (p.k_serpentine && p_rev) ? (p_tile.kb_begin + p_tile.kb_end - 1 - p_kb) : p_kb;
     const int s = p_it % STAGES;
     const uint32_t ph = (p_it / STAGES) & 1;
     if (!slot_known_free && !mbar_wait(empty_bar(s), ph ^ 1, ctx, kRoleProducer, s, p_kb)) return -1;
     mbar_arrive_expect_tx(full_bar(s), L::kStageBytes);
     const uint32_t a_dst = smem_base + s * L::kABytes;
     const uint32_t b_dst = smem_base + L::kBOffset + s * L::kBBytes;
-    tma_load_2d(a_dst, &tmap_a, full_bar(s), p_kb * kGemmBK, p_tile.m_blk * kTileM);
+    tma_load_2d(a_dst, &tmap_a, full_bar(s), kc * kGemmBK, p_tile.m_blk * kTileM);
     if constexpr (!B_MN) {
-      tma_load_2d(b_dst, &tmap_b, full_bar(s), p_kb * kGemmBK, p_tile.n_blk * BN);
+      tma_load_2d(b_dst, &tmap_b, full_bar(s), kc * kGemmBK, p_tile.n_blk * BN);
     } else {
 #pragma unroll
       for (int c = 0; c < BN / 64; ++c)
-        tma_load_2d(b_dst + c * 8192, &tmap_b, full_bar(s), p_tile.n_blk * BN + c * 64, p_kb * kGemmBK);
+        tma_load_2d(b_dst + c * 8192, &tmap_b, full_bar(s), p_tile.n_blk * BN + c * 64, kc * kGemmBK);
     }
     ++p_kb;
     ++p_it;
@@ -310,15 +319,18 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
         tc_fence_after();
         const uint32_t a_lo = smem_desc_lo(smem_base + s * L::kABytes, 16);
         const uint32_t b_lo = smem_desc_lo(smem_base + L::kBOffset + s * L::kBBytes, B_MN ? 8192 : 16);
+        // The stage's four k-steps go out as one instruction block per 128-row half (issued one by
+        // one, an MMA costs the issuing warp ~80 clocks, more than the tensor core needs for the
+        // 64- and 128-wide tiles).  16 K-elements further: 32 bytes along a K-major row, 16 rows
+        // (2048 B) of an N-major tile.
+        static_assert(kGemmBK == 64, "four k-steps per stage");
+        constexpr uint32_t kBStep = B_MN ? (2048 >> 4) : (32 >> 4);
+        const uint64_t bd = desc64(b_lo, desc_hi);
 #pragma unroll
-        for (int k = 0; k < kGemmBK / 16; ++k) {
-          // 16 K-elements further: 32 bytes along a K-major row, 16 rows (2048 B) of an N-major tile
-          const uint32_t a_k = a_lo + ((k * 32) >> 4);
-          const uint32_t b_k = b_lo + (B_MN ? (k * 2048) >> 4 : (k * 32) >> 4);
-#pragma unroll
-          for (int mt = 0; mt < MT; ++mt)   // the row halves of the CTA tile: 16 KB apart in the A stage
-            mma_ss_elect(d_tmem + mt * BN, a_k + ((mt * kGemmBM * 128) >> 4), desc_hi, b_k, desc_hi, idesc,
-                         (kb > t.kb_begin || k > 0) ? 1u : 0u);
+        for (int mt = 0; mt < MT; ++mt) {   // the row halves of the CTA tile: 16 KB apart in the A stage
+          const uint64_t ad = desc64(a_lo + ((mt * kGemmBM * 128) >> 4), desc_hi);
+          mma_ss_elect_x4(d_tmem + mt * BN, ad, ad + 2, ad + 4, ad + 6, bd, bd + kBStep, bd + 2 * kBStep, bd + 3 * kBStep,
+                          idesc, kb > t.kb_begin ? 1u : 0u);
         }
         mma_commit_elect(empty_bar(s));  // stage reusable once these MMAs have read it
       }

@@ -68,6 +68,24 @@ inline int env_gemm_mt() {
   return v;
 }
 
+// Tuning overrides for experiments: WARPIR_GEMM_GROUP_M=<row-blocks per rasterisation band>,
+// WARPIR_GEMM_KSERP=0|1 (every other tile of a CTA walks K backwards).
+inline int env_gemm_group_m() {
+  static const int v = [] {
+    const char* e = getenv("WARPIR_GEMM_GROUP_M");
+    const int g = e ? atoi(e) : 0;
+    return g > 0 && g <= 4096 ? g : 0;
+  }();
+  return v;
+}
+inline int env_gemm_kserp() {
+  static const int v = [] {
+    const char* e = getenv("WARPIR_GEMM_KSERP");
+    return e ? (atoi(e) != 0 ? 1 : 0) : -1;
+  }();
+  return v;
+}
+
 // Tile width: the widest tile keeps the tensor core busiest per byte of shared-memory
 // traffic, but the tile count must fill the SMs.  Score = fraction of SM-waves that do
 // useful work x relative MMA efficiency of the tile width.
@@ -201,6 +219,8 @@ inline int gemm_impl(const void* A, const void* B, void* C, int64_t M, int64_t N
   p.partial = nullptr;
   p.status = dev->status;
   p.trace = g_trace;
+  if (env_gemm_group_m()) p.group_m = env_gemm_group_m();
+  if (env_gemm_kserp() >= 0 && !ch.stream_k) p.k_serpentine = env_gemm_kserp();
   p.n_dst = n_dst;
   for (int d = 0; d < n_dst; ++d) p.dst[d] = static_cast<__nv_bfloat16*>(dsts[d]);
 
