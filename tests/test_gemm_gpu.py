@@ -121,6 +121,25 @@ def test_k_split_paths_on_two_streams_at_once(lib):
         check(C.cpu(), R.gemm_ref(A, B))
 
 
+@pytest.mark.parametrize("shape", [(2048, 4096, 2048), (2000, 4104, 2056), (4096, 2048, 4096), (520, 8192, 2048)])
+@pytest.mark.parametrize("b_layout", [0, 1])
+def test_large_tiles_on_cta_pairs(shape, b_layout, lib):
+    """Shapes for which the library picks the 256 x 256 tile, computed by a pair of CTAs (cta_group::2
+    MMAs, each CTA holding half of the tile's rows of A and of B), in both storage layouts of B and with
+    ragged edges in every dimension; sampled row blocks against the oracle plus linearity over the whole
+    output."""
+    M, N, K = shape
+    A, B = R.gemm_inputs(M, N, K, seed=M + N, b_layout=b_layout)
+    C = run_gemm(A, B, b_layout)
+    C2 = run_gemm((A.float() * 2).bfloat16(), B, b_layout)
+    assert torch.equal((C.float() * 2).bfloat16(), C2)
+    rows = torch.cat([torch.arange(s, min(s + 40, M)) for s in (0, 100, 236, M // 2 - 20, M - 40)])
+    ref = R.gemm_ref(A[rows], B, b_layout)
+    e = R.gemm_errors(C[rows], ref)
+    assert not torch.isnan(C.float()).any()
+    assert e["normalised"] <= R.GEMM_REL_TOL and e["elementwise"] <= R.GEMM_REL_TOL, e
+
+
 def test_config2_2048_against_oracle(lib):
     A, B = R.gemm_inputs(2048, 2048, 2048, seed=1)
     check(run_gemm(A, B, 1), R.gemm_ref(A, B))

@@ -219,14 +219,11 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
       const uint32_t k_lo = smem_desc_lo(kv_addr(idx), 16);
       const uint32_t d_tmem = tmem_base + t * 128 + (j & 1) * 64;
 #pragma unroll
-      for (int ch = 0; ch < D / 64; ++ch) {
-        // one 64-element chunk of the head dimension per instruction block: four k-steps of 16 elements,
-        // 32 bytes apart inside the chunk's 128-byte rows.  Issued one by one the MMAs cost the issuing
-        // warp ~80 clocks each, more than the tensor core needs for them (48 for 128 x 64 x 16 from
-        // shared memory, 64 for 128 x 128 x 16).
-        const uint64_t qd = desc64(q_lo + ((ch * L::kQChunkBytes) >> 4), desc_hi);
-        const uint64_t kd = desc64(k_lo + ((ch * L::kKVChunkBytes) >> 4), desc_hi);
-        mma_ss_elect_x4(d_tmem, qd, qd + 2, qd + 4, qd + 6, kd, kd + 2, kd + 4, kd + 6, idesc_qk, ch > 0 ? 1u : 0u);
+      for (int k = 0; k < D / 16; ++k) {
+        // 16 elements of the head dimension further: 32 bytes inside a 64-element chunk, then the next chunk
+        const uint32_t q_off = ((k / 4) * L::kQChunkBytes + (k % 4) * 32) >> 4;
+        const uint32_t k_off = ((k / 4) * L::kKVChunkBytes + (k % 4) * 32) >> 4;
+        mma_ss_elect(d_tmem, q_lo + q_off, desc_hi, k_lo + k_off, desc_hi, idesc_qk, k > 0 ? 1u : 0u);
       }
       mma_commit_elect(s_full(t, j & 1));
       mma_commit_elect(kv_empty(idx % STAGES));
@@ -247,12 +244,11 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
         tc_fence_after();
         const uint32_t v_lo = smem_desc_lo(kv_addr(idx), L::kKVChunkBytes);
         const uint32_t p_tmem = tmem_base + t * 128 + (j & 1) * 64;
-        {
-          // the block's four k-steps in one instruction block; 16 keys further = 8 packed-bf16 columns
-          // of P and 16 rows (2048 B) of V
-          static_assert(kAttnBKV == 64, "one block of four k-steps");
-          const uint64_t vd = desc64(v_lo, desc_hi);
-          mma_ts_elect_x4(o_tmem, p_tmem, vd, vd + 128, vd + 256, vd + 384, idesc_pv, j > 0 ? 1u : 0u);
+#pragma unroll
+        for (int k = 0; k < kAttnBKV / 16; ++k) {
+          // 16 keys further: 8 packed-bf16 columns of P, 16 rows (2048 B) of V
+          mma_ts_elect(o_tmem, p_tmem + k * 8, v_lo + ((k * 2048) >> 4), desc_hi, idesc_pv,
+                       (j > 0 || k > 0) ? 1u : 0u);
         }
         mma_commit_elect(pv_done(t, j & 1));
         mma_commit_elect(kv_empty(idx % STAGES));

@@ -204,13 +204,10 @@ attn_fwd_wide_sm100(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       const uint32_t k_lo = smem_desc_lo(kv_addr(idx), 16);
       const uint32_t s_tmem = tmem_base + t * 128;
 #pragma unroll
-      for (int ch = 0; ch < D / 64; ++ch) {
-        // one 64-element chunk of the head dimension per instruction block: four k-steps of 16 elements,
-        // 32 bytes apart inside the chunk's 128-byte rows (issued one by one, the issuing warp needs
-        // ~80 clocks per MMA, more than the 64 the tensor core takes)
-        const uint64_t qd = desc64(q_lo + ((ch * L::kChunkBytes) >> 4), desc_hi);
-        const uint64_t kd = desc64(k_lo + ((ch * L::kChunkBytes) >> 4), desc_hi);
-        mma_ss_elect_x4(s_tmem, qd, qd + 2, qd + 4, qd + 6, kd, kd + 2, kd + 4, kd + 6, idesc_qk, ch > 0 ? 1u : 0u);
+      for (int k = 0; k < D / 16; ++k) {
+        // 16 elements of the head dimension further: 32 bytes inside a 64-element chunk, then the next chunk
+        const uint32_t off = ((k / 4) * L::kChunkBytes + (k % 4) * 32) >> 4;
+        mma_ss_elect(s_tmem, q_lo + off, desc_hi, k_lo + off, desc_hi, idesc_qk, k > 0 ? 1u : 0u);
       }
       mma_commit_elect(s_full(t));
       if (t == last_user(j)) mma_commit_elect(kv_empty(idx % STAGES));
@@ -228,10 +225,9 @@ attn_fwd_wide_sm100(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       const uint32_t s_tmem = tmem_base + t * 128;
       const uint32_t o_tmem = tmem_base + kOCol + t * D;
 #pragma unroll
-      for (int q4 = 0; q4 < kWideBKV / 64; ++q4) {
-        // four k-steps per instruction block; 16 keys further = 8 packed columns of P, 16 rows (2048 bytes) of V
-        const uint64_t vd = desc64(v_lo + ((q4 * 4 * 2048) >> 4), desc_hi);
-        mma_ts_elect_x4(o_tmem, s_tmem + q4 * 32, vd, vd + 128, vd + 256, vd + 384, idesc_pv, (j > 0 || q4 > 0) ? 1u : 0u);
+      for (int k = 0; k < kWideBKV / 16; ++k) {
+        // 16 keys further: 8 packed columns of P, 16 rows (2048 bytes) of V
+        mma_ts_elect(o_tmem, s_tmem + k * 8, v_lo + ((k * 2048) >> 4), desc_hi, idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
       }
       mma_commit_elect(pv_done(t));
       if (t == last_user(j)) mma_commit_elect(kv_empty(idx % STAGES));
@@ -316,7 +312,6 @@ attn_fwd_wide_sm100(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         mx7 = fmaxf(mx7, WIR_S(i + 7));
       }
       const float m_new = fmaxf(fmaxf(m, fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3))), fmaxf(fmaxf(mx4, mx5), fmaxf(mx6, mx7)));
-      if (quarter == 0 && lane == 0) WIR_TRACE_EVENT(p.trace, 1 + t, 104, j);
       const bool grow = (m_new - m) * c > kRescaleThreshold;  // true on the first block (m = -inf)
       if (__any_sync(0xffffffffu, grow)) {
         if (j > 0) {
@@ -362,7 +357,6 @@ attn_fwd_wide_sm100(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       }
 #undef WIR_S
       l += (la.x + lb.x) + (la.y + lb.y);
-      if (quarter == 0 && lane == 0) WIR_TRACE_EVENT(p.trace, 1 + t, 105, j);
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(p_full(t));

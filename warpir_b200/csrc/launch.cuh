@@ -11,6 +11,7 @@
 #include "attn_fwd_split_sm100.cuh"
 #include "attn_fwd_wide_sm100.cuh"
 #include "gemm_sm100.cuh"
+#include "gemm_pair_sm100.cuh"
 
 namespace wir {
 namespace host {
@@ -31,12 +32,27 @@ int launch_gemm_cfg(const CUtensorMap& ta, const CUtensorMap& tb, const wir::Gem
   return WARPIR_OK;
 }
 
+// 256 x 256 tiles on CTA pairs (gemm_pair_sm100.cuh); `grid` counts CTAs (two per cluster).
+template <int STAGES, bool B_MN>
+int launch_gemm_pair_cfg(const CUtensorMap& ta, const CUtensorMap& tb, const wir::GemmParams& p, int grid,
+                         cudaStream_t stream) {
+  auto kernel = wir::gemm_pair_sm100<STAGES, B_MN>;
+  constexpr int smem = wir::GemmPairSmem<STAGES>::kDynamicBytes;
+  static_assert(smem <= 232448, "shared memory limit per CTA");
+  static_assert(smem > 116 * 1024, "one CTA per SM is what keeps the tensor-memory allocation from blocking");
+  if (int rc = opt_in_smem(reinterpret_cast<const void*>(kernel), smem)) return rc;
+  kernel<<<grid, wir::kPairThreads, smem, stream>>>(ta, tb, p);
+  WIR_CUDA(cudaGetLastError());
+  return WARPIR_OK;
+}
+
 struct GemmChoice {
   int block_n;
   int splits;
   bool stream_k = false;   // deal k-blocks, not tiles, out to the CTAs (few rows: HBM-bound on B)
   int mt = 1;   // CTA tile height in units of 128 rows
   int a_rows = 128;   // rows of A loaded per stage (fewer for problems with few rows)
+  bool pair = false;  // the 256 x 256 tile on a CTA pair (cta_group::2) instead of one CTA
 };
 
 // One-off start-up offset between the two Q tiles' softmax warpgroups of the attention kernel,
@@ -55,6 +71,16 @@ inline int env_skinny_bn() {
   static const int v = [] {
     const char* e = getenv("WARPIR_SKINNY_BN");
     return e ? atoi(e) : 0;
+  }();
+  return v;
+}
+
+// Tuning override for experiments: WARPIR_GEMM_PAIR=0|1 turns the CTA-pair kernel off / on wherever
+// the 256 x 256 tile is chosen.
+inline int env_gemm_pair() {
+  static const int v = [] {
+    const char* e = getenv("WARPIR_GEMM_PAIR");
+    return e ? (atoi(e) != 0 ? 1 : 0) : -1;
   }();
   return v;
 }
@@ -200,6 +226,9 @@ inline int gemm_impl(const void* A, const void* B, void* C, int64_t M, int64_t N
   // Gathering: the 128-row tile keeps two accumulators, so its epilogue (which now also feeds the
   // slower stores to the peers) runs under the next tile's MMAs; the 256-row tile's does not.
   if (n_dst > 0 && fixed == nullptr) ch.mt = 1;
+  // the 256 x 256 tile runs on a CTA pair (needs an even number of SMs to pair up, which every sm_100 part has)
+  ch.pair = (ch.mt == 2 && ch.block_n == 256 && fixed == nullptr && ch.splits <= 1 && !ch.stream_k && dev->sm_count >= 2);
+  if (env_gemm_pair() >= 0) ch.pair = ch.pair && env_gemm_pair() != 0;
   const int num_kb = static_cast<int>((K + wir::kGemmBK - 1) / wir::kGemmBK);
   if (ch.splits > num_kb) ch.splits = num_kb;
   if (ch.splits > 1 && N % 4 != 0) ch.splits = 1;  // the reduce pass works on groups of four columns
@@ -226,6 +255,7 @@ inline int gemm_impl(const void* A, const void* B, void* C, int64_t M, int64_t N
 
   int64_t work = static_cast<int64_t>(p.tiles_m) * p.tiles_n * p.splits;
   int grid = static_cast<int>(work < dev->sm_count ? work : dev->sm_count);
+  if (ch.pair) grid = 2 * static_cast<int>(work < dev->sm_count / 2 ? work : dev->sm_count / 2);
   size_t sk_bytes = 0;
   if (ch.stream_k) {
     const int64_t units = static_cast<int64_t>(p.tiles_m) * p.tiles_n * num_kb;
@@ -248,13 +278,13 @@ inline int gemm_impl(const void* A, const void* B, void* C, int64_t M, int64_t N
   {
     const uint64_t dims[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(M)};
     const uint64_t strides[1] = {static_cast<uint64_t>(K) * 2};
-    const uint32_t box[2] = {wir::kGemmBK, static_cast<uint32_t>(ch.a_rows < 128 ? ch.a_rows : tile_m)};
+    const uint32_t box[2] = {wir::kGemmBK, static_cast<uint32_t>(ch.pair ? wir::kPairRows : (ch.a_rows < 128 ? ch.a_rows : tile_m))};
     if (int rc = make_tmap(&ta, A, 2, dims, strides, box)) return rc;
   }
   if (b_layout == 1) {
     const uint64_t dims[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(N)};
     const uint64_t strides[1] = {static_cast<uint64_t>(K) * 2};
-    const uint32_t box[2] = {wir::kGemmBK, static_cast<uint32_t>(ch.block_n)};
+    const uint32_t box[2] = {wir::kGemmBK, static_cast<uint32_t>(ch.pair ? wir::kPairRows : ch.block_n)};
     if (int rc = make_tmap(&tb, B, 2, dims, strides, box)) return rc;
   } else {
     const uint64_t dims[2] = {static_cast<uint64_t>(N), static_cast<uint64_t>(K)};
@@ -266,6 +296,7 @@ inline int gemm_impl(const void* A, const void* B, void* C, int64_t M, int64_t N
   int rc;
   const bool mn = (b_layout == 0);
   if (fixed != nullptr) rc = fixed(ta, tb, p, grid, stream);
+  else if (ch.pair) rc = mn ? launch_gemm_pair_cfg<6, true>(ta, tb, p, grid, stream) : launch_gemm_pair_cfg<6, false>(ta, tb, p, grid, stream);
   else if (ch.stream_k && ch.block_n == 128 && ch.a_rows == 16) rc = mn ? launch_gemm_cfg<128, 10, true, 1, 16>(ta, tb, p, grid, stream) : launch_gemm_cfg<128, 10, false, 1, 16>(ta, tb, p, grid, stream);
   else if (ch.stream_k && ch.block_n == 128) rc = mn ? launch_gemm_cfg<128, 8, true, 1, 64>(ta, tb, p, grid, stream) : launch_gemm_cfg<128, 8, false, 1, 64>(ta, tb, p, grid, stream);
   else if (ch.stream_k && ch.a_rows == 16) rc = mn ? launch_gemm_cfg<256, 6, true, 1, 16>(ta, tb, p, grid, stream) : launch_gemm_cfg<256, 6, false, 1, 16>(ta, tb, p, grid, stream);

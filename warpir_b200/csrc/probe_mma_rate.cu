@@ -31,27 +31,20 @@ struct ProbeParams {
   int bg_tma;
   int b_mn;       // 1: B operand N-major (64-element chunks of N, 8 KB apart, 128 bytes per K row), as V is in P V
   int single;     // 1: one MMA per instruction block (elect, descriptor moves and predicate set per MMA)
+  int random_data;   // 1: operands hold pseudo-random values in +-[0.5, 1) instead of zeros
+  int bg_alu;        // 1: eight more warps run the softmax's arithmetic (packed FMA, exponentials, bf16 packing) on registers
+  int commit_every;  // > 0: a tcgen05.commit (to a barrier nobody waits on) after every so many instruction blocks
+  float* sink;       // the arithmetic warps' results (never read)
   unsigned long long* out;   // per CTA: clocks until the last MMA was issued, clocks until all completed
   int* status;
 };
 
-constexpr int kProbeThreads = 192;          // warp 0 issuer, warp 1 TMA background, warps 2-5 tensor-memory background
+constexpr int kProbeThreads = 448;          // warp 0 issuer, warp 1 TMA background, warps 2-5 tensor-memory background, warps 6-13 arithmetic background
 constexpr int kProbeABytes = 128 * 128;     // 128 rows x 64 bf16
 constexpr int kProbeBBytes = 256 * 128;     // up to 256 rows x 64 bf16
 constexpr int kProbeBgBytes = 4 * 16384;    // four background TMA slots
 constexpr int kProbeBarOffset = kProbeABytes + kProbeBBytes + kProbeBgBytes;
 constexpr int kProbeSmem = kProbeBarOffset + 128 + 1024;
-
-__device__ __forceinline__ void mma_commit_pair_both_elect(uint32_t bar) {
-  // one arrival on the barrier at this offset in both CTAs of the pair
-  asm volatile(
-      "{\n\t.reg .pred e;\n\t.reg .b16 m;\n\t"
-      "mov.b16 m, 3;\n\t"
-      "elect.sync _|e, 0xffffffff;\n\t"
-      "@e tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], m;\n\t}"
-      ::"r"(bar)
-      : "memory");
-}
 
 template <bool PAIR>
 __global__ void __launch_bounds__(kProbeThreads, 1)
@@ -72,14 +65,22 @@ probe_mma_rate_kernel(const __grid_constant__ CUtensorMap tmap_bg, const ProbePa
   const int lane = threadIdx.x & 31;
   const uint32_t rank = PAIR ? cluster_ctarank() : 0u;
 
-  // operands: zeros (the rate does not depend on the values)
+  // operands: zeros, or pseudo-random bf16 pairs in +-[0.5, 1) (does the rate depend on the values?)
+  auto rnd = [&](uint32_t i) {
+    uint32_t h = (i + 1u + blockIdx.x * 65536u) * 2654435761u;
+    h ^= h >> 15;
+    h *= 2246822519u;
+    h ^= h >> 13;
+    return p.random_data ? ((h & 0x807f807fu) | 0x3f003f00u) : 0u;
+  };
   for (int i = threadIdx.x; i < (kProbeABytes + kProbeBBytes) / 16; i += kProbeThreads)
-    reinterpret_cast<uint4*>(smem)[i] = make_uint4(0u, 0u, 0u, 0u);
+    reinterpret_cast<uint4*>(smem)[i] = make_uint4(rnd(4 * i), rnd(4 * i + 1), rnd(4 * i + 2), rnd(4 * i + 3));
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     *stop_flag = 0;
     mbar_init(done_bar, 1);
     for (int s = 0; s < 4; ++s) mbar_init(bg_bar(s), 1);
+    mbar_init(bar_base + 8u * 5, 1);   // target of the extra commits
     fence_mbar_init();
   }
   fence_proxy_async_smem();
@@ -97,6 +98,21 @@ probe_mma_rate_kernel(const __grid_constant__ CUtensorMap tmap_bg, const ProbePa
   if (PAIR) cluster_sync_all();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_ptr_slot;
+  if (warp >= 2 && warp < 6) {
+    // A operand of the TS form (32 packed columns at column 256) and a zeroed accumulator
+    uint32_t r[32];
+    const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>((warp & 3) * 32) << 16);
+#pragma unroll
+    for (int i = 0; i < 32; ++i) r[i] = rnd(threadIdx.x * 32 + i);
+    tmem_st32(lane_addr + 256, r);
+#pragma unroll
+    for (int i = 0; i < 32; ++i) r[i] = 0u;
+    for (int c = 0; c < 8; ++c) tmem_st32(lane_addr + c * 32, r);
+    tmem_wait_st();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
 
   if (warp == 0) {
     if (rank == 0) {
@@ -112,6 +128,13 @@ probe_mma_rate_kernel(const __grid_constant__ CUtensorMap tmap_bg, const ProbePa
       const uint32_t a_tmem = tmem_base + 256;    // TS form: A as 32 packed columns
       __syncwarp();
       const long long t0 = clock64();
+      const uint32_t extra_bar = bar_base + 8u * 5;
+      auto maybe_commit = [&](int b) {
+        if (p.commit_every > 0 && (b + 1) % p.commit_every == 0) {
+          if (PAIR) mma_commit_pair_elect(mapa_shared(extra_bar, 0));
+          else mma_commit_elect(extra_bar);
+        }
+      };
       if (p.single) {
         const uint32_t a_lo = static_cast<uint32_t>(ad), b_lo = static_cast<uint32_t>(bd);
         for (int b = 0; b < p.batches; ++b) {
@@ -120,16 +143,19 @@ probe_mma_rate_kernel(const __grid_constant__ CUtensorMap tmap_bg, const ProbePa
             if (p.ts) mma_ts_elect(d_tmem, a_tmem + k * 8, b_lo + k * static_cast<uint32_t>(bs), desc_hi, idesc, 1u);
             else mma_ss_elect(d_tmem, a_lo + k * 2, desc_hi, b_lo + k * static_cast<uint32_t>(bs), desc_hi, idesc, 1u);
           }
+          maybe_commit(b);
         }
       } else if (p.ts) {
         for (int b = 0; b < p.batches; ++b) {
           if (PAIR) mma_ts_pair_x4(d_tmem, a_tmem, bd, bd + bs, bd + 2 * bs, bd + 3 * bs, idesc, 1u);
           else mma_ts_elect_x4(d_tmem, a_tmem, bd, bd + bs, bd + 2 * bs, bd + 3 * bs, idesc, 1u);
+          maybe_commit(b);
         }
       } else {
         for (int b = 0; b < p.batches; ++b) {
           if (PAIR) mma_ss_pair_x4(d_tmem, ad, ad + 2, ad + 4, ad + 6, bd, bd + bs, bd + 2 * bs, bd + 3 * bs, idesc, 1u);
           else mma_ss_elect_x4(d_tmem, ad, ad + 2, ad + 4, ad + 6, bd, bd + bs, bd + 2 * bs, bd + 3 * bs, idesc, 1u);
+          maybe_commit(b);
         }
       }
       const long long t1 = clock64();
@@ -174,6 +200,28 @@ probe_mma_rate_kernel(const __grid_constant__ CUtensorMap tmap_bg, const ProbePa
         mbar_wait_quiet(bg_bar(k & 3), (k >> 2) & 1);
       }
     }
+  } else if (warp >= 6) {
+    // -------------------------------------------------------------------- background arithmetic
+    if (p.bg_alu) {
+      float2 x[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) x[i] = make_float2(-0.001f * (threadIdx.x + i), -0.002f * (threadIdx.x + i));
+      float2 acc = make_float2(0.f, 0.f);
+      uint32_t packed = 0;
+      for (uint32_t it = 0; !*stop_flag && it < (1u << 22); ++it) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float2 y = __ffma2_rn(x[i], make_float2(1.0001f, 1.0001f), make_float2(-0.01f, -0.01f));
+          float2 e;
+          e.x = ex2_approx(y.x);
+          e.y = ex2_approx(y.y);
+          acc = __fadd2_rn(acc, e);
+          packed ^= pack_bf16(e.x, e.y);
+          x[i] = make_float2(y.x * 0.5f, y.y * 0.5f);
+        }
+      }
+      if (acc.x + acc.y == 12345.f) p.sink[threadIdx.x] = acc.x + __uint_as_float(packed);
+    }
   } else {
     // -------------------------------------------------------------------- background tensor-memory traffic
     if (p.bg_tmem) {
@@ -211,10 +259,12 @@ using namespace wir::host;
 // Runs the probe once on `device` and returns, through `clocks_out[0..1]`, the median over CTAs of
 // (clocks until the last MMA was issued, clocks until all MMAs completed).  `n` in {64, 128, 256};
 // pair = 1 uses cta_group::2 (256-row instructions over two SMs); b_mn = 1 reads B N-major; single = 1
-// issues the MMAs one per instruction block.  `bg_buffer` is 64 x 128 x 64
+// issues the MMAs one per instruction block; random_data = 1 fills the operands with random values;
+// bg_alu = 1 adds eight warps of softmax-like arithmetic; commit_every = k > 0 commits after every k blocks.  `bg_buffer` is 64 x 128 x 64
 // bf16 (1 MiB) of device memory for the background TMA loads (may be NULL when bg_tma = 0).
 extern "C" int warpir_probe_mma_rate(int n, int ts, int pair, int batches, int bg_tmem, int bg_tma, int b_mn,
-                                     int single, const void* bg_buffer, int device, double* clocks_out) {
+                                     int single, int random_data, int bg_alu, int commit_every,
+                                     const void* bg_buffer, int device, double* clocks_out) {
   g_last_error[0] = 0;
   if (n != 64 && n != 128 && n != 256) return fail(WARPIR_EINVAL, "n must be 64, 128 or 256");
   if (batches < 1 || batches > 65536) return fail(WARPIR_EINVAL, "batches must be in [1, 65536]");
@@ -238,7 +288,8 @@ extern "C" int warpir_probe_mma_rate(int n, int ts, int pair, int batches, int b
   unsigned long long* out = nullptr;
   WIR_CUDA(cudaMalloc(&out, sizeof(unsigned long long) * 2 * grid));
   WIR_CUDA(cudaMemset(out, 0, sizeof(unsigned long long) * 2 * grid));
-  wir::ProbeParams p{n, ts, batches, bg_tmem, bg_tma, b_mn ? 1 : 0, single ? 1 : 0, out, dev->status};
+  wir::ProbeParams p{n, ts, batches, bg_tmem, bg_tma, b_mn ? 1 : 0, single ? 1 : 0, random_data ? 1 : 0, bg_alu ? 1 : 0, commit_every, nullptr, out, dev->status};
+  p.sink = reinterpret_cast<float*>(out);   // never written (the guard in the kernel is never true)
   cudaError_t e;
   if (pair) {
     auto kernel = wir::probe_mma_rate_kernel<true>;

@@ -484,6 +484,27 @@ __device__ __forceinline__ void mma_commit_pair_elect(uint32_t bar_cluster) {
       : "memory");
 }
 
+// One arrival on the barrier at this shared-memory offset in BOTH CTAs of the pair, once every
+// pair-MMA issued so far by this thread has completed (a commit costs the issuing thread a few hundred
+// clocks, so one multicast commit instead of one per CTA).
+__device__ __forceinline__ void mma_commit_pair_both_elect(uint32_t bar) {
+  asm volatile(
+      "{\n\t.reg .pred e;\n\t.reg .b16 m;\n\t"
+      "mov.b16 m, 3;\n\t"
+      "elect.sync _|e, 0xffffffff;\n\t"
+      "@e tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], m;\n\t}"
+      ::"r"(bar)
+      : "memory");
+}
+// TMA load into this CTA's shared memory whose bytes are counted on the barrier at `bar_cluster`
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* m, uint32_t bar_cluster, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar_cluster), "r"(x), "r"(y)
+      : "memory");
+}
+
 // ---- tensor memory <-> registers (shape 32x32b: lane = row, one column per register) ----
 #define WIR_R4(r, o) "=r"(r[o + 0]), "=r"(r[o + 1]), "=r"(r[o + 2]), "=r"(r[o + 3])
 #define WIR_R16(r, o) WIR_R4(r, o), WIR_R4(r, o + 4), WIR_R4(r, o + 8), WIR_R4(r, o + 12)
