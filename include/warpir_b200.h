@@ -96,9 +96,12 @@ int warpir_gemm_bf16_ex(const void* A, const void* B, void* C, int64_t M, int64_
  * warpir_gemm_bf16_ex with splits > 1 grows a scratch buffer on demand and
  * warpir_gemm_bf16 allocates its status words on first use, so neither is usable there.
  *
- * This entry point computes exactly what warpir_gemm_bf16_ex(A, B, C, M, N, K, b_layout,
- * block_n, splits, ...) computes -- same kernels, same fixed reduction order, bit-identical
- * C -- but keeps the fp32 partial sums (and its kernel status words) in a statically
+ * With an explicit tile width (block_n = 64, 128 or 256) this entry point computes exactly what
+ * warpir_gemm_bf16_ex(A, B, C, M, N, K, b_layout, block_n, splits, ...) computes -- same
+ * kernels, same fixed reduction order, bit-identical C.  With block_n = 0 it picks the width
+ * by the tile count alone (it never takes the few-rows kernels that load only part of an A
+ * tile, nor stream-K, which warpir_gemm_bf16_ex may), so then the two agree to rounding, not
+ * bit for bit.  It keeps the fp32 partial sums (and its kernel status words) in a statically
  * allocated device array that is part of the library image.  It calls no cudaMalloc,
  * cudaFree or any other allocating routine.  Consequences:
  *  - every GPU whose context loads this library holds WARPIR_NOALLOC_SCRATCH_BYTES
@@ -111,8 +114,9 @@ int warpir_gemm_bf16_ex(const void* A, const void* B, void* C, int64_t M, int64_
  *    contents.  Nothing in it needs clearing between calls (every partial sum that is
  *    read has been written by the same call), but two calls that overlap on the GPU --
  *    different streams, or different host threads -- race on it: serialise them;
- *  - a bounded wait that runs out inside these launches is recorded in the static
- *    status words, not in the ones warpir_read_status reports.
+ *  - a bounded wait that runs out inside these launches is recorded in status words inside
+ *    the static array, not in the ones warpir_read_status reports: read (and clear) them
+ *    with warpir_noalloc_read_status, which allocates nothing either.
  * block_n is 0 (choose), 64, 128 or 256; splits is >= 1.  Other arguments, size rules
  * and return codes are those of warpir_gemm_bf16.
  * This function has no counterpart in the reference.
@@ -120,6 +124,11 @@ int warpir_gemm_bf16_ex(const void* A, const void* B, void* C, int64_t M, int64_
 #define WARPIR_NOALLOC_SCRATCH_BYTES (16u << 20)
 int warpir_gemm_bf16_splitk_noalloc(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K,
                                     int b_layout, int block_n, int splits, int device, void* cuda_stream);
+
+/* Status of the launches made by warpir_gemm_bf16_splitk_noalloc on `device`: same contract as
+ * warpir_read_status (waits for `cuda_stream`, reports, clears on error), same guarantee as the
+ * entry point it serves (no allocation).  No counterpart in the reference. */
+int warpir_noalloc_read_status(int device, void* cuda_stream, int* code, int* detail);
 
 /*
  * GEMM with the all-gather of its output fused into the epilogue.  In a job that splits the rows
@@ -196,6 +205,19 @@ int warpir_attn_bwd_bf16(const void* Q, const void* K, const void* V, const void
 int warpir_launch_generated(void* module_handle, const char* kernel_name, const void* const* tensor_ptrs,
                             const int64_t* dims, int n_tensors, const int64_t* scalars, int n_scalars,
                             int device, void* cuda_stream);
+
+/*
+ * What the launcher would run for C[M,N] = A[M,K] B on a device with `sms` SMs: CTA tile
+ * (block_m x block_n), whether the tile is computed by a CTA pair (cta_group 2), whether the
+ * k-blocks rather than the tiles are dealt out to the SMs (stream_k), and how many rows of A a
+ * stage loads (a_rows < 128 for problems with few rows).  Host arithmetic only: touches no device.
+ * The tile-planning pass of the Python front end (warpir_b200/passes/tile_planner.py) states the
+ * same rules for tile programs; this export lets the two be checked against each other.  The
+ * reference fixes its tile in the program text (tests/gemm_baseline_v2.py:32) and has no planner.
+ * Any output pointer may be NULL.
+ */
+int warpir_plan_gemm(int64_t M, int64_t N, int64_t K, int sms, int* block_m, int* block_n, int* cta_group,
+                     int* stream_k, int* a_rows);
 
 /*
  * Waits for `cuda_stream`, then reports and clears the device's status words:

@@ -36,7 +36,7 @@ def test_reference_pipelined_program_lowers_too():
     assert p.pipelined_in_ir and p.b_row_major and p.block_n == 0
 
 
-@pytest.mark.parametrize("bm,bn,stages", [(128, 256, 4), (128, 128, 6), (128, 64, 8), (256, 256, 3)])
+@pytest.mark.parametrize("bm,bn,stages", [(128, 256, 4), (128, 128, 6), (128, 64, 7), (256, 256, 5)])
 @pytest.mark.parametrize("pipelined", [False, True])
 def test_hardware_tiles_are_instantiated_as_written(bm, bn, stages, pipelined):
     k = build_gemm_kernel(bm, bn, 64, b_k_major=True)
@@ -45,7 +45,20 @@ def test_hardware_tiles_are_instantiated_as_written(bm, bn, stages, pipelined):
     L = Sm100Lowerer()
     src = L.lower(k)
     assert (L.plan.block_m, L.plan.block_n, L.plan.stages) == (bm, bn, stages) and not L.plan.b_row_major
-    assert f"launch_gemm_cfg<{bn}, {stages}, false, {bm // 128}>" in src and "/*b_layout=*/1" in src
+    inst = f"launch_gemm_pair_cfg<{stages}, false>" if (bm, bn) == (256, 256) else \
+        f"launch_gemm_cfg<{bn}, {stages}, false, {bm // 128}>"
+    assert inst in src and "/*b_layout=*/1" in src
+
+
+@pytest.mark.parametrize("bm,bn,floor", [(128, 64, 5), (128, 128, 4), (128, 256, 3)])
+def test_ring_shallower_than_one_cta_per_sm_is_deepened(bm, bn, floor):
+    """A program pipelined for another machine may ask for a ring so shallow that two CTAs would fit on
+    an SM (each allocates all of tensor memory); the instantiation is deepened to the floor, which the
+    program's semantics cannot see."""
+    k = kernel_pass(build_gemm_kernel(bm, bn, 64, b_k_major=True), REFERENCE_MODEL)     # 3 stages
+    L = Sm100Lowerer()
+    src = L.lower(k)
+    assert L.plan.stages == floor and f"launch_gemm_cfg<{bn}, {floor}, false, 1>" in src
 
 
 def test_ring_too_deep_for_shared_memory_is_rejected():
@@ -84,6 +97,32 @@ def test_unknown_programs_are_rejected_not_guessed():
     with pytest.raises(NotImplementedError, match="transpose_b"):
         analyze(_replace_loop_body(g, lambda b: [dataclasses.replace(o, transpose_b=True)
                                                   if isinstance(o, ir.MMAOp) else o for o in b]))
+    # a GEMM loop with anything besides loads, waits and the MMA must not be taken for a plain GEMM: the
+    # hand-written kernel would drop the extra op.  It lowers op by op instead.
+    def scaled(body):
+        out = []
+        for o in body:
+            if isinstance(o, ir.YieldOp):
+                mma = next(x for x in body if isinstance(x, ir.MMAOp))
+                half = ir.Value("c_half", mma.result.type)
+                out.append(ir.MulScalarOp(result=half, input=mma.result, scalar=0.5))
+                o = dataclasses.replace(o, values=(half,))
+            out.append(o)
+        return out
+    k_scaled = _replace_loop_body(g, scaled)
+    with pytest.raises(NotImplementedError, match="MulScalarOp"):
+        analyze(k_scaled)
+    L = Sm100Lowerer()
+    src = L.lower(k_scaled)
+    assert L.plan.kind == "tile_program" and "wir::tp::" in src
+    # ... and an op between the loop and the store (an epilogue on the accumulator) likewise
+    body = list(g.body)
+    st = next(o for o in body if isinstance(o, ir.TMAStoreOp))
+    scaled_out = ir.Value("c_scaled", st.source.type)
+    body[body.index(st):body.index(st) + 1] = [ir.MulScalarOp(result=scaled_out, input=st.source, scalar=2.0),
+                                              dataclasses.replace(st, source=scaled_out)]
+    with pytest.raises(NotImplementedError):
+        analyze(dataclasses.replace(g, body=tuple(body)))
     a = build_attention_kernel()
     with pytest.raises(NotImplementedError, match="row sum"):
         analyze(_replace_loop_body(a, lambda b: [o for o in b if not isinstance(o, ir.RowSumOp)]))

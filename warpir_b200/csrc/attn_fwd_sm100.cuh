@@ -42,6 +42,18 @@ constexpr int kAttnThreads = 352;  // 2 softmax warpgroups (1 per Q tile) + 2 MM
 constexpr int kAttnMmaWarp = 8;    // first MMA-issuing warp; the producer is warp kAttnMmaWarp + 2
 constexpr float kRescaleThreshold = 8.0f;
 
+// Role table of the 64-key kernel (the lowering's table is checked against it at compile time of
+// every emitted translation unit): softmax warps 0-7 (one warpgroup per Q tile), one MMA-issuing
+// warp per Q tile, one producer warp.
+struct AttnRoles {
+  static constexpr int kSoftmaxWarps = 8;
+  static constexpr int kFirstMmaWarp = kAttnMmaWarp;
+  static constexpr int kMmaWarps = 2;
+  static constexpr int kProducerWarp = kAttnMmaWarp + 2;
+  static constexpr int kThreads = kAttnThreads;
+};
+static_assert(AttnRoles::kThreads == 32 * (AttnRoles::kSoftmaxWarps + AttnRoles::kMmaWarps + 1), "thread count");
+
 struct AttnParams {
   int B, H, Hkv, S;        // S = query length = key length
   int D;

@@ -48,6 +48,18 @@ constexpr int kWideThreads = 384;   // 8 softmax warps, 2 MMA warps, 1 producer 
 constexpr int kWideMmaWarp = 8;
 constexpr int kWideBKV = 128;       // keys per block
 
+// Role table of the 128-key kernel: softmax warps 0-7, ONE MMA-issuing warp for both Q tiles, the
+// producer warp; warps 9 and 11 only complete the warpgroup whose registers move to the softmax warps.
+struct AttnWideRoles {
+  static constexpr int kSoftmaxWarps = 8;
+  static constexpr int kFirstMmaWarp = kWideMmaWarp;
+  static constexpr int kMmaWarps = 1;
+  static constexpr int kProducerWarp = kWideMmaWarp + 2;
+  static constexpr int kIdleWarps = 2;
+  static constexpr int kThreads = kWideThreads;
+};
+static_assert(AttnWideRoles::kThreads == 32 * (AttnWideRoles::kSoftmaxWarps + AttnWideRoles::kMmaWarps + 1 + AttnWideRoles::kIdleWarps), "thread count");
+
 template <int D>
 struct AttnWideSmem {
   static constexpr int kChunkBytes = 128 * 128;                  // 128 rows x 64 bf16 (Q, K and V tiles alike)

@@ -105,6 +105,19 @@ int warpir_read_status(int device, void* cuda_stream, int* code, int* detail) {
   return read_status_impl(device, cuda_stream, code, detail);
 }
 
+int warpir_plan_gemm(int64_t M, int64_t N, int64_t K, int sms, int* block_m, int* block_n, int* cta_group,
+                     int* stream_k, int* a_rows) {
+  g_last_error[0] = 0;
+  if (M <= 0 || N <= 0 || K <= 0 || sms <= 0) return fail(WARPIR_EINVAL, "sizes and the SM count must be positive");
+  const GemmChoice ch = plan_gemm_choice(M, N, K, sms, /*block_n=*/0, /*splits=*/0, /*n_dst=*/0, /*fixed=*/false);
+  if (block_m) *block_m = 128 * ch.mt;
+  if (block_n) *block_n = ch.block_n;
+  if (cta_group) *cta_group = ch.pair ? 2 : 1;
+  if (stream_k) *stream_k = ch.stream_k ? 1 : 0;
+  if (a_rows) *a_rows = ch.a_rows;
+  return WARPIR_OK;
+}
+
 }  // extern "C"
 
 extern "C" int warpir_selftest_bounded_wait(int device, void* cuda_stream, int64_t limit_ns) {
@@ -155,20 +168,37 @@ int noalloc_device_ptr(int device, float** out, int* sms) {
     if (ptr == nullptr) return fail(WARPIR_ECUDA, "cudaGetSymbolAddress returned a null device address");
     g_noalloc_ptr[device] = static_cast<float*>(ptr);
   }
-  if (g_encode == nullptr) {
-    void* fn = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q);
-    if (e != cudaSuccess || q != cudaDriverEntryPointSuccess || fn == nullptr)
-      return fail(WARPIR_EDRIVER, "cuTensorMapEncodeTiled not available from this driver");
-    g_encode = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(fn);
-  }
+  if (int rc = ensure_encode()) return rc;
   *out = g_noalloc_ptr[device];
   *sms = g_noalloc_sms[device];
   return WARPIR_OK;
 }
 
 }  // namespace
+
+// Status words of the allocation-free entry point: waits for the stream, copies the four words out of
+// the static array (a plain cudaMemcpy into caller stack memory: nothing is allocated) and clears
+// them when they hold an error.
+extern "C" int warpir_noalloc_read_status(int device, void* cuda_stream, int* code, int* detail) {
+  g_last_error[0] = 0;
+  if (device < 0 || device >= kMaxDevices) return fail(WARPIR_EDEVICE, "device index %d out of range", device);
+  DeviceGuard guard(device);
+  if (guard.err != cudaSuccess) return fail(WARPIR_ECUDA, "cudaSetDevice(%d): %s", device, cudaGetErrorString(guard.err));
+  float* scratch = nullptr;
+  int sms = 0;
+  if (int rc = noalloc_device_ptr(device, &scratch, &sms)) return rc;
+  cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+  int host[4] = {0, 0, 0, 0};
+  WIR_CUDA(cudaStreamSynchronize(stream));
+  WIR_CUDA(cudaMemcpy(host, scratch + kNoallocFloats, sizeof host, cudaMemcpyDeviceToHost));
+  if (host[0] != 0) WIR_CUDA(cudaMemset(scratch + kNoallocFloats, 0, sizeof host));
+  if (code) *code = host[0];
+  if (detail) *detail = host[2];
+  if (host[0] != 0)
+    return fail(WARPIR_EKERNEL, "kernel status %d: cta %d role %d tag %d detail %d", host[0], host[1], host[2] >> 16,
+                host[2] & 0xffff, host[3]);
+  return WARPIR_OK;
+}
 
 extern "C" int warpir_gemm_bf16_splitk_noalloc(const void* A, const void* B, void* C, int64_t M, int64_t N,
                                                int64_t K, int b_layout, int block_n, int splits, int device,

@@ -36,6 +36,18 @@ constexpr int kPairThreads = 192;   // producer warp, MMA warp, four epilogue wa
 constexpr int kPairBN = 256;        // output tile width = MMA N
 constexpr int kPairRows = 128;      // rows of A, of B and of the output tile per CTA
 
+// Role table of the pair kernel (checked against the lowering's, see GemmRoles): per CTA a producer
+// warp, the MMA warp (it issues in the pair's leader only) and one epilogue warpgroup.
+struct GemmPairRoles {
+  static constexpr int kProducerWarp = 0;
+  static constexpr int kMmaWarp = 1;
+  static constexpr int kFirstEpilogueWarp = 2;
+  static constexpr int kEpilogueWarps = 4;
+  static constexpr int kThreads = kPairThreads;
+  static constexpr int kCtasPerTile = 2;
+};
+static_assert(GemmPairRoles::kThreads == 32 * (2 + GemmPairRoles::kEpilogueWarps), "thread count");
+
 template <int STAGES>
 struct GemmPairSmem {
   static constexpr int kABytes = kPairRows * kGemmBK * 2;   // 16 KB

@@ -39,6 +39,18 @@ constexpr int kGemmThreads = 192; // producer warp + MMA warp + 4 epilogue warps
 __host__ __device__ constexpr int gemm_threads(int mt) { return 64 + 128 * mt; }
 constexpr int kGroupM = 16;       // rasterisation band height in row-blocks
 
+// Which warp does what.  The lowering writes its role table into every translation unit it emits as
+// static_asserts against these constants, so a table that drifts from the kernel fails to compile.
+template <int MT>
+struct GemmRoles {
+  static constexpr int kProducerWarp = 0;        // one elected lane issues the TMA loads
+  static constexpr int kMmaWarp = 1;             // one elected lane issues tcgen05.mma / commit
+  static constexpr int kFirstEpilogueWarp = 2;   // one warpgroup per 128 rows of the CTA tile
+  static constexpr int kEpilogueWarps = 4 * MT;
+  static constexpr int kThreads = 32 * (2 + kEpilogueWarps);
+};
+static_assert(GemmRoles<1>::kThreads == gemm_threads(1) && GemmRoles<2>::kThreads == gemm_threads(2), "thread counts");
+
 struct GemmParams {
   int M, N, K;
   int ldc;            // leading dimension of C in elements
@@ -256,6 +268,7 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
       if (producer_step(true) <= 0) break;
     WIR_TRACE_EVENT(p.trace, 4, 32, 0);
   }
+  static_assert(GemmRoles<MT>::kProducerWarp == 0 && GemmRoles<MT>::kMmaWarp == 1 && GemmRoles<MT>::kFirstEpilogueWarp == 2, "roles");
   if (warp == 1) {
     WIR_TRACE_DECL;
     if (lane == 0) WIR_TRACE_EVENT(p.trace, 5, 40, 0);

@@ -79,6 +79,21 @@ struct DeviceGuard {
   }
 };
 
+// cuTensorMapEncodeTiled, fetched once per process (whichever entry point gets here first).
+inline int ensure_encode() {
+  static std::once_flag once;
+  static int rc = WARPIR_OK;
+  std::call_once(once, [] {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q);
+    if (e != cudaSuccess || q != cudaDriverEntryPointSuccess || fn == nullptr) rc = WARPIR_EDRIVER;
+    else g_encode = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(fn);
+  });
+  if (rc != WARPIR_OK) return fail(WARPIR_EDRIVER, "cuTensorMapEncodeTiled not available from this driver");
+  return WARPIR_OK;
+}
+
 inline int get_device_state(int device, DeviceState** out) {
   if (device < 0 || device >= kMaxDevices) return fail(WARPIR_EDEVICE, "device index %d out of range", device);
   std::lock_guard<std::mutex> lock(g_mutex);
@@ -91,18 +106,14 @@ inline int get_device_state(int device, DeviceState** out) {
     WIR_CUDA(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device));
     if (major != 10) return fail(WARPIR_EDEVICE, "device %d has compute capability %d.x; sm_100a needed", device, major);
     WIR_CUDA(cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, device));
+    // the status words must live on `device`, whatever device the calling thread has current
+    DeviceGuard guard(device);
+    if (guard.err != cudaSuccess) return fail(WARPIR_ECUDA, "cudaSetDevice(%d): %s", device, cudaGetErrorString(guard.err));
     WIR_CUDA(cudaMalloc(&d.status, 4 * sizeof(int)));
     WIR_CUDA(cudaMemset(d.status, 0, 4 * sizeof(int)));
     d.ready = true;
   }
-  if (g_encode == nullptr) {
-    void* fn = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q);
-    if (e != cudaSuccess || q != cudaDriverEntryPointSuccess || fn == nullptr)
-      return fail(WARPIR_EDRIVER, "cuTensorMapEncodeTiled not available from this driver");
-    g_encode = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(fn);
-  }
+  if (int rc = ensure_encode()) return rc;
   *out = &d;
   return WARPIR_OK;
 }

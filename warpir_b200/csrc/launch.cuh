@@ -142,15 +142,61 @@ inline GemmChoice choose_gemm(int64_t M, int64_t N, int64_t K, int sms) {
   return c;
 }
 
-// `fixed`: when not null, the instantiation to launch (with `block_n` its tile width and
-// `fixed_mt` its tile height in units of 128 rows); used by
+// Everything the launcher decides about a GEMM from its extents: tile width and height, the CTA pair,
+// stream-K for problems with few rows.  `block_n` / `splits` != 0 are the caller's explicit choices,
+// `n_dst` > 0 the fused all-gather, `fixed` a pinned instantiation (then only the K decomposition is
+// left to decide).  passes/tile_planner.py states the same rules for tile programs; warpir_plan_gemm
+// exposes this function so that the two can be checked against each other.
+inline GemmChoice plan_gemm_choice(int64_t M, int64_t N, int64_t K, int sms, int block_n, int splits, int n_dst,
+                                   bool fixed) {
+  GemmChoice ch = choose_gemm(M, N, K, sms);
+  if (block_n != 0) { ch.block_n = block_n; ch.mt = 1; }
+  if (splits != 0) ch.splits = splits;
+  // few rows: 64-wide tiles (many CTAs streaming B), only the existing rows of A are loaded and
+  // the saved shared memory deepens the ring so more of B is in flight per SM
+  // With splits left to the library the k-blocks are dealt out evenly over all SMs (stream-K)
+  // and the tiles are wider, which makes the TMA boxes of B larger.
+  if (!fixed && block_n == 0 && M <= 64 && N >= 64 * 64) {
+    ch.block_n = 64;
+    ch.mt = 1;
+    ch.a_rows = (M <= 16) ? 16 : 64;
+    const int want = n_dst > 0 ? 64 : (env_skinny_bn() ? env_skinny_bn() : 128);   // no shared tiles when gathering
+    // Shared tiles cost a round trip of fp32 partial sums through L2, which grows with the row
+    // count: above 32 rows the static 64-wide tiling wins unless it leaves many SMs idle.
+    const int64_t tiles64 = (N + 63) / 64;
+    const double static_fill = static_cast<double>(tiles64) /
+                               static_cast<double>(((tiles64 + sms - 1) / sms) * sms);
+    if (splits == 0 && (want == 128 || want == 256) && N % 4 == 0 && (M <= 32 || static_fill < 0.7)) {
+      const int64_t tiles = (N + want - 1) / want;
+      const int64_t units = tiles * ((K + wir::kGemmBK - 1) / wir::kGemmBK);
+      if (tiles <= kSkMaxTiles && units >= 4 * sms) {
+        ch.block_n = want;
+        ch.stream_k = true;
+        ch.splits = 1;
+      }
+    }
+  }
+  if (env_gemm_mt() == 1 && !fixed) ch.mt = 1;
+  if (env_gemm_mt() == 2 && ch.block_n == 256 && !fixed) ch.mt = 2;
+  if (ch.splits > 1 && !fixed) ch.mt = 1;
+  // Gathering: the 128-row tile keeps two accumulators, so its epilogue (which now also feeds the
+  // slower stores to the peers) runs under the next tile's MMAs; the 256-row tile's does not.
+  if (n_dst > 0 && !fixed) ch.mt = 1;
+  // the 256 x 256 tile runs on a CTA pair (needs an even number of SMs to pair up, which every sm_100 part has)
+  ch.pair = (ch.mt == 2 && ch.block_n == 256 && !fixed && ch.splits <= 1 && !ch.stream_k && sms >= 2);
+  if (env_gemm_pair() >= 0) ch.pair = ch.pair && env_gemm_pair() != 0;
+  return ch;
+}
+
+// `fixed`: when not null, the instantiation to launch (with `block_n` its tile width,
+// `fixed_mt` its tile height in units of 128 rows and `fixed_pair` whether it is the CTA-pair kernel); used by
 // the translation units the lowering emits, which pin tile width and ring depth.
 // `dsts` / `n_dst` (fused all-gather): instead of C, n_dst destinations for the finished tiles, each
 // the start of this problem's rows in one GPU's copy of the full output (memory of this GPU or peer
 // memory mapped into its address space).  K-splitting is off in that mode: a tile leaves the SM once.
 inline int gemm_impl(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K, int b_layout, int block_n,
                      int splits, int device, void* cuda_stream, GemmLaunchFn fixed = nullptr, int fixed_mt = 1,
-                     void* const* dsts = nullptr, int n_dst = 0) {
+                     void* const* dsts = nullptr, int n_dst = 0, bool fixed_pair = false) {
   g_last_error[0] = 0;
   if (n_dst < 0 || n_dst > wir::GemmParams::kMaxDst || (n_dst > 0 && dsts == nullptr))
     return fail(WARPIR_EINVAL, "n_dst must be in [1, %d] with a destination array", wir::GemmParams::kMaxDst);
@@ -192,43 +238,11 @@ inline int gemm_impl(const void* A, const void* B, void* C, int64_t M, int64_t N
   if (K % 8 != 0) return fail(WARPIR_ESHAPE, "K = %lld: the row pitch of A must be a multiple of 16 bytes (K %% 8 == 0)", (long long)K);
   if (b_layout == 0 && N % 8 != 0) return fail(WARPIR_ESHAPE, "N = %lld: with B stored [K,N] its row pitch must be a multiple of 16 bytes (N %% 8 == 0)", (long long)N);
 
-  GemmChoice ch = choose_gemm(M, N, K, dev->sm_count);
-  if (block_n != 0) { ch.block_n = block_n; ch.mt = 1; }
-  if (splits != 0) ch.splits = splits;
-  if (fixed != nullptr) ch.mt = fixed_mt;
-  // few rows: 64-wide tiles (many CTAs streaming B), only the existing rows of A are loaded and
-  // the saved shared memory deepens the ring so more of B is in flight per SM
-  // With splits left to the library the k-blocks are dealt out evenly over all SMs (stream-K)
-  // and the tiles are wider, which makes the TMA boxes of B larger.
-  if (fixed == nullptr && block_n == 0 && M <= 64 && N >= 64 * 64) {
-    ch.block_n = 64;
-    ch.mt = 1;
-    ch.a_rows = (M <= 16) ? 16 : 64;
-    const int want = n_dst > 0 ? 64 : (env_skinny_bn() ? env_skinny_bn() : 128);   // no shared tiles when gathering
-    // Shared tiles cost a round trip of fp32 partial sums through L2, which grows with the row
-    // count: above 32 rows the static 64-wide tiling wins unless it leaves many SMs idle.
-    const int64_t tiles64 = (N + 63) / 64;
-    const double static_fill = static_cast<double>(tiles64) /
-                               static_cast<double>(((tiles64 + dev->sm_count - 1) / dev->sm_count) * dev->sm_count);
-    if (splits == 0 && (want == 128 || want == 256) && N % 4 == 0 && (M <= 32 || static_fill < 0.7)) {
-      const int64_t tiles = (N + want - 1) / want;
-      const int64_t units = tiles * ((K + wir::kGemmBK - 1) / wir::kGemmBK);
-      if (tiles <= kSkMaxTiles && units >= 4 * dev->sm_count) {
-        ch.block_n = want;
-        ch.stream_k = true;
-        ch.splits = 1;
-      }
-    }
+  GemmChoice ch = plan_gemm_choice(M, N, K, dev->sm_count, block_n, splits, n_dst, fixed != nullptr);
+  if (fixed != nullptr) {
+    ch.mt = fixed_mt;
+    ch.pair = fixed_pair;   // a pinned instantiation says which kernel it is
   }
-  if (env_gemm_mt() == 1 && fixed == nullptr) ch.mt = 1;
-  if (env_gemm_mt() == 2 && ch.block_n == 256 && fixed == nullptr) ch.mt = 2;
-  if (ch.splits > 1 && fixed == nullptr) ch.mt = 1;
-  // Gathering: the 128-row tile keeps two accumulators, so its epilogue (which now also feeds the
-  // slower stores to the peers) runs under the next tile's MMAs; the 256-row tile's does not.
-  if (n_dst > 0 && fixed == nullptr) ch.mt = 1;
-  // the 256 x 256 tile runs on a CTA pair (needs an even number of SMs to pair up, which every sm_100 part has)
-  ch.pair = (ch.mt == 2 && ch.block_n == 256 && fixed == nullptr && ch.splits <= 1 && !ch.stream_k && dev->sm_count >= 2);
-  if (env_gemm_pair() >= 0) ch.pair = ch.pair && env_gemm_pair() != 0;
   const int num_kb = static_cast<int>((K + wir::kGemmBK - 1) / wir::kGemmBK);
   if (ch.splits > num_kb) ch.splits = num_kb;
   if (ch.splits > 1 && N % 4 != 0) ch.splits = 1;  // the reduce pass works on groups of four columns

@@ -52,7 +52,17 @@ LOG2E = 1.4426950408889634
 HW_BLOCK_M = (128, 256)                   # 256: two 128-row MMAs per k-step share one B tile
 HW_BLOCK_K = 64
 HW_BLOCK_N = (64, 128, 256)
-GEMM_STAGES = {(128, 256): 4, (128, 128): 6, (128, 64): 8, (256, 256): 3}   # fills the 192 KB operand ring
+HW_TILES = ((128, 256), (128, 128), (128, 64), (256, 256))     # CTA tiles the GEMM kernels are instantiated with
+ONE_CTA_PER_SM_BYTES = 116 * 1024      # a kernel holding more shared memory than this runs one CTA per SM
+
+
+def min_stages(block_m: int, block_n: int, block_k: int = HW_BLOCK_K, cta_group: int = 1) -> int:
+    """Shallowest ring a GEMM kernel may be instantiated with: every CTA allocates all of tensor memory,
+    so two CTAs must never share an SM, which the kernels guarantee by holding more than half of its
+    shared memory.  A ring deeper than the schedule asks for does not change what the program
+    computes, only how far the loads run ahead."""
+    stage = 2 * block_k * (block_m + block_n) // cta_group
+    return max(2, ONE_CTA_PER_SM_BYTES // stage + 1)
 
 
 @dataclass(frozen=True)
@@ -65,6 +75,7 @@ class GemmPlan:
     b_row_major: bool                          # True: B stored [K,N]; False: B stored [N,K]
     block_n: int                               # hardware tile width, 0 = chosen per launch
     block_m: int                               # hardware tile height (128 or 256) when block_n is fixed
+    cta_group: int                             # 2: the tile is computed by a CTA pair (cta_group::2)
     stages: int                                # ring depth of the instantiated kernel
     pipelined_in_ir: bool
     row_builtin: str
@@ -86,7 +97,8 @@ class AttentionPlan:
     head_dim: int
     tile_as_written: Tuple[int, int]           # (block_q, block_kv) in the IR
     exp2_scale: float                          # constant applied inside exp2 (scale * log2 e)
-    roles: RoleTable
+    roles: RoleTable                           # of the 64-key kernel (what a causal launch runs)
+    roles_wide: RoleTable                      # of the 128-key kernel (what a launch without a mask runs)
 
     @property
     def kind(self) -> str:
@@ -117,12 +129,22 @@ def _reject(kernel: Kernel, why: str):
 
 
 # --------------------------------------------------------------------------- analysis
-def _analyze_gemm(kernel: Kernel, loop: ForOp) -> GemmPlan:
+def _analyze_gemm(kernel: Kernel, loop: ForOp, machine: Optional["_ms.MachineModel"] = None) -> GemmPlan:
     iv = loop.induction_var
     mmas = [o for o in loop.body if isinstance(o, (_ops.MMAOp, _ops.MMABufOp))]
     mma = mmas[0]
     pre_loop = [o for o in kernel.body if o is not loop]
     pipelined = isinstance(mma, _ops.MMABufOp)
+    # The hand-written kernel computes loads -> MMA -> store and nothing else.  Any other op in the loop
+    # (a scale, an epilogue on the accumulator) or a yield of something other than the MMA's result would
+    # be silently dropped, so such programs are not a GEMM for this purpose: they go op by op.
+    loop_ok = (_ops.TMALoadOp, _ops.TMALoadBufOp, _ops.WaitOp, _ops.WaitBufOp, _ops.MMAOp, _ops.MMABufOp, _ops.YieldOp)
+    extra = [o for o in loop.body if not isinstance(o, loop_ok)]
+    if extra:
+        _reject(kernel, f"the loop body holds {type(extra[0]).__name__} besides loads, waits and the MMA")
+    yields = [o for o in loop.body if isinstance(o, _ops.YieldOp)]
+    if len(yields) != 1 or len(loop.iter_args) != 1 or tuple(yields[0].values) != (mma.result,):
+        _reject(kernel, "the loop does not yield exactly the MMA's result")
 
     if pipelined:
         loads = {o.buf: o for o in loop.body if isinstance(o, _ops.TMALoadBufOp)}
@@ -173,6 +195,11 @@ def _analyze_gemm(kernel: Kernel, loop: ForOp) -> GemmPlan:
         _reject(kernel, "loop tile_size differs from the K extent of the tiles")
 
     stores = [o for o in pre_loop if isinstance(o, _ops.TMAStoreOp)]
+    after_ok = (_ops.TMAStoreOp, _ops.WaitBufOp, _ops.MMABufOp) if pipelined else (_ops.TMAStoreOp,)
+    after = kernel.body[list(kernel.body).index(loop) + 1:]
+    stray = [o for o in after if not isinstance(o, after_ok)]
+    if stray:
+        _reject(kernel, f"{type(stray[0]).__name__} follows the loop: the accumulator is not stored as it is")
     result_of = {r: ia.block_arg for r, ia in zip(loop.results, loop.iter_args)}
     if len(stores) != 1 or result_of.get(stores[0].source) != mma.accum:
         _reject(kernel, "the loop result is not stored exactly once")
@@ -180,19 +207,26 @@ def _analyze_gemm(kernel: Kernel, loop: ForOp) -> GemmPlan:
     if tuple(st.coords[2:]) != (ca[2], col):
         _reject(kernel, "the store coordinates do not match the operands' grid mapping")
 
-    hw_legal = (block_k == HW_BLOCK_K and (block_m, block_n) in GEMM_STAGES)
+    hw_legal = (block_k == HW_BLOCK_K and (block_m, block_n) in HW_TILES)
     fixed_n = block_n if hw_legal else 0
+    cta_group = _ms.default_cta_group(block_m, block_n) if hw_legal else 1
     if fixed_n and not stages:
-        sched = _ms.schedule_loop(loop)
-        stages = sched.num_stages if sched else GEMM_STAGES[(block_m, block_n)]
-    if fixed_n and stages * 2 * block_k * (block_m + block_n) > _ms.SM100_RING_BUDGET:
-        _reject(kernel, f"{stages} stages of a {block_m}x{block_n}x{block_k} tile do not fit in shared memory")
-    if not fixed_n:
+        sched = _ms.schedule_loop(loop, machine)
+        if sched is None:
+            _reject(kernel, "the loop cannot be scheduled on this machine model")
+        stages = sched.num_stages
+    if fixed_n:
+        # the depth the program (or the scheduler) asks for, but never so shallow that two CTAs fit on an SM
+        stages = max(stages, min_stages(block_m, block_n, block_k, cta_group))
+        if stages * 2 * block_k * (block_m + block_n) // cta_group > _ms.SM100_RING_BUDGET:
+            _reject(kernel, f"{stages} stages of a {block_m}x{block_n}x{block_k} tile do not fit in shared memory")
+    else:
         stages = 0   # re-tiled: width and ring depth are picked per launch from the problem size
     return GemmPlan(name=kernel.name, a=ld_a.source.name, b=ld_b.source.name, c=st.dest.name,
                     tile_as_written=(block_m, block_n, block_k), b_row_major=b_row_major, block_n=fixed_n,
-                    block_m=block_m if fixed_n else 0, stages=stages, pipelined_in_ir=pipelined, row_builtin=ca[2].name, col_builtin=col.name,
-                    roles=assign_roles(kernel))
+                    block_m=block_m if fixed_n else 0, cta_group=cta_group, stages=stages, pipelined_in_ir=pipelined,
+                    row_builtin=ca[2].name, col_builtin=col.name,
+                    roles=assign_roles(kernel, tile_rows=block_m if fixed_n else 128, cta_group=cta_group))
 
 
 def _analyze_attention(kernel: Kernel, loop: ForOp) -> AttentionPlan:
@@ -239,18 +273,21 @@ def _analyze_attention(kernel: Kernel, loop: ForOp) -> AttentionPlan:
         _reject(kernel, "the exp2 scale must be positive")
     return AttentionPlan(name=kernel.name, q=ld_q.source.name, k=ld_k.source.name, v=ld_v.source.name,
                          o=post[1].dest.name, head_dim=q_tile.cols, tile_as_written=(q_tile.rows, kv_tile.rows),
-                         exp2_scale=float(scaled.scalar), roles=assign_roles(kernel))
+                         exp2_scale=float(scaled.scalar), roles=assign_roles(kernel, keys_per_block=64),
+                         roles_wide=assign_roles(kernel, keys_per_block=128))
 
 
-def analyze(kernel: Kernel) -> Plan:
-    """Recognise ``kernel`` and extract the parameters its sm_100a kernel is instantiated with."""
+def analyze(kernel: Kernel, machine: Optional["_ms.MachineModel"] = None) -> Plan:
+    """Recognise ``kernel`` and extract the parameters its sm_100a kernel is instantiated with.
+    ``machine``: the model an un-pipelined GEMM loop is scheduled on for its ring depth (default: the
+    sm_100a model of its tile shape)."""
     loop = _top_loop(kernel)
     n_mma = sum(isinstance(o, (_ops.MMAOp, _ops.MMABufOp)) for o in loop.body)
     for v in (*kernel.inputs, *kernel.outputs):
         if not isinstance(v.type, (GlobalType, IntType)):
             raise TypeError(f"Cannot lower kernel argument {v!r}")
     if n_mma == 1:
-        return _analyze_gemm(kernel, loop)
+        return _analyze_gemm(kernel, loop, machine)
     if n_mma == 2:
         return _analyze_attention(kernel, loop)
     _reject(kernel, f"{n_mma} MMAs in the loop")
@@ -297,14 +334,21 @@ def _tensor_index(kernel: Kernel, name: str) -> int:
 def _emit_gemm(kernel: Kernel, plan: GemmPlan) -> str:
     ia, ib, ic = (_tensor_index(kernel, n) for n in (plan.a, plan.b, plan.c))
     b_layout = 0 if plan.b_row_major else 1
-    if plan.block_n:
-        inst = (f"&wir::host::launch_gemm_cfg<{plan.block_n}, {plan.stages}, "
-                f"{'true' if plan.b_row_major else 'false'}, {plan.block_m // 128}>")
+    b_mn = 'true' if plan.b_row_major else 'false'
+    if plan.block_n and plan.cta_group == 2:
+        inst = f"&wir::host::launch_gemm_pair_cfg<{plan.stages}, {b_mn}>"
+        fixed = (f"{plan.block_n}, /*splits=*/1, device, stream, {inst}, /*tile rows / 128=*/{plan.block_m // 128}, "
+                 f"nullptr, 0, /*CTA pair=*/true")
+    elif plan.block_n:
+        inst = f"&wir::host::launch_gemm_cfg<{plan.block_n}, {plan.stages}, {b_mn}, {plan.block_m // 128}>"
         fixed = f"{plan.block_n}, /*splits=*/1, device, stream, {inst}, /*tile rows / 128=*/{plan.block_m // 128}"
     else:
         fixed = "/*block_n: per launch*/0, /*splits: per launch*/0, device, stream"
     n_dim = "dims[4 * {i} + 3]".format(i=ic)
     return f"""
+// who issues what in the instantiated kernel, as planned by the warp-assignment pass
+{plan.roles.static_asserts()}
+
 extern "C" int {plan.name}_launch(const void* const* tensors, const int64_t* dims, const int64_t* scalars,
                                   int device, void* stream) {{
   (void)scalars;  // the K extent is taken from the A tensor, as the loop bound of the program is
@@ -321,6 +365,11 @@ extern "C" int {plan.name}_launch(const void* const* tensors, const int64_t* dim
 def _emit_attention(kernel: Kernel, plan: AttentionPlan) -> str:
     iq, ik, iv_, io = (_tensor_index(kernel, n) for n in (plan.q, plan.k, plan.v, plan.o))
     return f"""
+// who issues what in the two kernels a launch may run (64-key blocks with a causal mask, 128-key blocks
+// without), as planned by the warp-assignment pass
+{plan.roles.static_asserts()}
+{plan.roles_wide.static_asserts()}
+
 // `scalars` may carry two optional trailing values after the program's own ints:
 // scalars[n_ints] != 0 selects the causal variant, and a non-NULL tensors[n_tensors] is an
 // fp32 [B, H, S] buffer that receives the log-sum-exp.  (The tile program as written is
@@ -350,17 +399,38 @@ class Sm100Lowerer:
     ``op_by_op=True`` skips the recognition step and emits every program, the GEMM and
     the attention forward included, one helper call per op (``lowering/generic.py``)."""
 
-    def __init__(self, op_by_op: bool = False) -> None:
+    def __init__(self, op_by_op: bool = False, problem: Optional[Tuple[int, int, int]] = None,
+                 machine: Optional["_ms.MachineModel"] = None) -> None:
+        """``problem = (M, N, K)``: a GEMM program is re-tiled for that problem by the tile planner
+        (``passes/tile_planner.py``), pipelined by ``kernel_pass`` and pinned to the resulting
+        instantiation, instead of leaving the tile to the launcher.  ``machine``: the model the ring depth
+        of a not yet pipelined GEMM loop is solved on (default: the sm_100a model of its tile)."""
         self.op_by_op = op_by_op
+        self.problem = problem
+        self.machine = machine
         self.plan = None
+        self.tile_plan = None
 
     def lower(self, kernel: Kernel) -> str:
         from .generic import emit_tile_program
         self.plan = None
+        self.tile_plan = None
         plan, body, why = None, None, ""
+        planned_note = ""
         if not self.op_by_op:
             try:
-                plan = analyze(kernel)
+                plan = analyze(kernel, self.machine)
+                if isinstance(plan, GemmPlan) and self.problem is not None:
+                    from ..passes.tile_planner import plan_gemm, retile
+                    tp = plan_gemm(*self.problem)
+                    self.tile_plan = tp
+                    if not tp.stream_k and tp.a_rows == 128:
+                        kernel = _ms.kernel_pass(retile(kernel, tp), self.machine)
+                        plan = analyze(kernel, self.machine)
+                        planned_note = f"re-tiled for M, N, K = {self.problem}: {tp.describe()}"
+                    else:
+                        planned_note = (f"for M, N, K = {self.problem} the planner asks for {tp.describe()}: "
+                                        "left to the launcher, which implements that path")
             except NotImplementedError as exc:     # not one of the two recognised programs
                 why = str(exc)
         if plan is None:
@@ -371,8 +441,10 @@ class Sm100Lowerer:
             if why:
                 shown["emitted op by op because"] = why
         else:
-            shown = {k: v for k, v in vars(plan).items() if k != "roles"}
+            shown = {k: v for k, v in vars(plan).items() if k not in ("roles", "roles_wide")}
             shown["warps"] = {r.name: r.warps for r in plan.roles.roles}
+            if planned_note:
+                shown["tile planner"] = planned_note
             body = _emit_gemm(kernel, plan) if isinstance(plan, GemmPlan) else _emit_attention(kernel, plan)
         self.plan = plan
         head = _PREAMBLE.format(ir=_comment(format_kernel(kernel)),

@@ -21,7 +21,12 @@ What differs:
   tile shape on a B200: a ``tcgen05.mma`` over a 128 x N x 64 stage occupies the
   tensor core for 128*N*64*2/8192 clocks, a TMA load takes about a microsecond
   to land, and the number of loads in flight is bounded by how many stages fit
-  in the 227 KB of shared memory rather than by a fixed slot count.
+  in the 227 KB of shared memory rather than by a fixed slot count;
+* the ring depth is an OUTPUT of the schedule on such a machine (``_ring_plan``): the
+  lifetime of a slot (load issue to the end of the MMA that reads it) divided by the
+  initiation interval, with the interval raised until that many slots fit in shared
+  memory.  A machine with a shorter load latency or more shared memory gets a
+  different depth, and the lowering instantiates the kernel with whatever comes out.
 """
 from __future__ import annotations
 
@@ -78,18 +83,26 @@ SM100_MMA_FLOP_PER_CLK = 8192          # dense bf16 per SM
 SM100_TMA_LATENCY_CLK = 1800           # about a microsecond from issue to landed tile
 
 
-def sm100_model(block_m: int, block_n: int, block_k: int, cycle_clocks: int = 128) -> MachineModel:
-    """Machine model for one pipeline stage of a ``block_m x block_n x block_k`` GEMM tile."""
-    mma_clk = 2 * block_m * block_n * block_k / SM100_MMA_FLOP_PER_CLK
-    stage_bytes = 2 * block_k * (block_m + block_n)
-    max_stages = max(2, SM100_RING_BUDGET // stage_bytes)
+def sm100_model(block_m: int, block_n: int, block_k: int, cycle_clocks: int = 128, cta_group: int = 1,
+                tma_latency_clk: int = SM100_TMA_LATENCY_CLK, ring_budget: int = SM100_RING_BUDGET) -> MachineModel:
+    """Machine model for one pipeline stage of a ``block_m x block_n x block_k`` GEMM tile.
+    ``cta_group = 2``: the tile is computed by a CTA pair, each CTA holding half of A's and half of
+    B's rows (half the stage bytes per CTA, both tensor cores working on the stage)."""
+    mma_clk = 2 * block_m * block_n * block_k / (SM100_MMA_FLOP_PER_CLK * cta_group)
+    stage_bytes = 2 * block_k * (block_m + block_n) // cta_group
+    max_stages = max(2, ring_budget // stage_bytes)
     return MachineModel(
-        name=f"sm100-{block_m}x{block_n}x{block_k}",
-        tma_load_latency=math.ceil(SM100_TMA_LATENCY_CLK / cycle_clocks),
+        name=f"sm100-{block_m}x{block_n}x{block_k}" + ("-pair" if cta_group == 2 else ""),
+        tma_load_latency=math.ceil(tma_latency_clk / cycle_clocks),
         mma_latency=max(1, math.ceil(mma_clk / cycle_clocks)),
-        tma_store_latency=math.ceil(SM100_TMA_LATENCY_CLK / cycle_clocks),
+        tma_store_latency=math.ceil(tma_latency_clk / cycle_clocks),
         resources={"tma": 2 * max_stages, "tc": 1},
         max_cycles=400, depth=max_stages + 2, max_stages=max_stages, cycle_clocks=cycle_clocks)
+
+
+def default_cta_group(block_m: int, block_n: int) -> int:
+    """The 256 x 256 tile runs on a CTA pair (``csrc/gemm_pair_sm100.cuh``); every other tile on one CTA."""
+    return 2 if (block_m, block_n) == (256, 256) else 1
 
 
 # --------------------------------------------------------------------------- solver
@@ -230,7 +243,7 @@ def schedule_loop(loop: ForOp, machine: Optional[MachineModel] = None) -> Option
     """Build the dependence graph of ``loop`` and solve it on ``machine``."""
     if machine is None:
         shape = _gemm_tile_shape(loop)
-        machine = sm100_model(*shape) if shape else REFERENCE_MODEL
+        machine = sm100_model(*shape, cta_group=default_cta_group(shape[0], shape[1])) if shape else REFERENCE_MODEL
     latency = {TMALoadOp: ("tma", machine.tma_load_latency), MMAOp: ("tc", machine.mma_latency),
                TMAStoreOp: ("tma", machine.tma_store_latency)}
     nodes: Dict[str, MSInstruction] = {}
@@ -261,15 +274,35 @@ def schedule_loop(loop: ForOp, machine: Optional[MachineModel] = None) -> Option
     _, _, _, ii, stages, stage_of = mgr.solve(machine.max_cycles, machine.depth, machine.resources)
     if ii is None:
         return None
-    if machine.max_stages is not None and stages != machine.max_stages:
-        # On sm_100a the ring is always made as deep as shared memory allows: the schedule says
-        # how many stages the steady state NEEDS, but load latency varies with where the tile
-        # comes from (L2 or HBM), and every extra stage is cover that costs nothing.  Loads go out
-        # at stage 0 and the MMA consumes them at the last stage.
-        last = machine.max_stages - 1
-        stage_of = {k: (last if nodes[k].resource == "tc" else 0) for k in stage_of}
-        stages = machine.max_stages
+    if machine.max_stages is not None:
+        ii, stages, stage_of = _ring_plan(mgr, nodes, ii, machine)
     return LoopSchedule(ii=ii, num_stages=stages, stage_of=stage_of, start_of=mgr.start_of, machine=machine)
+
+
+def _ring_plan(mgr: "MSInstructionManager", nodes: Dict[str, MSInstruction], ii: int,
+               machine: MachineModel) -> Tuple[int, int, Dict[str, int]]:
+    """Ring depth from the solved schedule, for machines whose shared memory bounds it.
+
+    The reference counts stages as ``start // II`` of the last instruction, plus one.  That is the
+    number of iterations in flight at an instant, but a ring slot is occupied from the moment its
+    load is issued until the MMA that reads it has FINISHED, which is ``start(mma) + latency(mma)``
+    later: the slots a schedule needs are that lifetime divided by II, rounded up.  (The reference's
+    own model gives 3 either way: loads at 0, MMA at 12 for 4 cycles, II = 6.)  If shared memory
+    holds fewer slots than that, the loop cannot run at the solver's II: II is raised until the
+    slots fit, which is the model's statement that the loop is then bound by load latency rather
+    than by the tensor core.  Loads are placed at stage 0 and the MMAs at the last stage.
+    """
+    start = mgr.start_of
+    loads = [n for n in nodes.values() if n.resource == "tma"]
+    mmas = [n for n in nodes.values() if n.resource == "tc"]
+    first_load = min(start[n.name] for n in loads)
+    lifetime = max(start[n.name] + n.latency for n in mmas) - first_load
+    ii_fit = ii
+    while -(-lifetime // ii_fit) > machine.max_stages:
+        ii_fit += 1
+    stages = max(2, -(-lifetime // ii_fit))
+    stage_of = {k: (stages - 1 if n.resource == "tc" else 0) for k, n in nodes.items()}
+    return ii_fit, stages, stage_of
 
 
 def _pipeline(loop: ForOp, sched: LoopSchedule) -> List[Op]:

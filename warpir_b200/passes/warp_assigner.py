@@ -18,7 +18,9 @@ Two layers:
   and everything that touches accumulator rows (tensor-memory loads, softmax,
   conversion, stores) goes to warpgroups of four warps, because a warp can only
   reach the 32 tensor-memory lanes ``32 * (warp_id % 4)``...  It returns the role
-  table the kernels are instantiated with and checks it with the solver above.
+  table of the kernel the program is instantiated as; ``RoleTable.static_asserts``
+  turns the table into compile-time checks against the constants that kernel's
+  header exports, which the lowering writes into every translation unit.
 """
 from __future__ import annotations
 
@@ -137,7 +139,7 @@ class WAInstructionManager:
 # --------------------------------------------------------------------------- sm_100a roles
 @dataclass(frozen=True)
 class Role:
-    name: str            # "producer", "mma", "epilogue", "softmax"
+    name: str            # "producer", "mma", "epilogue", "softmax", "idle"
     warps: Tuple[int, ...]
     issues: Tuple[str, ...]   # op mnemonics this role executes
     single_thread: bool       # one elected lane does the issuing
@@ -145,15 +147,44 @@ class Role:
 
 @dataclass(frozen=True)
 class RoleTable:
+    """Who issues what in the kernel a tile program is instantiated as.
+
+    The table is not commentary: ``static_asserts()`` renders it as C++ checks against the
+    constants the kernel header exports (``csrc/*_sm100.cuh``: ``GemmRoles<MT>``, ``GemmPairRoles``,
+    ``AttnRoles``, ``AttnWideRoles``), and the lowering writes those into every translation unit
+    it emits, so a table that disagrees with the kernel does not compile."""
+
     kind: str                 # "gemm" or "attention"
     roles: Tuple[Role, ...]
-    threads: int
+    threads: int              # per CTA
+    cxx: str                  # the header's constants this table mirrors
+    ctas_per_tile: int = 1    # 2: a CTA pair (cta_group::2) computes one tile
 
     def warp_of(self, mnemonic: str) -> Tuple[int, ...]:
         for r in self.roles:
             if mnemonic in r.issues:
                 return r.warps
         raise KeyError(mnemonic)
+
+    def role(self, name: str) -> Role:
+        return next(r for r in self.roles if r.name == name)
+
+    def static_asserts(self) -> str:
+        c = f"wir::{self.cxx}"
+        checks = [f"{c}::kThreads == {self.threads}", f"{c}::kProducerWarp == {self.role('producer').warps[0]}"]
+        if self.kind == "gemm":
+            epi = self.role("epilogue").warps
+            checks += [f"{c}::kMmaWarp == {self.role('mma').warps[0]}", f"{c}::kFirstEpilogueWarp == {epi[0]}",
+                       f"{c}::kEpilogueWarps == {len(epi)}"]
+            if self.ctas_per_tile > 1:
+                checks.append(f"{c}::kCtasPerTile == {self.ctas_per_tile}")
+        else:
+            mma = self.role("mma").warps
+            checks += [f"{c}::kSoftmaxWarps == {len(self.role('softmax').warps)}", f"{c}::kFirstMmaWarp == {mma[0]}",
+                       f"{c}::kMmaWarps == {len(mma)}"]
+        body = " &&\n              ".join(checks)
+        return (f'static_assert({body},\n              "the role table the lowering planned with disagrees '
+                f'with the kernel ({self.cxx})");')
 
 
 _ROW_OPS = ("zero", "neg_infty", "copy", "mul_scalar", "sub", "mul", "exp2", "row_max", "row_sum",
@@ -167,29 +198,60 @@ def _loop_ops(kernel: Kernel):
     return ()
 
 
-def assign_roles(kernel: Kernel) -> RoleTable:
+def gemm_roles(tile_rows: int = 128, cta_group: int = 1) -> RoleTable:
+    """Role table of the GEMM kernels: ``tile_rows`` = 128 or 256 rows per CTA tile
+    (``gemm_bf16_sm100<.., MT>``), ``cta_group`` = 2 for the 256-row tile on a CTA pair
+    (``gemm_pair_sm100``)."""
+    if cta_group == 2:
+        return RoleTable("gemm", (
+            Role("producer", (0,), ("tma_load", "tma_load_buf"), True),
+            Role("mma", (1,), ("mma", "mma_buf", "wait", "wait_buf"), True),      # issues in the pair's leader only
+            Role("epilogue", (2, 3, 4, 5), ("tma_store", "zero"), False),
+        ), threads=192, cxx="GemmPairRoles", ctas_per_tile=2)
+    mt = tile_rows // 128
+    return RoleTable("gemm", (
+        Role("producer", (0,), ("tma_load", "tma_load_buf"), True),
+        Role("mma", (1,), ("mma", "mma_buf", "wait", "wait_buf"), True),
+        Role("epilogue", tuple(range(2, 2 + 4 * mt)), ("tma_store", "zero"), False),   # a warpgroup per 128 rows
+    ), threads=32 * (2 + 4 * mt), cxx=f"GemmRoles<{mt}>")
+
+
+def attention_roles(keys_per_block: int = 64) -> RoleTable:
+    """Role table of the attention-forward kernels: two softmax warpgroups (warps 0-3 and 4-7, one per
+    128-row Q tile, also doing the O rescale and the final store); with 64-key blocks one MMA-issuing
+    warp per Q tile (8, 9) and the producer at warp 10 (352 threads); with 128-key blocks ONE issuer
+    (warp 8) serving both tiles in turn, the producer at warp 10 and two idle warps (9, 11) that only
+    complete the warpgroup whose registers move to the softmax warps (384 threads)."""
+    if keys_per_block == 128:
+        return RoleTable("attention", (
+            Role("softmax", tuple(range(8)), _ROW_OPS, False),
+            Role("mma", (8,), ("mma", "wait"), True),
+            Role("producer", (10,), ("tma_load",), True),
+            Role("idle", (9, 11), (), False),
+        ), threads=384, cxx="AttnWideRoles")
+    return RoleTable("attention", (
+        Role("softmax", tuple(range(8)), _ROW_OPS, False),
+        Role("mma", (8, 9), ("mma", "wait"), True),
+        Role("producer", (10,), ("tma_load",), True),
+    ), threads=352, cxx="AttnRoles")
+
+
+def assign_roles(kernel: Kernel, tile_rows: int = 128, cta_group: int = 1, keys_per_block: int = 64) -> RoleTable:
     """Role table for a GEMM-shaped or attention-shaped tile program on sm_100a.
 
-    GEMM: warp 0 producer, warp 1 MMA issuer, warps 2-5 epilogue (one warpgroup: the four
-    tensor-memory lane quarters).  Attention: two softmax warpgroups (warps 0-3 and 4-7, one
-    per 128-row Q tile, also doing the O rescale and the final store), warp 8 MMA issuer,
-    warp 9 producer.
+    On Blackwell the split is structural rather than searched: TMA loads and ``tcgen05.mma`` are
+    each issued by one elected thread, so loads get a producer warp and MMAs an issuer warp, and
+    everything that touches accumulator rows goes to warpgroups of four warps, because a warp
+    reaches only the 32 tensor-memory lanes ``32 * (warp_id % 4)``.  What varies is which kernel
+    the program is instantiated as (tile height, CTA pairs, keys per block): the keyword arguments.
     """
     body = _loop_ops(kernel)
     n_mma = sum(isinstance(o, (_ops.MMAOp, _ops.MMABufOp)) for o in body)
     has_rows = any(isinstance(o, (_ops.RowMaxOp, _ops.Exp2Op, _ops.RowSumOp)) for o in body)
     if n_mma == 1 and not has_rows:
-        return RoleTable("gemm", (
-            Role("producer", (0,), ("tma_load", "tma_load_buf"), True),
-            Role("mma", (1,), ("mma", "mma_buf", "wait", "wait_buf"), True),
-            Role("epilogue", (2, 3, 4, 5), ("tma_store", "zero"), False),
-        ), threads=192)
+        return gemm_roles(tile_rows, cta_group)
     if n_mma == 2 and has_rows:
-        return RoleTable("attention", (
-            Role("softmax", (0, 1, 2, 3, 4, 5, 6, 7), _ROW_OPS, False),
-            Role("mma", (8,), ("mma", "wait"), True),
-            Role("producer", (9,), ("tma_load",), True),
-        ), threads=320)
+        return attention_roles(keys_per_block)
     raise NotImplementedError(
         f"kernel {kernel.name!r} is neither a loads+MMA loop nor an online-softmax attention loop")
 

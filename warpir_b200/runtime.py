@@ -27,7 +27,8 @@ EXPORTS = (
     "warpir_abi_version", "warpir_strerror", "warpir_last_error", "warpir_gemm_bf16",
     "warpir_gemm_bf16_ex", "warpir_gemm_bf16_allgather", "warpir_attn_fwd_bf16", "warpir_attn_fwd_bf16_ex", "warpir_attn_bwd_bf16",
     "warpir_launch_generated", "warpir_read_status",
-    "warpir_gemm_bf16_splitk_noalloc", "warpir_selftest_bounded_wait",
+    "warpir_gemm_bf16_splitk_noalloc", "warpir_noalloc_read_status", "warpir_selftest_bounded_wait",
+    "warpir_plan_gemm",
 )
 
 
@@ -83,6 +84,10 @@ def load_library() -> ctypes.CDLL:
         lib.warpir_selftest_bounded_wait.argtypes = [ci, vp, i64]
         lib.warpir_read_status.restype = ci
         lib.warpir_read_status.argtypes = [ci, vp, ctypes.POINTER(ci), ctypes.POINTER(ci)]
+        lib.warpir_noalloc_read_status.restype = ci
+        lib.warpir_noalloc_read_status.argtypes = [ci, vp, ctypes.POINTER(ci), ctypes.POINTER(ci)]
+        lib.warpir_plan_gemm.restype = ci
+        lib.warpir_plan_gemm.argtypes = [i64, i64, i64, ci] + [ctypes.POINTER(ci)] * 5
         if lib.warpir_abi_version() != ABI_VERSION:
             raise RuntimeError(f"ABI {lib.warpir_abi_version()} != expected {ABI_VERSION}: rebuild the library")
         _lib = lib
