@@ -62,7 +62,7 @@ def load_peaks():
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the workload's kernel, from one ncu
 # capture each (summaries and the exact commands: profiles/*.md); None where none was taken
 NCU_DRAM_BYTES_PER_LAUNCH = {
-    "gemm_8192": 941.9e6,
+    "gemm_8192": 1157.0e6,     # gemm_pair_sm100, band of 8 row-blocks, A tiles evict_last
     "gemm_skinny_m16": 138.3e6,
     "attn_noncausal_b16_h16_s4096_d128": 1059.3e6,
     "attn_causal_b4_h32_s8192_d128": 1058.8e6,
@@ -626,15 +626,15 @@ def run_gpu_arm(args, w, name):
         step()
         torch.cuda.synchronize()
     if small:
-        times = time_regions_graph(step, args.steps, 0, dist_on, device)
+        times = time_regions_graph(step, args.steps, 0, dist_on, device, args.regions)
     else:
-        times = time_regions(time_steps, step, args.steps, 0, dist_on, device)
+        times = time_regions(time_steps, step, args.steps, 0, dist_on, device, args.regions)
     ms = statistics.median(times)
     per = ms / args.steps
     value = flops_of(w) * world / per / 1e9          # TFLOP/s, whole job
     # one long region: under the power cap the clock settles well below what a 20-step burst sees
     sustained = None
-    if not small:
+    if not small and args.sustained:
         n_long = max(args.steps, int(math.ceil(1100.0 / per)))
         ms_long = time_steps(step, n_long, 0, dist_on, device)
         sustained = {"steps": n_long, "seconds": ms_long / 1e3, "ms_per_step": ms_long / n_long,
@@ -779,6 +779,9 @@ def main():
     ap.add_argument("--no-allgather", dest="allgather", action="store_false",
                     help="with --gpus > 1: skip the GEMM with its output all-gather fused into the epilogue")
     ap.add_argument("--allgather", dest="allgather", action="store_true", help=argparse.SUPPRESS)   # the default
+    ap.add_argument("--regions", type=int, default=REGIONS, help="timed regions of --steps launches each (median reported)")
+    ap.add_argument("--no-sustained", dest="sustained", action="store_false",
+                    help="skip the region of at least a second (for profiler captures, which want few launches)")
     ap.add_argument("--no-strong", dest="strong", action="store_false",
                     help="with --gpus > 1: skip the strong-scaling runs (fixed total work split over the GPUs)")
     args = ap.parse_args()

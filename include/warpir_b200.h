@@ -162,13 +162,11 @@ int warpir_attn_fwd_bf16(const void* Q, const void* K, const void* V, void* O, f
                          float softmax_scale, int causal, int device, void* cuda_stream);
 
 /*
- * Same with the kernel variant spelled out: 0 lets the library choose, 1 is the single-CTA
- * kernel with 64-key blocks and one softmax warpgroup per 128-row Q tile, 2 the CTA-pair kernel
- * (clusters of two CTAs whose tensor cores share 256-row MMAs; head dimension 128 only), 3 the
- * single-CTA kernel with two softmax warpgroups per Q tile (each takes half of the score
- * columns), 4 the single-CTA kernel with 128-key blocks (one score tile per Q tile, the two
- * Q tiles of a CTA taking turns on the tensor core).  Results agree to rounding.  The library's
- * own choice (0) is 4 without a causal mask and 1 with one.
+ * Same with the kernel variant spelled out: 0 lets the library choose, 1 is the kernel with 64-key
+ * blocks and double-buffered scores (one MMA-issuing warp per 128-row Q tile), 4 the kernel with 128-key
+ * blocks (one score tile per Q tile, the two Q tiles of a CTA taking turns on the tensor core).  Other
+ * values are rejected (2 and 3 named experimental kernels that measured slower and were withdrawn).
+ * Results agree to rounding.  The library's own choice (0) is 4 without a causal mask and 1 with one.
  * No counterpart in the reference; exists for tests and tuning.
  */
 int warpir_attn_fwd_bf16_ex(const void* Q, const void* K, const void* V, void* O, float* LSE,

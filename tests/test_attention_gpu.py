@@ -54,19 +54,18 @@ def test_ragged_lengths(S, D, causal, lib):
     check(O, L, *R.attention_ref(Q, K, V, None, causal))
 
 
-@pytest.mark.parametrize("variant", [1, 2, 3, 4])
+@pytest.mark.parametrize("variant", [1, 4])
 @pytest.mark.parametrize("causal", [False, True])
 @pytest.mark.parametrize("S", [1, 129, 512, 700, 1100, 2048])
 def test_every_kernel_variant_at_d128(S, causal, variant, lib):
-    """One softmax warpgroup per tile (1), CTA pairs (2), two softmax warpgroups per tile (3) and
-    128-key blocks (4) against the oracle, with grouped K/V heads, across lengths that leave tiles and clusters partly
-    or wholly past the end of the sequence."""
+    """Both forward kernels (64-key blocks: 1, 128-key blocks: 4) against the oracle, with grouped K/V heads,
+    across lengths that leave tiles partly or wholly past the end of the sequence."""
     Q, K, V = R.attention_inputs(2, 4, S, 128, seed=S + variant, Hkv=2)
     O, L = run_attn(Q, K, V, causal, variant=variant)
     check(O, L, *R.attention_ref(Q, K, V, None, causal))
 
 
-@pytest.mark.parametrize("variant", [1, 2, 3, 4])
+@pytest.mark.parametrize("variant", [1, 4])
 def test_rescale_path_in_every_variant(variant, lib):
     Q, K, V = R.attention_inputs(1, 2, 1024, 128, seed=2)
     ramp = torch.linspace(0.2, 6.0, 1024).view(1, 1, 1024, 1)
@@ -75,7 +74,7 @@ def test_rescale_path_in_every_variant(variant, lib):
     check(O, L, *R.attention_ref(Q, K, V, None, True))
 
 
-@pytest.mark.parametrize("variant", [1, 3, 4])
+@pytest.mark.parametrize("variant", [1, 4])
 @pytest.mark.parametrize("causal", [False, True])
 @pytest.mark.parametrize("S", [1, 100, 384, 1000, 2048])
 def test_kernel_variants_at_d64(S, causal, variant, lib):
@@ -92,10 +91,9 @@ def test_kernel_variants_at_d64(S, causal, variant, lib):
 def test_variant_rejections(lib):
     Q, K, V = (t.cuda() for t in R.attention_inputs(1, 1, 64, 64, seed=1))
     O = torch.empty_like(Q)
-    with pytest.raises(runtime.WarpirError):
-        runtime.launch_attention(Q, K, V, O, None, None, False, 2)     # pairs exist for D = 128 only
-    with pytest.raises(runtime.WarpirError):
-        runtime.launch_attention(Q, K, V, O, None, None, False, 5)
+    for bad in (2, 3, 5, -1):                     # only 0 (choose), 1 and 4 name a kernel
+        with pytest.raises(runtime.WarpirError):
+            runtime.launch_attention(Q, K, V, O, None, None, False, bad)
 
 
 def test_grouped_kv_heads_and_custom_scale(lib):

@@ -69,6 +69,21 @@ def build_library(force: bool = False, verbose: bool = False) -> Path:
     return LIB_PATH
 
 
+def build_variant(tag: str, defines) -> Path:
+    """Another build of the library with extra -D flags (``-DWIR_TRACE`` event traces,
+    ``-DWIR_ABLATE=n`` measurement builds): ``lib/libwarpir_b200_<tag>.so``.  Load it by pointing
+    ``WARPIR_B200_LIBRARY`` at it."""
+    LIB_DIR.mkdir(exist_ok=True)
+    out = LIB_DIR / f"libwarpir_b200_{tag}.so"
+    flags = [f for f in NVCC_FLAGS if f not in ("-Xptxas", "-v")]
+    cmd = [find_nvcc(), *flags, *[f"-D{d}" for d in defines], "-I", str(INCLUDE), "-o", str(out), str(CSRC / "capi.cu")]
+    proc = subprocess.run(cmd, capture_output=True, text=True)
+    if proc.returncode != 0:
+        sys.stderr.write(proc.stdout + proc.stderr)
+        raise RuntimeError(f"nvcc failed ({proc.returncode}): {' '.join(cmd)}")
+    return out
+
+
 PROBE_PATH = LIB_DIR / "libwarpir_probe.so"
 
 
@@ -88,5 +103,9 @@ def build_probe(force: bool = False) -> Path:
 
 
 if __name__ == "__main__":
-    path = build_library(force="--force" in sys.argv, verbose="-v" in sys.argv)
-    print(path)
+    if "--variant" in sys.argv:      # python -m warpir_b200.build --variant trace WIR_TRACE
+        i = sys.argv.index("--variant")
+        print(build_variant(sys.argv[i + 1], sys.argv[i + 2:]))
+    else:
+        path = build_library(force="--force" in sys.argv, verbose="-v" in sys.argv)
+        print(path)

@@ -293,6 +293,12 @@ attn_fwd_wide_sm100(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       tc_fence_after();
       if (quarter == 0 && lane == 0) WIR_TRACE_EVENT(p.trace, 1 + t, 101, j);
 
+#if defined(WIR_ABLATE) && WIR_ABLATE == 3
+      // measurement build: no softmax at all, only the barrier handshake (results are meaningless)
+      tc_fence_before();
+      mbar_arrive(p_full(t));
+      continue;
+#endif
       uint32_t sb[128];  // this thread's row of raw scores, as fp32 bit patterns
       tmem_ld32(s_addr, sb);
       tmem_ld32(s_addr + 32, sb + 32);
@@ -312,8 +318,14 @@ attn_fwd_wide_sm100(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
 
       float mx0 = WIR_S(0), mx1 = WIR_S(1), mx2 = WIR_S(2), mx3 = WIR_S(3);
       float mx4 = WIR_S(4), mx5 = WIR_S(5), mx6 = WIR_S(6), mx7 = WIR_S(7);
+      // measurement builds (-DWIR_ABLATE=1|2|3, results meaningless): 2 also drops the row max
+#if defined(WIR_ABLATE) && WIR_ABLATE == 2
+#pragma unroll
+      for (int i = 8; i < 16; i += 8) {
+#else
 #pragma unroll
       for (int i = 8; i < 128; i += 8) {
+#endif
         mx0 = fmaxf(mx0, WIR_S(i));
         mx1 = fmaxf(mx1, WIR_S(i + 1));
         mx2 = fmaxf(mx2, WIR_S(i + 2));
@@ -359,8 +371,12 @@ attn_fwd_wide_sm100(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         for (int i = 0; i < 16; ++i) {
           const float2 x = __ffma2_rn(make_float2(WIR_S(ch * 32 + 2 * i), WIR_S(ch * 32 + 2 * i + 1)), c2, neg_mc2);
           float2 e;
+#if defined(WIR_ABLATE) && (WIR_ABLATE == 1 || WIR_ABLATE == 2)
+          e = x;   // measurement build: no exponentials
+#else
           e.x = ex2_approx(x.x);
           e.y = ex2_approx(x.y);
+#endif
           if (i & 1) lb = __fadd2_rn(lb, e);
           else la = __fadd2_rn(la, e);
           pk[i] = pack_bf16(e.x, e.y);

@@ -125,6 +125,7 @@ gemm_pair_sm100(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
       uint32_t it = 0;
       bool ok = true;
       TileCoord t;
+      const uint64_t pol_a = l2_policy_evict_last(), pol_b = l2_policy_evict_first();
       for (int tile = cl; ok && tile < total_tiles; tile += ncl) {
         decode_tile(tile, p, t);
         const int row_a = t.m_blk * 2 * kPairRows + static_cast<int>(rank) * kPairRows;
@@ -137,9 +138,11 @@ gemm_pair_sm100(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
           const uint32_t full_leader = mapa_shared(full_bar(s), 0);
           const uint32_t a_dst = smem_base + s * L::kABytes;
           const uint32_t b_dst = smem_base + L::kBOffset + s * L::kBBytes;
-          tma_load_2d_pair(a_dst, &tmap_a, full_leader, kb * kGemmBK, row_a);
+          if (p.l2_hints & 1) tma_load_2d_pair_hint(a_dst, &tmap_a, full_leader, kb * kGemmBK, row_a, pol_a);
+          else tma_load_2d_pair(a_dst, &tmap_a, full_leader, kb * kGemmBK, row_a);
           if constexpr (!B_MN) {
-            tma_load_2d_pair(b_dst, &tmap_b, full_leader, kb * kGemmBK, row_b);
+            if (p.l2_hints & 2) tma_load_2d_pair_hint(b_dst, &tmap_b, full_leader, kb * kGemmBK, row_b, pol_b);
+            else tma_load_2d_pair(b_dst, &tmap_b, full_leader, kb * kGemmBK, row_b);
           } else {
 #pragma unroll
             for (int c = 0; c < kPairRows / 64; ++c)
@@ -223,7 +226,8 @@ gemm_pair_sm100(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
               q.y = pack_bf16(__uint_as_float(r[8 * v + 2]), __uint_as_float(r[8 * v + 3]));
               q.z = pack_bf16(__uint_as_float(r[8 * v + 4]), __uint_as_float(r[8 * v + 5]));
               q.w = pack_bf16(__uint_as_float(r[8 * v + 6]), __uint_as_float(r[8 * v + 7]));
-              reinterpret_cast<uint4*>(dst)[v] = q;
+              if (p.l2_hints & 4) __stcs(reinterpret_cast<uint4*>(dst) + v, q);
+              else reinterpret_cast<uint4*>(dst)[v] = q;
             }
           } else {
 #pragma unroll

@@ -26,7 +26,11 @@
 //
 // Work items (output tile x K-split) are handed out statically, `gridDim.x`
 // apart, walking the tile grid in bands of kGroupM row-blocks so that the CTAs
-// running at any moment share A and B panels in L2.
+// running at any moment share A and B panels in L2.  (DRAM traffic stays near "every wave of
+// tiles reads its own rows of A and columns of B once": ~1.1-1.2 GB per 8192^3 launch for 0.4 GB
+// of operands, whatever the band height, the K direction of alternate tiles or the L2
+// eviction hints; the reuse that is left on the table is ACROSS waves, and L2 does not
+// keep a 33-67 MB row band alive under the 60 MB that stream through per wave.)
 #pragma once
 
 #include "ptx.cuh"
@@ -37,7 +41,7 @@ constexpr int kGemmBM = 128;      // rows of an output tile = MMA M
 constexpr int kGemmBK = 64;       // K extent of one pipeline stage: 64 bf16 = one 128-byte swizzle row
 constexpr int kGemmThreads = 192; // producer warp + MMA warp + 4 epilogue warps (per 128 rows of the tile)
 __host__ __device__ constexpr int gemm_threads(int mt) { return 64 + 128 * mt; }
-constexpr int kGroupM = 16;       // rasterisation band height in row-blocks
+constexpr int kGroupM = 8;        // rasterisation band height in row-blocks (measured on 8192^3: least DRAM traffic of 4/8/12/16/32)
 
 // Which warp does what.  The lowering writes its role table into every translation unit it emits as
 // static_asserts against these constants, so a table that drifts from the kernel fails to compile.
@@ -83,6 +87,12 @@ struct GemmParams {
   // 1: every other tile of a CTA walks K backwards, so that a wave starts on the K end the
   // previous wave finished on, which is what an LRU cache still holds of the shared panel
   int k_serpentine = 0;
+  // L2 hints of the pair kernel (bit 0: A tiles evict_last, bit 1: B tiles evict_first, bit 2: streaming
+  // stores of C).  Measured on 8192^3 (DRAM read + write per launch, band of 8): none 1186 MB, A evict_last
+  // 1157 MB and ~1 % faster, B evict_first 2137 MB (a B tile is still wanted by the other clusters of the
+  // wave when it goes), streaming stores no change.  No setting brings a row band of A (33 MB) through
+  // to the next wave of tiles.
+  int l2_hints = 1;
 };
 
 // Shared memory: the A tiles of all stages first, then the B tiles, then barriers.  A_ROWS < 128

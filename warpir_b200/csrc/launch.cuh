@@ -7,8 +7,6 @@
 #include "host_common.cuh"
 #include "attn_bwd_sm100.cuh"
 #include "attn_fwd_sm100.cuh"
-#include "attn_fwd_pair_sm100.cuh"
-#include "attn_fwd_split_sm100.cuh"
 #include "attn_fwd_wide_sm100.cuh"
 #include "gemm_sm100.cuh"
 #include "gemm_pair_sm100.cuh"
@@ -60,7 +58,8 @@ struct GemmChoice {
 inline int env_attn_stagger() {
   static const int v = [] {
     const char* e = getenv("WARPIR_ATTN_STAGGER");
-    return e ? atoi(e) : 1000;
+    const int c = e ? atoi(e) : 1000;
+    return c < 0 ? 0 : (c > 100000 ? 100000 : c);   // the kernel spins for this long once: keep it bounded
   }();
   return v;
 }
@@ -101,6 +100,13 @@ inline int env_gemm_group_m() {
     const char* e = getenv("WARPIR_GEMM_GROUP_M");
     const int g = e ? atoi(e) : 0;
     return g > 0 && g <= 4096 ? g : 0;
+  }();
+  return v;
+}
+inline int env_gemm_l2_hints() {
+  static const int v = [] {
+    const char* e = getenv("WARPIR_GEMM_L2_HINTS");
+    return e ? (atoi(e) & 7) : -1;
   }();
   return v;
 }
@@ -264,6 +270,7 @@ inline int gemm_impl(const void* A, const void* B, void* C, int64_t M, int64_t N
   p.trace = g_trace;
   if (env_gemm_group_m()) p.group_m = env_gemm_group_m();
   if (env_gemm_kserp() >= 0 && !ch.stream_k) p.k_serpentine = env_gemm_kserp();
+  if (env_gemm_l2_hints() >= 0) p.l2_hints = env_gemm_l2_hints();
   p.n_dst = n_dst;
   for (int d = 0; d < n_dst; ++d) p.dst[d] = static_cast<__nv_bfloat16*>(dsts[d]);
 
@@ -350,22 +357,6 @@ int launch_attn_cfg(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensor
   return WARPIR_OK;
 }
 
-// Two softmax warpgroups per Q tile (attn_fwd_split_sm100.cuh).
-template <int D, bool CAUSAL>
-int launch_attn_split_cfg(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const wir::AttnParams& p,
-                          cudaStream_t stream) {
-  auto kernel = wir::attn_fwd_split_sm100<D, CAUSAL>;
-  constexpr int smem = wir::AttnSplitSmem<D>::kDynamicBytes;
-  static_assert(smem <= 232448, "shared memory limit per CTA");
-  static_assert(smem > 116 * 1024, "one CTA per SM is what keeps the tensor-memory allocation from blocking");
-  if (int rc = opt_in_smem(reinterpret_cast<const void*>(kernel), smem)) return rc;
-  const int pairs = (p.S + 2 * wir::kAttnBQ - 1) / (2 * wir::kAttnBQ);
-  dim3 grid(pairs, p.H, p.B);
-  kernel<<<grid, wir::kSplitThreads, smem, stream>>>(tq, tk, tv, p);
-  WIR_CUDA(cudaGetLastError());
-  return WARPIR_OK;
-}
-
 // 128-key blocks, two Q tiles taking turns on the tensor core (attn_fwd_wide_sm100.cuh).
 template <int D, bool CAUSAL>
 int launch_attn_wide_cfg(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const wir::AttnParams& p,
@@ -382,43 +373,11 @@ int launch_attn_wide_cfg(const CUtensorMap& tq, const CUtensorMap& tk, const CUt
   return WARPIR_OK;
 }
 
-// Head dimension 128 on CTA pairs (attn_fwd_pair_sm100.cuh): clusters of two CTAs, four Q tiles each.
-template <bool CAUSAL>
-int launch_attn_pair_cfg(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const wir::AttnParams& p,
-                         cudaStream_t stream) {
-  auto kernel = wir::attn_fwd_pair_sm100<CAUSAL>;
-  constexpr int smem = wir::AttnPairSmem::kDynamicBytes;
-  static_assert(smem <= 232448, "shared memory limit per CTA");
-  static_assert(smem > 116 * 1024, "one CTA per SM is what keeps the tensor-memory allocation from blocking");
-  if (int rc = opt_in_smem(reinterpret_cast<const void*>(kernel), smem)) return rc;
-  const int clusters = (p.S + 4 * wir::kAttnBQ - 1) / (4 * wir::kAttnBQ);
-  dim3 grid(2 * clusters, p.H, p.B);
-  kernel<<<grid, wir::kAttnThreads, smem, stream>>>(tq, tk, tv, p);
-  WIR_CUDA(cudaGetLastError());
-  return WARPIR_OK;
-}
-
-// WARPIR_ATTN_WIDE=0|1 and WARPIR_ATTN_SPLIT=0|1 override the choice of the 128-key forward and of the
-// forward with two softmax warpgroups per tile (read once per process).
+// WARPIR_ATTN_WIDE=0|1 overrides the choice between the 64-key and the 128-key forward (read once per process).
 inline int env_attn_wide() {
   static const int v = [] {
     const char* e = getenv("WARPIR_ATTN_WIDE");
     return e ? (atoi(e) != 0 ? 1 : 0) : -1;
-  }();
-  return v;
-}
-inline int env_attn_split() {
-  static const int v = [] {
-    const char* e = getenv("WARPIR_ATTN_SPLIT");
-    return e ? (atoi(e) != 0 ? 1 : 0) : -1;
-  }();
-  return v;
-}
-// WARPIR_ATTN_PAIR=0|1 overrides the choice between the single-CTA and the CTA-pair forward.
-inline int env_attn_pair() {
-  static const int v = [] {
-    const char* e = getenv("WARPIR_ATTN_PAIR");
-    return e ? atoi(e) : -1;
   }();
   return v;
 }
@@ -429,9 +388,8 @@ inline int attn_impl(const void* Q, const void* K, const void* V, void* O, float
   g_last_error[0] = 0;
   if (B < 0 || Hq < 0 || Hkv < 0 || S < 0) return fail(WARPIR_EINVAL, "negative size");
   if (D != 64 && D != 128) return fail(WARPIR_ESHAPE, "D = %lld: head dimension must be 64 or 128", (long long)D);
-  if (variant < 0 || variant > 4)
-    return fail(WARPIR_EINVAL, "variant must be 0 (choose), 1 (one softmax warpgroup per tile), 2 (CTA pairs), 3 (two softmax warpgroups per tile) or 4 (128-key blocks)");
-  if (variant == 2 && D != 128) return fail(WARPIR_ESHAPE, "the CTA-pair kernel covers head dimension 128 only");
+  if (variant != 0 && variant != 1 && variant != 4)
+    return fail(WARPIR_EINVAL, "variant must be 0 (choose), 1 (64-key blocks) or 4 (128-key blocks)");
   if (B == 0 || Hq == 0 || S == 0) return WARPIR_OK;
   if (Hkv <= 0 || Hq % Hkv != 0) return fail(WARPIR_ESHAPE, "Hq = %lld must be a positive multiple of Hkv = %lld", (long long)Hq, (long long)Hkv);
   if (!(softmax_scale > 0.f) || !std::isfinite(softmax_scale)) return fail(WARPIR_EINVAL, "softmax_scale must be positive and finite");
@@ -475,17 +433,6 @@ inline int attn_impl(const void* Q, const void* K, const void* V, void* O, float
   p.status = dev->status;
   p.trace = g_trace;
   p.stagger_clocks = env_attn_stagger();
-  bool pair = false;                                        // default: the single-CTA kernel
-  if (env_attn_pair() >= 0) pair = (D == 128) && env_attn_pair() != 0;
-  if (variant != 0) pair = (variant == 2);
-  if (pair) {
-    CUtensorMap tk_half;   // a CTA loads half the keys of a K block
-    const uint64_t dims[3] = {static_cast<uint64_t>(D), static_cast<uint64_t>(S), static_cast<uint64_t>(B * Hkv)};
-    const uint64_t strides[2] = {static_cast<uint64_t>(D) * 2, static_cast<uint64_t>(S) * D * 2};
-    const uint32_t box_k[3] = {64, 32, 1};
-    if (int rc = make_tmap(&tk_half, K, 3, dims, strides, box_k)) return rc;
-    return causal ? launch_attn_pair_cfg<true>(tq, tk_half, tv, p, stream) : launch_attn_pair_cfg<false>(tq, tk_half, tv, p, stream);
-  }
   // Measured (TFLOP/s, 128-key kernel vs 64-key kernel): without a causal mask 1177 vs 1134 at head
   // dimension 128 and 635 vs 581-616 at 64; with one 1052-1104 vs 1123 and 550 vs 607 (the tiles of a
   // CTA end a block apart and a 128-key diagonal block is masked whole).  So the mask decides.
@@ -500,13 +447,6 @@ inline int attn_impl(const void* Q, const void* K, const void* V, void* O, float
     if (int rc = make_tmap(&tv128, V, 3, dims, strides, box)) return rc;
     if (D == 128) return causal ? launch_attn_wide_cfg<128, true>(tq, tk128, tv128, p, stream) : launch_attn_wide_cfg<128, false>(tq, tk128, tv128, p, stream);
     return causal ? launch_attn_wide_cfg<64, true>(tq, tk128, tv128, p, stream) : launch_attn_wide_cfg<64, false>(tq, tk128, tv128, p, stream);
-  }
-  bool split = false;
-  if (env_attn_split() >= 0) split = env_attn_split() != 0;
-  if (variant != 0) split = (variant == 3);
-  if (split) {
-    if (D == 128) return causal ? launch_attn_split_cfg<128, true>(tq, tk, tv, p, stream) : launch_attn_split_cfg<128, false>(tq, tk, tv, p, stream);
-    return causal ? launch_attn_split_cfg<64, true>(tq, tk, tv, p, stream) : launch_attn_split_cfg<64, false>(tq, tk, tv, p, stream);
   }
   if (D == 128) return causal ? launch_attn_cfg<128, true>(tq, tk, tv, p, stream) : launch_attn_cfg<128, false>(tq, tk, tv, p, stream);
   return causal ? launch_attn_cfg<64, true>(tq, tk, tv, p, stream) : launch_attn_cfg<64, false>(tq, tk, tv, p, stream);

@@ -79,5 +79,20 @@ def format_table(rows: List[Dict[str, float]]) -> str:
     return "\n".join(lines)
 
 
+def factor_matrix(device: int = 0) -> str:
+    """What slows a stream of MMAs down: every combination of the three kinds of background load and a
+    tcgen05.commit after every eight MMAs, for the two narrow widths, shared- and tensor-memory A."""
+    import itertools
+    lines = ["| form | N | tmem ld/st | TMA loads | arithmetic | commit every 8 MMAs | clocks / MMA |", "|---|---|---|---|---|---|---|"]
+    for ts in (False, True):
+        for n in (128, 64):
+            for tmem, tma, alu, com in itertools.product((False, True), repeat=4):
+                r = mma_rate(n, ts, False, bg_tmem=tmem, bg_tma=tma, bg_alu=alu, commit_every=2 if com else 0, device=device)
+                yn = lambda b: "yes" if b else "-"
+                lines.append(f"| {'TS' if ts else 'SS'} | {n} | {yn(tmem)} | {yn(tma)} | {yn(alu)} | {yn(com)} | {r['clocks_per_mma']:.1f} |")
+    return "\n".join(lines)
+
+
 if __name__ == "__main__":
-    print(format_table(sweep()))
+    import sys
+    print(factor_matrix() if "--matrix" in sys.argv else format_table(sweep()))

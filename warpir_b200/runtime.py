@@ -12,6 +12,7 @@ library, or without an sm_100 GPU, every entry point raises.
 from __future__ import annotations
 
 import ctypes
+import os
 import math
 import threading
 from pathlib import Path
@@ -51,11 +52,14 @@ def load_library() -> ctypes.CDLL:
     with _lock:
         if _lib is not None:
             return _lib
-        if not _LIB_PATH.exists():
+        # WARPIR_B200_LIBRARY names another build of the same library (a debug build with event
+        # traces, a measurement build); it must export the same ABI
+        path = Path(os.environ["WARPIR_B200_LIBRARY"]).resolve() if os.environ.get("WARPIR_B200_LIBRARY") else _LIB_PATH
+        if not path.exists():
             raise FileNotFoundError(
-                f"{_LIB_PATH} is missing: build it with `python -m warpir_b200.build` "
+                f"{path} is missing: build it with `python -m warpir_b200.build` "
                 "(there is no fallback path)")
-        lib = ctypes.CDLL(str(_LIB_PATH))
+        lib = ctypes.CDLL(str(path))
         vp, i64, ci, cf = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int, ctypes.c_float
         lib.warpir_abi_version.restype = ci
         lib.warpir_abi_version.argtypes = []
@@ -173,9 +177,8 @@ def launch_attention(Q, K, V, O, LSE=None, softmax_scale: Optional[float] = None
     with ``[N, D]`` tensors (tests/test_modal_attention.py:25-39) as well as
     ``[B, H, S, D]`` tensors with grouped KV heads; ``LSE`` (fp32 ``[B, H, S]``
     or ``[N]``) is filled when given.  Scale defaults to ``1/sqrt(D)``.
-    ``variant``: 0 lets the library choose, 1 forces the single-CTA kernel, 2 the CTA-pair
-    kernel (head dimension 128 only), 3 the kernel with two softmax warpgroups per Q tile, 4 the kernel with 128-key blocks
-    (the library's own choice without a causal mask; with one it is 1).
+    ``variant``: 0 lets the library choose, 1 forces the kernel with 64-key blocks, 4 the kernel with
+    128-key blocks (the library's own choice without a causal mask; with one it is 1).
     """
     import torch
     lib = load_library()
