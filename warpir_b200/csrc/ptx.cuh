@@ -113,6 +113,7 @@ __device__ __forceinline__ void report_error(const AbortCtx& ctx, int code, int 
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const AbortCtx& ctx,
                                           int role, int tag, int detail) {
   if (mbar_test_wait(bar, parity)) return true;
+  if (*ctx.flag) return false;      // the CTA is already giving up: do not start another wait
   uint64_t t0 = 0;
   for (uint32_t poll = 0; poll < kWaitPolls; ++poll) {
     if (mbar_try_wait(bar, parity)) return true;
