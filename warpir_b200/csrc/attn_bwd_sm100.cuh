@@ -31,10 +31,13 @@
 // Tensor memory: T0[2] at columns 0 / 64, T1[2] at 128 / 192 (double-buffered so stage 1
 // of step it+1 runs while the compute warps work on step it), acc0 at 256, acc1 at
 // 256 + D.  Warp 0 is the TMA producer, warp 1 issues every MMA (whole warp, one elected
-// lane), warps 2-9 are two compute warpgroups: thread = one tensor-memory lane (row), and the
-// two groups split the 64 columns of T0 / T1 between them (there is no row reduction in the
-// backward, so the split needs no exchange; two warps per scheduler hide each other's
-// tensor-memory and exponential latencies).
+// lane), warps 2-9 are two compute warpgroups: thread = one tensor-memory lane (row).  The
+// groups take the steps in turn (group g the steps of parity g, which are the steps of score
+// buffer g), each doing all 64 columns of its step in two passes of 32.  That keeps the groups
+// out of phase: while one waits for its scores, loads them or hands P / dS over, the other is
+// in its arithmetic, so the exponential and conversion units (the compute warps' bottleneck)
+// stay busy.  With both groups on the same step (splitting its columns) every one of those
+// waits was paid once per step by all eight warps at once.
 // MMAs execute in issue order, which makes the aliasing safe: stage 1 of step it+2
 // overwrites T0/T1[b] only after stage 2 of step it, which reads P/dS from them.
 #pragma once
@@ -72,8 +75,8 @@ struct AttnBwdSmem {
   static constexpr int kYChunkBytes = kBwdBY * 128;
   static constexpr int kYTileBytes = (D / 64) * kYChunkBytes;
   static constexpr int kYOffset = DKV ? 2 * kXTileBytes : 0;
-  static constexpr int kStatsOffset = kYOffset + kStages * 2 * kYTileBytes;   // [2 buffers][2 vectors][64] floats
-  static constexpr int kBarOffset = kStatsOffset + 2 * 2 * kBwdBY * 4;
+  static constexpr int kStatsOffset = kYOffset + kStages * 2 * kYTileBytes;   // [2 groups][2 buffers][2 vectors][64] floats
+  static constexpr int kBarOffset = kStatsOffset + 2 * 2 * 2 * kBwdBY * 4;
   // x_full, y_full[S], y_empty[S], t_full[2], pds_full[2], acc_done, drain
   static constexpr int kNumBars = 1 + 2 * kStages + 6;
   static constexpr int kTmemPtrOffset = kBarOffset + kNumBars * 8;
@@ -161,7 +164,7 @@ attn_bwd_sm100(const __grid_constant__ CUtensorMap tmap_x0, const __grid_constan
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(t_full(b), 1);
-      mbar_init(pds_full(b), kBwdComputeThreads);
+      mbar_init(pds_full(b), kBwdComputeThreads / 2);   // the one warpgroup that owns buffer b
     }
     mbar_init(acc_done, 1);
     mbar_init(drain_bar, 1);
@@ -267,7 +270,9 @@ attn_bwd_sm100(const __grid_constant__ CUtensorMap tmap_x0, const __grid_constan
           mma_ts_elect_x4(tmem_base + kAccCol, ds_tmem, y0d, y0d + 128, y0d + 256, y0d + 384, idesc_acc, acc);
         }
       }
-      mma_commit_elect(y_empty(it % STAGES));
+      // No commit for the ring slot here: a tcgen05.commit holds the issuing thread for a few hundred clocks
+      // while the tensor core's short queue drains, so a step has exactly one (stage 1's, below).  That commit
+      // also covers this step's stage 2, and the compute warps, who wait for it anyway, release the slot.
       if (it + 1 == n_it) mma_commit_elect(acc_done);
       if (lane == 0) WIR_TRACE_EVENT(p.trace, 0, 2, it);
       if (it + 2 < n_it) ok = stage1(it + 2);
@@ -281,7 +286,7 @@ attn_bwd_sm100(const __grid_constant__ CUtensorMap tmap_x0, const __grid_constan
   } else {
     // ------------------------------------------------------------------ compute warps
     const int quarter = warp & 3;                       // tensor-memory lanes 32*quarter .. +31
-    const int half = (warp - 2) >> 2;                   // which 32 of the 64 columns of T0 / T1
+    const int half = (warp - 2) >> 2;                   // warpgroup: takes the steps of this parity (score buffer `half`)
     const int tid = quarter * 32 + lane;                // row of the resident tiles owned by this thread
     const int x_row = x_row0 + tid;
     const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
@@ -290,6 +295,7 @@ attn_bwd_sm100(const __grid_constant__ CUtensorMap tmap_x0, const __grid_constan
     bool ok = true;
     WIR_TRACE_DECL;
     const bool traced = (quarter == 0 && lane == 0);
+    if (traced) WIR_TRACE_EVENT(p.trace, 1 + half, 90, 0);     // set-up done, prologue starts
 
     // per-row statistics (DKV = false): L2 = LSE log2 e, ds = delta * scale; delta is computed here
     float row_l2 = 0.f, row_ds = 0.f;
@@ -334,38 +340,39 @@ attn_bwd_sm100(const __grid_constant__ CUtensorMap tmap_x0, const __grid_constan
       mbar_arrive(x_full);
     }
 
-    // DKV: the 64 per-column statistics of a Q tile are staged in shared memory by one warpgroup
-    // (threads 0-63 LSE, 64-127 delta), fetched from global memory one step ahead so that the
-    // round trip is off the critical path
+    // DKV: the 64 per-column statistics (LSE, delta) of a step's Q tile are staged in shared memory by the
+    // warpgroup that owns the step (threads 0-63 LSE, 64-127 delta), fetched from global memory one of its
+    // steps ahead so that the round trip is off the critical path
     auto fetch_stat = [&](int it) -> float {
       const int q = y_tile_of(it) * kBwdBY + (tid & 63);
       const size_t r = static_cast<size_t>(y_plane_of(it)) * p.S + min(q, p.S - 1);
       return (tid < 64) ? p.LSE[r] * kLog2e : p.delta[r] * p.scale;
     };
     float stat_next = 0.f;
-    if (DKV && half == 0 && n_it > 0) stat_next = fetch_stat(0);
+    if (DKV && half < n_it) stat_next = fetch_stat(half);
 
-    for (int it = 0; it < n_it; ++it) {
-      const int b = it & 1;
+    const int b = half;                                   // this group's score buffer
+    for (int it = half; it < n_it; it += 2) {
       const int y_row0 = y_tile_of(it) * kBwdBY;
-      float* st = stats + b * 2 * kBwdBY;
+      // the group's own double buffer: every warp of the group has passed the previous step's barrier, hence
+      // finished reading this buffer two steps ago
+      float* st = stats + (half * 2 + ((it >> 1) & 1)) * 2 * kBwdBY;
       if constexpr (DKV) {
-        if (half == 0) st[tid] = stat_next;
-        asm volatile("bar.sync 2, 256;" ::: "memory");
-        if (half == 0 && it + 1 < n_it) stat_next = fetch_stat(it + 1);
+        st[tid] = stat_next;
+        if (it + 2 < n_it) stat_next = fetch_stat(it + 2);
       }
       if (traced) WIR_TRACE_EVENT(p.trace, 1 + half, 10, it);
       const bool got = mbar_wait(t_full(b), (it >> 1) & 1, ctx, kRoleSoftmax, b, it);
       if (DKV) {
-        // the compute warps meet at a named barrier every step, so they must agree on going on
+        // the group's warps meet at a named barrier every step (it also publishes st), so they must agree on going on
         uint32_t all;
         asm volatile(
             "{\n\t.reg .pred a, q;\n\t"
             "setp.ne.u32 q, %1, 0;\n\t"
-            "bar.red.and.pred a, 3, 256, q;\n\t"
+            "bar.red.and.pred a, %2, 128, q;\n\t"
             "selp.u32 %0, 1, 0, a;\n\t}"
             : "=r"(all)
-            : "r"(got ? 1u : 0u)
+            : "r"(got ? 1u : 0u), "r"(2 + half)
             : "memory");
         if (all == 0) { ok = false; break; }
       } else if (!__all_sync(0xffffffffu, got)) {
@@ -373,46 +380,70 @@ attn_bwd_sm100(const __grid_constant__ CUtensorMap tmap_x0, const __grid_constan
         break;
       }
       tc_fence_after();
-
+      // stage 1 of this step was committed after stage 2 of step it - 2: that step's ring slot is free
+      if (it >= 2 && tid == 0) mbar_arrive(y_empty((it - 2) % STAGES));
       if (traced) WIR_TRACE_EVENT(p.trace, 1 + half, 11, it);
-      uint32_t t0[32], t1[32];
-      tmem_ld32(lane_base + b * 64 + half * 32, t0);
-      tmem_ld32(lane_base + 128 + b * 64 + half * 32, t1);
-      tmem_wait_ld();
-      if (traced) WIR_TRACE_EVENT(p.trace, 1 + half, 12, it);
+#if defined(WIR_BWD_ABLATE) && WIR_BWD_ABLATE == 3   // measurement build 3: the compute warps only pass the hand-offs on
+      mbar_arrive(pds_full(b));
+      continue;
+#endif
 
       // masks are only needed on tiles that touch the diagonal or the end of the sequence
       const bool ragged = (y_row0 + kBwdBY > p.S) || (x_row0 + kBwdBX > p.S);
       const bool diagonal = CAUSAL && (DKV ? (y_row0 < x_row0 + kBwdBX) : (y_row0 + kBwdBY > x_row0));
       const bool masked = ragged || diagonal;
-      uint32_t pk[16], dk[16];
+#pragma unroll 1
+      for (int pass = 0; pass < 2; ++pass) {              // 32 of the 64 columns of T0 / T1 at a time
+        uint32_t t0[32], t1[32];
+        tmem_ld32(lane_base + b * 64 + pass * 32, t0);
+        tmem_ld32(lane_base + 128 + b * 64 + pass * 32, t1);
+        tmem_wait_ld();
+        if (traced) WIR_TRACE_EVENT(p.trace, 1 + half, 12, it);
+        uint32_t pk[16], dk[16];
+#if defined(WIR_BWD_ABLATE) && WIR_BWD_ABLATE == 1    // measurement build 1: tensor-memory traffic as is, no arithmetic
 #pragma unroll
-      for (int i = 0; i < 16; ++i) {
-        float pv[2], dv[2];
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          const int col = half * 32 + 2 * i + h;        // column of T0 / T1
-          const float l2 = DKV ? st[col] : row_l2;
-          const float dsc = DKV ? st[kBwdBY + col] : row_ds;
-          float pe = ex2_approx(fmaf(__uint_as_float(t0[2 * i + h]), c, -l2));
-          if (masked) {
-            const int y = y_row0 + col;                 // index along the streamed tile
-            const int qi = DKV ? y : x_row;             // query index
-            const int ki = DKV ? x_row : y;             // key index
-            if (qi >= p.S || ki >= p.S || (CAUSAL && ki > qi)) pe = 0.f;
-          }
-          pv[h] = pe;
-          dv[h] = pe * fmaf(__uint_as_float(t1[2 * i + h]), p.scale, -dsc);
+        for (int i = 0; i < 16; ++i) {
+          pk[i] = t0[2 * i] & 0x3f003f00u;
+          dk[i] = t1[2 * i] & 0x3f003f00u;
         }
-        pk[i] = pack_bf16(pv[0], pv[1]);
-        dk[i] = pack_bf16(dv[0], dv[1]);
+#else
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          float pv[2], dv[2];
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            const int col = pass * 32 + 2 * i + h;        // column of T0 / T1
+            const float l2 = DKV ? st[col] : row_l2;
+            const float dsc = DKV ? st[kBwdBY + col] : row_ds;
+#if defined(WIR_BWD_ABLATE) && WIR_BWD_ABLATE == 4    // measurement build 4: no exponentials
+            float pe = fmaf(__uint_as_float(t0[2 * i + h]), c, -l2);
+#else
+            float pe = ex2_approx(fmaf(__uint_as_float(t0[2 * i + h]), c, -l2));
+#endif
+            if (masked) {
+              const int y = y_row0 + col;                 // index along the streamed tile
+              const int qi = DKV ? y : x_row;             // query index
+              const int ki = DKV ? x_row : y;             // key index
+              if (qi >= p.S || ki >= p.S || (CAUSAL && ki > qi)) pe = 0.f;
+            }
+            pv[h] = pe;
+            dv[h] = pe * fmaf(__uint_as_float(t1[2 * i + h]), p.scale, -dsc);
+          }
+#if defined(WIR_BWD_ABLATE) && WIR_BWD_ABLATE == 5    // measurement build 5: bf16 by truncation (a byte permute), no conversions
+          pk[i] = __byte_perm(__float_as_uint(pv[0]), __float_as_uint(pv[1]), 0x7632);
+          dk[i] = __byte_perm(__float_as_uint(dv[0]), __float_as_uint(dv[1]), 0x7632);
+#else
+          pk[i] = pack_bf16(pv[0], pv[1]);
+          dk[i] = pack_bf16(dv[0], dv[1]);
+#endif
+        }
+#endif
+        // Packed bf16: a pass's 32 values fill 16 columns.  The 32 packed columns sit at columns 16..47 of
+        // the buffer, so each pass overwrites only columns that have been read already (pass 0 read 0..31
+        // and writes 16..31, pass 1 read 32..63 and writes 32..47).
+        if constexpr (DKV) tmem_st16(lane_base + b * 64 + 16 + pass * 16, pk);
+        tmem_st16(lane_base + 128 + b * 64 + 16 + pass * 16, dk);
       }
-      // Packed bf16: this group's 32 values fill 16 columns.  The 32 packed columns sit at
-      // columns 16..47 of the buffer, so each group overwrites only columns it has read itself
-      // (group 0 read 0..31 and writes 16..31, group 1 read 32..63 and writes 32..47) and the
-      // groups need no barrier between their loads and stores.
-      if constexpr (DKV) tmem_st16(lane_base + b * 64 + 16 + half * 16, pk);
-      tmem_st16(lane_base + 128 + b * 64 + 16 + half * 16, dk);
       if (traced) WIR_TRACE_EVENT(p.trace, 1 + half, 13, it);
       tmem_wait_st();
       tc_fence_before();
@@ -422,6 +453,7 @@ attn_bwd_sm100(const __grid_constant__ CUtensorMap tmap_x0, const __grid_constan
 
     if (ok && n_it > 0) {
       const bool got = mbar_wait(acc_done, 0, ctx, kRoleEpilogue, 0, n_it);
+      if (traced) WIR_TRACE_EVENT(p.trace, 1 + half, 92, 0);   // accumulators complete
       if (__all_sync(0xffffffffu, got)) {
         tc_fence_after();
         const bool live = x_row < p.S;
@@ -456,6 +488,12 @@ attn_bwd_sm100(const __grid_constant__ CUtensorMap tmap_x0, const __grid_constan
 
   tc_fence_before();
   __syncthreads();
+#ifdef WIR_TRACE
+  if (threadIdx.x == 64) {
+    WIR_TRACE_DECL;
+    WIR_TRACE_EVENT(p.trace, 3, 93, 0);   // epilogue done (its own region: this thread's counter starts anew)
+  }
+#endif
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, kTmemCols);

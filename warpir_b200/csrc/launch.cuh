@@ -433,10 +433,10 @@ inline int attn_impl(const void* Q, const void* K, const void* V, void* O, float
   p.status = dev->status;
   p.trace = g_trace;
   p.stagger_clocks = env_attn_stagger();
-  // Measured (TFLOP/s, 128-key kernel vs 64-key kernel): without a causal mask 1177 vs 1134 at head
-  // dimension 128 and 635 vs 581-616 at 64; with one 1052-1104 vs 1123 and 550 vs 607 (the tiles of a
-  // CTA end a block apart and a 128-key diagonal block is masked whole).  So the mask decides.
-  bool wide = !causal;
+  // Measured (sustained TFLOP/s, 128-key kernel vs 64-key kernel): without a causal mask 1077 vs 1077 at head
+  // dimension 128 and 706 vs 659 at 64; with one 1005 vs 1044 at 128 (the tiles of a CTA end a block apart and
+  // a 128-key diagonal block is masked whole) and 660 vs 644 at 64.
+  bool wide = !causal || D == 64;
   if (env_attn_wide() >= 0) wide = env_attn_wide() != 0;
   if (variant != 0) wide = (variant == 4);
   if (wide) {
@@ -524,8 +524,8 @@ inline int attn_bwd_impl(const void* Q, const void* K, const void* V, const void
   if (D == 128) rc = c ? launch_attn_bwd_cfg<128, true, false>(q_x, g_x, k_y, v_y, p, stream) : launch_attn_bwd_cfg<128, false, false>(q_x, g_x, k_y, v_y, p, stream);
   else rc = c ? launch_attn_bwd_cfg<64, true, false>(q_x, g_x, k_y, v_y, p, stream) : launch_attn_bwd_cfg<64, false, false>(q_x, g_x, k_y, v_y, p, stream);
   if (rc) return rc;
-#ifdef WIR_TRACE
-  if (getenv("WARPIR_BWD_DQ_ONLY")) return rc;   // debug builds: keep the first launch's trace
+#if defined(WIR_TRACE) || defined(WIR_BWD_ABLATE)
+  if (getenv("WARPIR_BWD_DQ_ONLY")) return rc;   // debug and measurement builds: the first launch alone
 #endif
   // 2: dV and dK per K/V tile, streaming Q and dO of the head group
   p.out0 = dV;
