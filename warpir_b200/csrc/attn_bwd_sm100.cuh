@@ -214,15 +214,23 @@ attn_bwd_sm100(const __grid_constant__ CUtensorMap tmap_x0, const __grid_constan
     constexpr uint32_t desc_hi = smem_desc_hi_sw128(1024);
     const uint32_t x0_lo = smem_desc_lo(smem_base, 16);
     const uint32_t x1_lo = smem_desc_lo(smem_base + L::kXTileBytes, 16);
-    auto y_addr = [&](int it) { return smem_base + L::kYOffset + (it % STAGES) * 2 * L::kYTileBytes; };
+    // Ring position (slot, phase parity) of a step's streamed tiles, carried along by additions: the issuing
+    // warp takes 6-12 clocks over every dependent instruction, and `it % STAGES`, `it / STAGES` with six or
+    // twelve stages are a dozen of them each.
+    struct RingPos { uint32_t slot, phase; };
+    auto ring_next = [](RingPos r) {
+      if (++r.slot == static_cast<uint32_t>(STAGES)) { r.slot = 0; r.phase ^= 1u; }
+      return r;
+    };
+    auto y_addr = [&](RingPos r) { return smem_base + L::kYOffset + r.slot * (2 * L::kYTileBytes); };
+    auto wait_y = [&](RingPos r, int it) { return mbar_wait_warp(y_full(r.slot), r.phase, ctx, kRoleMma, 10, it); };
     bool ok = true;
     WIR_TRACE_DECL;
-    auto stage1 = [&](int it) -> bool {
-      if (!mbar_wait_warp(y_full(it % STAGES), (it / STAGES) & 1, ctx, kRoleMma, 10, it)) return false;
-      tc_fence_after();
+    // stage 1 of step `it`, whose streamed tiles (ring position r) have landed
+    auto stage1 = [&](int it, RingPos r) {
       const int b = it & 1;
-      const uint32_t y0_lo = smem_desc_lo(y_addr(it), 16);
-      const uint32_t y1_lo = smem_desc_lo(y_addr(it) + L::kYTileBytes, 16);
+      const uint32_t y0_lo = smem_desc_lo(y_addr(r), 16);
+      const uint32_t y1_lo = smem_desc_lo(y_addr(r) + L::kYTileBytes, 16);
       // groups of four k-steps (one 64-column chunk of the head dimension: 32 bytes per step)
 #pragma unroll
       for (int c4 = 0; c4 < D / 64; ++c4) {
@@ -241,22 +249,36 @@ attn_bwd_sm100(const __grid_constant__ CUtensorMap tmap_x0, const __grid_constan
         }
       }
       mma_commit_elect(t_full(b));
-      return true;
     };
 
     if (n_it > 0) ok = mbar_wait_warp(x_full, 0, ctx, kRoleMma, 1, 0);
     tc_fence_after();
-    for (int it = 0; ok && it < 2 && it < n_it; ++it) ok = stage1(it);
+    RingPos cur{0u, 0u}, ahead{0u, 0u};      // positions of step it and of step it + 2
+    for (int it = 0; ok && it < 2 && it < n_it; ++it) {
+      ok = wait_y(ahead, it);
+      if (ok) {
+        tc_fence_after();
+        stage1(it, ahead);
+      }
+      ahead = ring_next(ahead);
+    }
+    if (n_it == 1) ahead = ring_next(ahead);
     for (int it = 0; ok && it < n_it; ++it) {
       const int b = it & 1;
+      const bool more = it + 2 < n_it;
+      // The tiles of step it + 2 were asked for some steps ago.  Their barrier is tested here, before the one
+      // wait that is a true dependency (a look at a barrier costs the issuing warp 75-150 clocks even when it is
+      // long complete, and the tensor core's queue is about four MMAs deep); only if they have not landed yet
+      // is there a wait between the two stages.
+      const bool landed = !more || __all_sync(0xffffffffu, mbar_test_wait(y_full(ahead.slot), ahead.phase));
       if (lane == 0) WIR_TRACE_EVENT(p.trace, 0, 0, it);
       if (!mbar_wait_warp(pds_full(b), (it >> 1) & 1, ctx, kRoleMma, 20, it)) { ok = false; break; }
       tc_fence_after();
       if (lane == 0) WIR_TRACE_EVENT(p.trace, 0, 1, it);
       // as B operands the streamed tiles are read with the 64 tile rows as K: chunks of 64
       // columns kYChunkBytes apart, 16 rows (2048 bytes) per k-step
-      const uint32_t y0_mn = smem_desc_lo(y_addr(it), L::kYChunkBytes);
-      const uint32_t y1_mn = smem_desc_lo(y_addr(it) + L::kYTileBytes, L::kYChunkBytes);
+      const uint32_t y0_mn = smem_desc_lo(y_addr(cur), L::kYChunkBytes);
+      const uint32_t y1_mn = smem_desc_lo(y_addr(cur) + L::kYTileBytes, L::kYChunkBytes);
       const uint32_t p_tmem = tmem_base + b * 64 + 16;          // bf16 P inside T0[b]
       const uint32_t ds_tmem = tmem_base + 128 + b * 64 + 16;   // bf16 dS inside T1[b]
       {
@@ -270,13 +292,17 @@ attn_bwd_sm100(const __grid_constant__ CUtensorMap tmap_x0, const __grid_constan
           mma_ts_elect_x4(tmem_base + kAccCol, ds_tmem, y0d, y0d + 128, y0d + 256, y0d + 384, idesc_acc, acc);
         }
       }
-      // No commit for the ring slot here: a tcgen05.commit holds the issuing thread for a few hundred clocks
-      // while the tensor core's short queue drains, so a step has exactly one (stage 1's, below).  That commit
-      // also covers this step's stage 2, and the compute warps, who wait for it anyway, release the slot.
+      // No commit for the ring slot here: a step has exactly one commit (stage 1's, below, which also covers
+      // this stage 2), and the compute warps, who wait for it anyway, release the slot.
       if (it + 1 == n_it) mma_commit_elect(acc_done);
       if (lane == 0) WIR_TRACE_EVENT(p.trace, 0, 2, it);
-      if (it + 2 < n_it) ok = stage1(it + 2);
+      if (more) {
+        if (!landed && !wait_y(ahead, it + 2)) { ok = false; break; }
+        stage1(it + 2, ahead);
+      }
       if (lane == 0) WIR_TRACE_EVENT(p.trace, 0, 3, it);
+      cur = ring_next(cur);
+      ahead = ring_next(ahead);
     }
     if (!ok || *abort_flag) {
       mma_commit_elect(drain_bar);

@@ -121,9 +121,7 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
   const int n0 = (qt0 * kAttnBQ >= p.S) ? 0 : (CAUSAL ? min(nkv, 2 * qt0 + 2) : nkv);
   const int n1 = (qt1 * kAttnBQ >= p.S) ? 0 : (CAUSAL ? min(nkv, 2 * qt1 + 2) : nkv);
   const int n_max = max(n0, n1);
-  // position of K(j) / V(j) in the load sequence K0, K1, V0, K2, V1, K3, ...
-  auto k_index = [&](int j) -> uint32_t { return j == 0 ? 0u : static_cast<uint32_t>(2 * j - 1); };
-  auto v_index = [&](int j) -> uint32_t { return static_cast<uint32_t>(j + 1 < n_max ? 2 * j + 2 : 2 * j + 1); };
+  // load sequence of the K/V ring: K0, K1, V0, K2, V1, K3, ... (K(j) is tile 2j - 1, V(j) tile 2j + 2, the last V tile 2j + 1)
 
   // Producer state (one lane of the producer warp).  That lane also initialises the barriers and
   // issues the loads of Q and of the first K block before the CTA-wide barrier below, so their
@@ -212,23 +210,34 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
     const uint32_t q_lo = smem_desc_lo(smem_base + L::kQOffset + t * L::kQTileBytes, 16);
     const uint32_t o_tmem = tmem_base + kOCol + t * D;
     bool ok = true;
-    auto kv_addr = [&](uint32_t idx) { return smem_base + L::kKVOffset + (idx % STAGES) * L::kKVTileBytes; };
-    auto wait_kv = [&](uint32_t idx, int tag) {
-      return mbar_wait_warp(kv_full(idx % STAGES), (idx / STAGES) & 1, ctx, kRoleMma, tag, idx);
+    // Where a tile of the load sequence K0, K1, V0, K2, V1, K3, ... sits in the ring: slot and phase parity,
+    // carried along by additions.  (index % STAGES and index / STAGES with ten or twelve stages are a dozen
+    // dependent instructions each, several times per step, and the issuing warp takes 6-12 clocks over every
+    // dependent instruction: more than the MMAs of a step last.)
+    struct RingPos { uint32_t slot, phase; };
+    auto ring_next = [](RingPos r, uint32_t by) {
+      r.slot += by;
+      if (r.slot >= static_cast<uint32_t>(STAGES)) { r.slot -= STAGES; r.phase ^= 1u; }
+      return r;
     };
+    auto ring_prev = [](RingPos r) {
+      if (r.slot == 0) { r.slot = STAGES - 1; r.phase ^= 1u; } else { --r.slot; }
+      return r;
+    };
+    auto kv_addr = [&](RingPos r) { return smem_base + L::kKVOffset + r.slot * L::kKVTileBytes; };
+    auto wait_kv = [&](RingPos r, int tag) { return mbar_wait_warp(kv_full(r.slot), r.phase, ctx, kRoleMma, tag, r.slot); };
     // every K/V slot is released by BOTH issuers (its empty barrier counts two arrivals); the
     // issuer whose tile does not visit a block releases it once the block has landed
-    auto skip_tile = [&](uint32_t idx) -> bool {
-      if (!wait_kv(idx, 40 + t)) return false;
-      mbar_arrive_elect(kv_empty(idx % STAGES));
+    auto skip_tile = [&](RingPos r) -> bool {
+      if (!wait_kv(r, 40 + t)) return false;
+      mbar_arrive_elect(kv_empty(r.slot));
       return true;
     };
     // S_t[j & 1] = Q_t K(j)^T, four MMAs (one 64-element chunk of the head dimension) per instruction
-    // block.  K(j) must have landed (the caller made sure).
+    // block.  K(j), at ring position r, must have landed (the caller made sure).
     const uint64_t qd = desc64(q_lo, desc_hi);
-    auto issue_qk = [&](int j) {
-      const uint32_t idx = k_index(j);
-      const uint64_t kd = desc64(smem_desc_lo(kv_addr(idx), 16), desc_hi);
+    auto issue_qk = [&](int j, RingPos r) {
+      const uint64_t kd = desc64(smem_desc_lo(kv_addr(r), 16), desc_hi);
       const uint32_t d_tmem = tmem_base + t * 128 + (j & 1) * 64;
 #pragma unroll
       for (int c = 0; c < D / 64; ++c) {
@@ -237,50 +246,54 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
                         kd + ko + 6, idesc_qk, c > 0 ? 1u : 0u);
       }
       mma_commit_elect(s_full(t, j & 1));
-      mma_commit_elect(kv_empty(idx % STAGES));
+      mma_commit_elect(kv_empty(r.slot));
     };
     // a block this tile does not visit: release its slot once it has landed
-    auto qk_or_skip = [&](int j) -> bool {
+    auto qk_or_skip = [&](int j, RingPos r) -> bool {
       if (j < n) {
-        if (!wait_kv(k_index(j), 10 + t)) return false;
+        if (!wait_kv(r, 10 + t)) return false;
         tc_fence_after();
-        issue_qk(j);
+        issue_qk(j, r);
         return true;
       }
-      return skip_tile(k_index(j));
+      return skip_tile(r);
     };
 
     if (n > 0) ok = mbar_wait_warp(q_full, 0, ctx, kRoleMma, 1, 0);
-    for (int j = 0; ok && j < 2 && j < n_max; ++j) ok = qk_or_skip(j);
+    for (int j = 0; ok && j < 2 && j < n_max; ++j) ok = qk_or_skip(j, RingPos{static_cast<uint32_t>(j), 0u});   // K0, K1: slots 0, 1
 
+    // V(j) is tile 2j + 2 of the sequence (2j + 1 for the last block, which has no K(j + 1) before it), K(j + 2) tile 2j + 3
+    RingPos vreg{2u, 0u};
     for (int j = 0; ok && j < n_max; ++j) {
-      const uint32_t idx = v_index(j);
+      const RingPos vpos = (j + 1 < n_max) ? vreg : ring_prev(vreg);
+      const RingPos kpos = ring_next(vreg, 1);
+      vreg = ring_next(vreg, 2);
       if (j < n) {
         // The tiles the producer delivers well ahead are made sure of FIRST: a wait costs the issuing warp
         // 75-150 clocks even on a barrier long complete, and the tensor core's queue is about four MMAs deep,
         // so nothing but the fence should stand between P becoming ready and the MMAs that follow it.
-        // (Testing the three barriers together, one vote and one branch, measured 3-4 % slower here; it is
-        // what the 128-key kernel does, where it measured 1 % faster.)
+        // (Testing the three barriers together, one vote and one branch, measured 3-4 % slower here, and the two
+        // ring-slot barriers together 5 % slower; the 128-key kernel tests all three together, 1 % faster there.)
         const bool next_scores = j + 2 < n;
-        if (!wait_kv(idx, 30 + t)) { ok = false; break; }
-        if (next_scores && !wait_kv(k_index(j + 2), 10 + t)) { ok = false; break; }
+        if (!wait_kv(vpos, 30 + t)) { ok = false; break; }
+        if (next_scores && !wait_kv(kpos, 10 + t)) { ok = false; break; }
         if (lane == 0) WIR_TRACE_EVENT(p.trace, 3 * t, 1 + 10 * t, j);
         if (!mbar_wait_warp(p_full(t, j & 1), (j >> 1) & 1, ctx, kRoleMma, 20 + t, j)) { ok = false; break; }
         tc_fence_after();
         if (lane == 0) WIR_TRACE_EVENT(p.trace, 3 * t, 2 + 10 * t, j);
-        const uint64_t vd = desc64(smem_desc_lo(kv_addr(idx), L::kKVChunkBytes), desc_hi);
+        const uint64_t vd = desc64(smem_desc_lo(kv_addr(vpos), L::kKVChunkBytes), desc_hi);
         const uint32_t p_tmem = tmem_base + t * 128 + (j & 1) * 64;
         // 16 keys further: 8 packed-bf16 columns of P, 16 rows (2048 B = 128 descriptor units) of V
         mma_ts_elect_x4(o_tmem, p_tmem, vd, vd + 128, vd + 256, vd + 384, idesc_pv, j > 0 ? 1u : 0u);
         mma_commit_elect(pv_done(t, j & 1));
-        mma_commit_elect(kv_empty(idx % STAGES));
+        mma_commit_elect(kv_empty(vpos.slot));
         if (lane == 0) WIR_TRACE_EVENT(p.trace, 3 * t, 3 + 10 * t, j);
         // S_t[j & 1] is rewritten by the scores of block j + 2: in issue order behind P V(j), which reads P from it
-        if (next_scores) issue_qk(j + 2);
-        else if (j + 2 < n_max) ok = skip_tile(k_index(j + 2));
+        if (next_scores) issue_qk(j + 2, kpos);
+        else if (j + 2 < n_max) ok = skip_tile(kpos);
       } else {
-        ok = skip_tile(idx);
-        if (ok && j + 2 < n_max) ok = qk_or_skip(j + 2);
+        ok = skip_tile(vpos);
+        if (ok && j + 2 < n_max) ok = qk_or_skip(j + 2, kpos);
       }
       if (lane == 0) WIR_TRACE_EVENT(p.trace, 3 * t, 4 + 10 * t, j);
     }

@@ -379,24 +379,40 @@ probe_mma_rate_kernel(const __grid_constant__ CUtensorMap tmap_bg, const ProbePa
     const uint32_t a_tmem = tmem_base + 256;    // TS form: A as 32 packed columns
     __syncwarp();
     const long long t0 = clock64();
-    for (int b = 0; b < p.batches; ++b) {
-      if (p.single) {
-        const uint32_t a_lo = static_cast<uint32_t>(ad), b_lo = static_cast<uint32_t>(bd);
+    // a countdown, not `(b + 1) % commit_every`: a division by a run-time value is some thirty dependent
+    // instructions, which the issuing warp takes 6-12 clocks each over -- more than the MMAs it would
+    // separate last (an earlier version of this probe measured that division and called it the commit's cost)
+    int left = p.commit_every > 0 ? p.commit_every : 0x7fffffff;
+    const uint32_t extra_cluster = PAIR ? mapa_shared(extra_bar, 0) : extra_bar;
+    auto maybe_commit = [&](int) {
+      if (--left == 0) {
+        left = p.commit_every;
+        if (PAIR) mma_commit_pair_elect(extra_cluster);
+        else mma_commit_elect(extra_bar);
+      }
+    };
+    // one loop per form, so that each is as tight as a kernel's own (the choice is not re-made per block)
+    if (p.single) {
+      const uint32_t a_lo = static_cast<uint32_t>(ad), b_lo = static_cast<uint32_t>(bd);
+      for (int b = 0; b < p.batches; ++b) {
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
           if (p.ts) mma_ts_elect(d_tmem, a_tmem + k * 8, b_lo + k * static_cast<uint32_t>(bs), desc_hi, idesc, 1u);
           else mma_ss_elect(d_tmem, a_lo + k * 2, desc_hi, b_lo + k * static_cast<uint32_t>(bs), desc_hi, idesc, 1u);
         }
-      } else if (p.ts) {
+        maybe_commit(b);
+      }
+    } else if (p.ts) {
+      for (int b = 0; b < p.batches; ++b) {
         if (PAIR) mma_ts_pair_x4(d_tmem, a_tmem, bd, bd + bs, bd + 2 * bs, bd + 3 * bs, idesc, 1u);
         else mma_ts_elect_x4(d_tmem, a_tmem, bd, bd + bs, bd + 2 * bs, bd + 3 * bs, idesc, 1u);
-      } else {
+        maybe_commit(b);
+      }
+    } else {
+      for (int b = 0; b < p.batches; ++b) {
         if (PAIR) mma_ss_pair_x4(d_tmem, ad, ad + 2, ad + 4, ad + 6, bd, bd + bs, bd + 2 * bs, bd + 3 * bs, idesc, 1u);
         else mma_ss_elect_x4(d_tmem, ad, ad + 2, ad + 4, ad + 6, bd, bd + bs, bd + 2 * bs, bd + 3 * bs, idesc, 1u);
-      }
-      if (p.commit_every > 0 && (b + 1) % p.commit_every == 0) {
-        if (PAIR) mma_commit_pair_elect(mapa_shared(extra_bar, 0));
-        else mma_commit_elect(extra_bar);
+        maybe_commit(b);
       }
     }
     t[0] = clock64() - t0;
