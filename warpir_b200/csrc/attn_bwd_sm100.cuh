@@ -326,41 +326,56 @@ attn_bwd_sm100(const __grid_constant__ CUtensorMap tmap_x0, const __grid_constan
     // per-row statistics (DKV = false): L2 = LSE log2 e, ds = delta * scale; delta is computed here
     float row_l2 = 0.f, row_ds = 0.f;
     if constexpr (!DKV) {
-      // Each thread reads its row of O and dO (for delta) and copies one of the two resident
-      // operands into tensor memory as the A operand of stage 1: group 0 the Q row, group 1 the
-      // dO row.  A row of D bf16 is D/2 32-bit words, exactly the packed layout the MMA reads.
+      // Each thread copies its row of one of the two resident operands into tensor memory as the A operand of
+      // stage 1 (group 0 the Q row, group 1 the dO row; a row of D bf16 is D/2 32-bit words, exactly the packed
+      // layout the MMA reads) and computes half of delta = rowsum(dO * O), group g over columns g D/2 ...; the
+      // halves meet in shared memory.  All loads of a batch are issued before the first use: the prologue is a
+      // chain of round trips to L2 or HBM, and a CTA has nothing else to do meanwhile.
       uint32_t xw[D / 2];
 #pragma unroll
       for (int i = 0; i < D / 2; ++i) xw[i] = 0u;
-      if (x_row < p.S) {
-        const size_t r = static_cast<size_t>(x_plane) * p.S + x_row;
-        const uint4* o4 = reinterpret_cast<const uint4*>(p.O + r * D);
-        const uint4* g4 = reinterpret_cast<const uint4*>(p.dO + r * D);
-        const uint4* q4 = reinterpret_cast<const uint4*>(p.Q + r * D);
-        float acc = 0.f;
+      float part = 0.f, lse = 0.f;
+      const bool live = x_row < p.S;
+      const size_t r = static_cast<size_t>(x_plane) * p.S + (live ? x_row : 0);
+      if (live) {
+        const uint4* x4 = reinterpret_cast<const uint4*>((half == 0 ? p.Q : p.dO) + r * D);
+        const uint4* o4 = reinterpret_cast<const uint4*>(p.O + r * D) + half * (D / 16);
+        const uint4* g4 = reinterpret_cast<const uint4*>(p.dO + r * D) + half * (D / 16);
 #pragma unroll
         for (int v = 0; v < D / 8; ++v) {
-          const uint4 a = __ldg(o4 + v), g = __ldg(g4 + v);
-          const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&a);
-          const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&g);
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const float2 af = __bfloat1622float2(a2[e]), gf = __bfloat1622float2(g2[e]);
-            acc = fmaf(af.x, gf.x, acc);
-            acc = fmaf(af.y, gf.y, acc);
-          }
-          const uint4 x = (half == 0) ? __ldg(q4 + v) : g;
+          const uint4 x = __ldg(x4 + v);
           xw[4 * v + 0] = x.x;
           xw[4 * v + 1] = x.y;
           xw[4 * v + 2] = x.z;
           xw[4 * v + 3] = x.w;
         }
-        if (half == 0) p.delta[r] = acc;
-        row_ds = acc * p.scale;
-        row_l2 = p.LSE[r] * kLog2e;
+        uint4 a[D / 16], g[D / 16];
+#pragma unroll
+        for (int v = 0; v < D / 16; ++v) {
+          a[v] = __ldg(o4 + v);
+          g[v] = __ldg(g4 + v);
+        }
+        lse = p.LSE[r];
+#pragma unroll
+        for (int v = 0; v < D / 16; ++v) {
+          const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&a[v]);
+          const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&g[v]);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float2 af = __bfloat1622float2(a2[e]), gf = __bfloat1622float2(g2[e]);
+            part = fmaf(af.x, gf.x, part);
+            part = fmaf(af.y, gf.y, part);
+          }
+        }
       }
 #pragma unroll
       for (int i = 0; i < D / 2; i += 32) tmem_st32(lane_base + kXCol + half * (D / 2) + i, xw + i);
+      stats[half * kBwdBX + tid] = part;
+      asm volatile("bar.sync 2, 256;" ::: "memory");
+      const float delta = stats[tid] + stats[kBwdBX + tid];
+      if (live && half == 0) p.delta[r] = delta;
+      row_ds = delta * p.scale;
+      row_l2 = lse * kLog2e;
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(x_full);
@@ -377,6 +392,7 @@ attn_bwd_sm100(const __grid_constant__ CUtensorMap tmap_x0, const __grid_constan
     float stat_next = 0.f;
     if (DKV && half < n_it) stat_next = fetch_stat(half);
 
+    if (traced) WIR_TRACE_EVENT(p.trace, 1 + half, 91, 0);     // prologue done
     const int b = half;                                   // this group's score buffer
     for (int it = half; it < n_it; it += 2) {
       const int y_row0 = y_tile_of(it) * kBwdBY;
@@ -482,21 +498,36 @@ attn_bwd_sm100(const __grid_constant__ CUtensorMap tmap_x0, const __grid_constan
       if (traced) WIR_TRACE_EVENT(p.trace, 1 + half, 92, 0);   // accumulators complete
       if (__all_sync(0xffffffffu, got)) {
         tc_fence_after();
-        const bool live = x_row < p.S;
-        const size_t r = static_cast<size_t>(x_plane) * p.S + (live ? x_row : 0);
+        // A store instruction of a warp with one row per lane writes 32 separate 16-byte pieces, and the
+        // memory pipeline takes them one cache line at a time (the epilogue of the dK / dV launch took 10000
+        // clocks for 128 KB that way).  So each warp turns its 32 x 32 block around in shared memory
+        // (XOR-swizzled, conflict-free both ways; the ring is idle by now) and stores whole 128-byte rows, four
+        // rows per instruction.
+        uint8_t* stage = smem + L::kYOffset + (warp - 2) * 4096;
+        const int row0 = x_row0 + quarter * 32;
+        const int rows_valid = min(32, p.S - row0);
+        const size_t r0 = static_cast<size_t>(x_plane) * p.S + row0;
 #pragma unroll 1
         for (int a = 0; a < (DKV ? 2 : 1); ++a) {
-          float* dst = (a == 0 ? p.out0 : p.out1) + r * D;
+          float* dst = (a == 0 ? p.out0 : p.out1) + r0 * D;
 #pragma unroll 1
           for (int cidx = half * (D / 64); cidx < (half + 1) * (D / 64); ++cidx) {   // each group stores half the columns
             uint32_t o[32];
             tmem_ld32(lane_base + kAccCol + a * D + cidx * 32, o);
             tmem_wait_ld();
-            if (live) {
 #pragma unroll
-              for (int v = 0; v < 8; ++v)
-                reinterpret_cast<uint4*>(dst + cidx * 32)[v] = make_uint4(o[4 * v], o[4 * v + 1], o[4 * v + 2], o[4 * v + 3]);
+            for (int v = 0; v < 8; ++v)
+              *reinterpret_cast<uint4*>(stage + lane * 128 + ((v ^ (lane & 7)) << 4)) =
+                  make_uint4(o[4 * v], o[4 * v + 1], o[4 * v + 2], o[4 * v + 3]);
+            __syncwarp();
+#pragma unroll
+            for (int rr = 0; rr < 8; ++rr) {
+              const int rl = rr * 4 + (lane >> 3);
+              const uint4 q = *reinterpret_cast<const uint4*>(stage + rl * 128 + (((lane & 7) ^ (rl & 7)) << 4));
+              if (rl < rows_valid)
+                *reinterpret_cast<uint4*>(dst + static_cast<size_t>(rl) * D + cidx * 32 + (lane & 7) * 4) = q;
             }
+            __syncwarp();
           }
         }
       }
