@@ -1,0 +1,562 @@
+// Attention backward for sm_100a in steps of 128 streamed rows (the library's choice; the 64-row kernel of
+// attn_bwd_sm100.cuh remains as the other variant).  Same mathematics and the same two launches of one template:
+//
+//   DKV = false (grid over 128-row Q tiles):  X0 = Q, X1 = dO resident; streams K, V tiles; accumulates dQ.
+//     Its prologue also computes delta = rowsum(dO * O) and stores it for the second launch.
+//   DKV = true  (grid over 128-key K/V tiles): X0 = K, X1 = V resident; streams the Q, dO tiles of every query
+//     head of the group; accumulates dV and dK.
+//
+// With c = scale * log2(e), per step j (Y0, Y1 the streamed 128 x D tiles):
+//
+//   A1:  T0 = X0 Y0^T            A2:  T1 = X1 Y1^T                       (128 x 128 each, operands in shared memory)
+//   P  = 2^(c T0 - LSE log2e)    dS = P (T1 - delta) scale               (compute warps, packed to bf16 in place)
+//   DKV:  B1: acc0 += P Y1 (dV)  B2: acc1 += dS Y0 (dK)       else  B: acc0 += dS Y0 (dQ)     (A from tensor memory)
+//
+// Why 128 rows per step: the warp that issues the MMAs is the kernel's clock.  It gets through its own dependent
+// instructions at 6-12 clocks each and pays 75-150 for every look at a barrier, and the tensor core's queue is
+// only about four MMAs deep; with 64-row steps (16 MMAs of 128 x 64 x 16, which from shared memory take 48 clocks
+// for 32 of arithmetic, and 4-8 of 128 x 128 x 16) it spent twice the tensor core's time per step.  Here a step
+// is 24 or 32 MMAs of 128 x 128 x 16 at the full rate, with the same number of hand-offs as a 64-row step had.
+//
+// Tensor memory has no room to double-buffer 128-column score tiles next to the accumulators (T0 128 + T1 128 +
+// acc0 D + acc1 D = 512 at D = 128), so the overlap comes from the order of issue instead:
+//
+//   B1(j)  A1(j+1)  B2(j)  A2(j+1)        (dQ launch:  A1(j+1)  B(j)  A2(j+1))
+//
+// P of step j is produced from T0 while A2(j) and B2(j-1) execute, dS from T1 (and the P values, which the
+// threads keep in registers) while B1(j) and A1(j+1) execute: each compute phase runs under two of the four MMA
+// groups.  MMAs execute in issue order, which makes the aliasing safe: A1(j+1) overwrites T0 (and P inside it)
+// behind B1(j), which reads P; A2(j+1) overwrites T1 behind B2(j) / B(j), which reads dS.
+//
+// Shared memory: X0, X1, then a ring of STREAMED TILES (not steps): Y0(0), Y1(0), Y0(1), ...; a tile goes back to
+// the producer behind the last MMA group that reads it (Y1(j) after B1(j), or after A2(j) in the dQ launch; Y0(j)
+// after B2(j) / B(j)).  Warp 0 is the TMA producer, warp 1 issues every MMA (whole warp, one elected lane, four
+// MMAs per instruction block), warps 2-9 are two compute warpgroups: thread = one tensor-memory lane (row), group
+// g takes columns 64 g ... of T0 / T1.  Packed P sits at columns 32-95 of T0 and packed dS at 32-95 of T1, so that
+// each group overwrites only columns it has loaded itself (group 0 loads 0-63 and writes 32-63, group 1 loads
+// 64-127 and writes 64-95).  Every wait is bounded.
+#pragma once
+
+#include "attn_bwd_sm100.cuh"
+
+namespace wir {
+
+constexpr int kBw2Rows = 128;   // rows of the resident AND of the streamed tiles
+
+template <int D, bool DKV>
+struct AttnBwdWideSmem {
+  static constexpr int kSlots = (D == 128) ? 5 : 10;                 // ring of streamed tiles
+  static constexpr int kChunkBytes = kBw2Rows * 128;                 // 128 rows x 64 bf16
+  static constexpr int kTileBytes = (D / 64) * kChunkBytes;
+  static constexpr int kRingOffset = 2 * kTileBytes;
+  static constexpr int kStatsOffset = kRingOffset + kSlots * kTileBytes;   // [2 vectors][128] floats
+  static constexpr int kBarOffset = kStatsOffset + 2 * kBw2Rows * 4;
+  // x_full, y_full[S], y_empty[S], t0_full, t1_full, p_ready, ds_ready, acc_done, drain
+  static constexpr int kNumBars = 2 * kSlots + 7;
+  static constexpr int kTmemPtrOffset = kBarOffset + kNumBars * 8;
+  static constexpr int kAbortOffset = kTmemPtrOffset + 4;
+  static constexpr int kBytes = kAbortOffset + 4;
+  static constexpr int kDynamicBytes = kBytes + 1024;
+};
+
+template <int D, bool CAUSAL, bool DKV>
+__global__ void __launch_bounds__(kBwdThreads, 1)
+attn_bwd_wide_sm100(const __grid_constant__ CUtensorMap tmap_x0, const __grid_constant__ CUtensorMap tmap_x1,
+                    const __grid_constant__ CUtensorMap tmap_y0, const __grid_constant__ CUtensorMap tmap_y1,
+                    const AttnBwdParams p) {
+  using L = AttnBwdWideSmem<D, DKV>;
+  constexpr int SLOTS = L::kSlots;
+  constexpr uint32_t kTmemCols = 512;
+  constexpr uint32_t kT1Col = 128, kAccCol = 256;
+  constexpr uint32_t kPackCol = 32;    // packed P / dS start here inside T0 / T1
+#ifdef WIR_BWD_POLY_EVERY
+  constexpr int kPolyEvery = WIR_BWD_POLY_EVERY;
+#else
+  constexpr int kPolyEvery = 4;        // one pair of exponentials in four on the FMA pipe (0: none)
+#endif
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const uint32_t smem_base = smem_u32(smem);
+  const uint32_t bar_base = smem_base + L::kBarOffset;
+  const uint32_t x_full = bar_base;
+  auto y_full = [&](uint32_t s) { return bar_base + 8u * (1 + s); };
+  auto y_empty = [&](uint32_t s) { return bar_base + 8u * (1 + SLOTS + s); };
+  const uint32_t t0_full = bar_base + 8u * (1 + 2 * SLOTS);
+  const uint32_t t1_full = bar_base + 8u * (2 + 2 * SLOTS);
+  const uint32_t p_ready = bar_base + 8u * (3 + 2 * SLOTS);
+  const uint32_t ds_ready = bar_base + 8u * (4 + 2 * SLOTS);
+  const uint32_t acc_done = bar_base + 8u * (5 + 2 * SLOTS);
+  const uint32_t drain_bar = bar_base + 8u * (6 + 2 * SLOTS);
+  volatile uint32_t* tmem_ptr_slot = reinterpret_cast<volatile uint32_t*>(smem + L::kTmemPtrOffset);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kAbortOffset);
+  float* stats = reinterpret_cast<float*>(smem + L::kStatsOffset);
+  const AbortCtx ctx{abort_flag, p.status};
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  // ---- which tile, which steps ---------------------------------------------------------
+  const int group = p.H / p.Hkv;
+  const int batch = blockIdx.z;
+  const int ny = (p.S + kBw2Rows - 1) / kBw2Rows;      // 128-row tiles along the sequence
+  // DKV = false: blockIdx.x (heaviest causal tiles first) is the Q tile, blockIdx.y the query head.
+  // DKV = true : blockIdx.x is the K/V tile, blockIdx.y the K/V head.
+  const int xt = (!DKV && CAUSAL) ? (gridDim.x - 1 - blockIdx.x) : blockIdx.x;
+  const int x_row0 = xt * kBw2Rows;
+  const int head = blockIdx.y;
+  const int x_plane = DKV ? (batch * p.Hkv + head) : (batch * p.H + head);
+  // steps: DKV = false walks K/V tiles 0 .. y_end-1 of the head's K/V head;
+  //        DKV = true  walks, for each query head of the group, Q tiles y_begin .. ny-1
+  const int y_begin = (DKV && CAUSAL) ? xt : 0;
+  const int y_end = (!DKV && CAUSAL) ? min(ny, xt + 1) : ny;
+  const int per_head = max(0, y_end - y_begin);
+  const int n_it = DKV ? per_head * group : per_head;
+  auto y_tile_of = [&](int it) { return y_begin + (DKV ? it % per_head : it); };
+  auto y_plane_of = [&](int it) {
+    return DKV ? (batch * p.H + head * group + it / per_head) : (batch * p.Hkv + head / group);
+  };
+
+  // Ring position of a streamed tile: slot and phase parity, carried along by additions.
+  struct RingPos { uint32_t slot, phase; };
+  auto ring_next = [](RingPos r, uint32_t by) {
+    r.slot += by;
+    if (r.slot >= static_cast<uint32_t>(SLOTS)) { r.slot -= SLOTS; r.phase ^= 1u; }
+    return r;
+  };
+  auto tile_addr = [&](RingPos r) { return smem_base + L::kRingOffset + r.slot * L::kTileBytes; };
+
+  // Producer (thread 0, which also initialises the barriers): streamed tile `which` (0: Y0, 1: Y1) of step `it`
+  // into the ring at `pos`.  The resident tiles and the first step go out before the CTA-wide barrier below.
+  auto load_tile = [&](int it, int which, RingPos pos) -> bool {
+    if (!mbar_wait(y_empty(pos.slot), pos.phase ^ 1, ctx, kRoleProducer, pos.slot, it)) return false;
+    mbar_arrive_expect_tx(y_full(pos.slot), L::kTileBytes);
+    const uint32_t dst = tile_addr(pos);
+    const int row = y_tile_of(it) * kBw2Rows, plane = y_plane_of(it);
+#pragma unroll
+    for (int c = 0; c < D / 64; ++c)
+      tma_load_3d(dst + c * L::kChunkBytes, which == 0 ? &tmap_y0 : &tmap_y1, y_full(pos.slot), c * 64, row, plane);
+    return true;
+  };
+  bool p_ok = true;
+  RingPos p_pos{0u, 0u};
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    mbar_init(x_full, 1);
+    for (int s = 0; s < SLOTS; ++s) {
+      mbar_init(y_full(s), 1);
+      mbar_init(y_empty(s), 1);
+    }
+    mbar_init(t0_full, 1);
+    mbar_init(t1_full, 1);
+    mbar_init(p_ready, kBwdComputeThreads);
+    mbar_init(ds_ready, kBwdComputeThreads);
+    mbar_init(acc_done, 1);
+    mbar_init(drain_bar, 1);
+    fence_mbar_init();
+    fence_proxy_async_smem();
+    if (n_it > 0) {
+      mbar_arrive_expect_tx(x_full, 2 * L::kTileBytes);
+#pragma unroll
+      for (int c = 0; c < D / 64; ++c) {
+        tma_load_3d(smem_base + c * L::kChunkBytes, &tmap_x0, x_full, c * 64, x_row0, x_plane);
+        tma_load_3d(smem_base + L::kTileBytes + c * L::kChunkBytes, &tmap_x1, x_full, c * 64, x_row0, x_plane);
+      }
+      p_ok = load_tile(0, 0, p_pos);
+      p_pos = ring_next(p_pos, 1);
+      if (p_ok) {
+        p_ok = load_tile(0, 1, p_pos);
+        p_pos = ring_next(p_pos, 1);
+      }
+    }
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_ptr_slot)), kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_ptr_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ producer
+    if (lane == 0 && n_it > 0) {
+      bool ok = p_ok;
+      int issued = ok ? 2 : 0;    // tiles handed to the copy engine so far (step 0 went out before the barrier)
+      for (int it = 1; ok && it < n_it; ++it) {
+#pragma unroll
+        for (int which = 0; which < 2; ++which) {
+          if (!ok) break;
+          ok = load_tile(it, which, p_pos);
+          if (ok) {
+            p_pos = ring_next(p_pos, 1);
+            ++issued;
+          }
+        }
+      }
+      if (!ok || *abort_flag) {
+        // every copy in flight must have landed before the CTA may exit: tile k completes phase k / SLOTS of barrier k % SLOTS
+        mbar_wait_quiet(x_full, 0);
+        const int n = issued < SLOTS ? issued : SLOTS;
+        for (int back = 1; back <= n; ++back) {
+          const int k = issued - back;
+          mbar_wait_quiet(y_full(k % SLOTS), (k / SLOTS) & 1);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    constexpr uint32_t idesc_t = idesc_bf16_f32(kBw2Rows, kBw2Rows, 0, 0);   // X Y^T: both K-major, N = 128
+    constexpr uint32_t idesc_acc = idesc_bf16_f32(kBw2Rows, D, 0, 1);        // (P | dS) Y: B is MN-major, N = D
+    constexpr uint32_t desc_hi = smem_desc_hi_sw128(1024);
+    const uint64_t x0d = desc64(smem_desc_lo(smem_base, 16), desc_hi);
+    const uint64_t x1d = desc64(smem_desc_lo(smem_base + L::kTileBytes, 16), desc_hi);
+    auto wait_tile = [&](RingPos r, int it) { return mbar_wait_warp(y_full(r.slot), r.phase, ctx, kRoleMma, 10, it); };
+    // T = X Y^T: D/16 k-steps, four (one 64-element chunk of the head dimension, 32 bytes per step) per block
+    auto issue_a = [&](uint32_t t_col, uint64_t xd, RingPos r) {
+      const uint64_t yd = desc64(smem_desc_lo(tile_addr(r), 16), desc_hi);
+#pragma unroll
+      for (int c = 0; c < D / 64; ++c) {
+        const uint64_t o = static_cast<uint64_t>((c * L::kChunkBytes) >> 4);
+        mma_ss_elect_x4(tmem_base + t_col, xd + o, xd + o + 2, xd + o + 4, xd + o + 6, yd + o, yd + o + 2, yd + o + 4,
+                        yd + o + 6, idesc_t, c > 0 ? 1u : 0u);
+      }
+    };
+    // acc += (P | dS) Y: the 128 streamed rows are the K dimension, eight k-steps of 16 rows (2048 bytes of an
+    // MN-major tile whose 64-column chunks are kChunkBytes apart), A = 8 packed columns of tensor memory per step
+    auto issue_b = [&](uint32_t acc_col, uint32_t a_col, RingPos r, uint32_t accumulate) {
+      const uint64_t yd = desc64(smem_desc_lo(tile_addr(r), L::kChunkBytes), desc_hi);
+#pragma unroll
+      for (int m = 0; m < kBw2Rows / 64; ++m) {
+        const uint64_t y = yd + static_cast<uint64_t>(512 * m);
+        mma_ts_elect_x4(tmem_base + acc_col, tmem_base + a_col + 32 * m, y, y + 128, y + 256, y + 384, idesc_acc,
+                        (accumulate != 0u || m > 0) ? 1u : 0u);
+      }
+    };
+    bool ok = true;
+    WIR_TRACE_DECL;
+    RingPos pos0{0u, 0u}, pos1{1u, 0u};     // Y0(j), Y1(j) of the current step; the next step's are two tiles on
+
+    if (n_it > 0) ok = mbar_wait_warp(x_full, 0, ctx, kRoleMma, 1, 0);
+    if (ok && n_it > 0) ok = wait_tile(pos0, 0);
+    if (ok && n_it > 0) {
+      tc_fence_after();
+      issue_a(0, x0d, pos0);
+      mma_commit_elect(t0_full);
+      ok = wait_tile(pos1, 0);
+      if (ok) {
+        tc_fence_after();
+        issue_a(kT1Col, x1d, pos1);
+        mma_commit_elect(t1_full);
+        if (!DKV) mma_commit_elect(y_empty(pos1.slot));      // dQ launch: A2 is the last reader of V(j)
+      }
+    }
+    for (int it = 0; ok && it < n_it; ++it) {
+      const uint32_t ph = static_cast<uint32_t>(it) & 1u;
+      const bool more = it + 1 < n_it;
+      const RingPos nxt0 = ring_next(pos0, 2), nxt1 = ring_next(pos1, 2);
+      const uint32_t acc = it > 0 ? 1u : 0u;
+      // the next step's tiles were asked for long ago: look at their barriers before the waits that are true
+      // dependencies, so that nothing but a fence stands between those and the MMAs
+      if (more && !wait_tile(nxt0, it + 1)) { ok = false; break; }
+      if (lane == 0) WIR_TRACE_EVENT(p.trace, 0, 0, it);
+      if (!mbar_wait_warp(p_ready, ph, ctx, kRoleMma, 20, it)) { ok = false; break; }
+      tc_fence_after();
+      if (lane == 0) WIR_TRACE_EVENT(p.trace, 0, 1, it);
+      if constexpr (DKV) {
+        issue_b(kAccCol, kPackCol, pos1, acc);                 // dV += P^T dO
+        mma_commit_elect(y_empty(pos1.slot));
+      }
+      if (more) {
+        issue_a(0, x0d, nxt0);                                  // next scores, behind the MMAs that read P
+        mma_commit_elect(t0_full);
+      }
+      if (lane == 0) WIR_TRACE_EVENT(p.trace, 0, 2, it);
+      if (more && !wait_tile(nxt1, it + 1)) { ok = false; break; }
+      if (!mbar_wait_warp(ds_ready, ph, ctx, kRoleMma, 30, it)) { ok = false; break; }
+      tc_fence_after();
+      if (lane == 0) WIR_TRACE_EVENT(p.trace, 0, 3, it);
+      issue_b(DKV ? kAccCol + D : kAccCol, kT1Col + kPackCol, pos0, acc);   // dK += dS^T Q   /   dQ += dS K
+      mma_commit_elect(y_empty(pos0.slot));
+      if (!more) mma_commit_elect(acc_done);
+      if (more) {
+        issue_a(kT1Col, x1d, nxt1);                             // next dP, behind the MMAs that read dS
+        mma_commit_elect(t1_full);
+        if (!DKV) mma_commit_elect(y_empty(nxt1.slot));
+      }
+      if (lane == 0) WIR_TRACE_EVENT(p.trace, 0, 4, it);
+      pos0 = nxt0;
+      pos1 = nxt1;
+    }
+    if (!ok || *abort_flag) {
+      mma_commit_elect(drain_bar);
+      mbar_wait_quiet(drain_bar, 0);
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------------------------------------------ compute warps
+    const int quarter = warp & 3;                       // tensor-memory lanes 32*quarter .. +31
+    const int half = (warp - 2) >> 2;                   // warpgroup: columns 64 half ... of T0 / T1
+    const int tid = quarter * 32 + lane;                // row of the resident tiles owned by this thread
+    const int x_row = x_row0 + tid;
+    const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+    const float c = p.scale_log2;
+    constexpr float kLog2e = 1.4426950408889634f;
+    bool ok = true;
+    WIR_TRACE_DECL;
+    const bool traced = (quarter == 0 && lane == 0);
+    if (traced) WIR_TRACE_EVENT(p.trace, 1 + half, 90, 0);     // set-up done, prologue starts
+
+    // per-row statistics (DKV = false): L2 = LSE log2 e, ds = delta * scale; delta is computed here, each
+    // group over half of the columns (all loads of a batch in flight at once), the halves meet in shared memory
+    float row_l2 = 0.f, row_ds = 0.f;
+    if constexpr (!DKV) {
+      float part = 0.f, lse = 0.f;
+      const bool live = x_row < p.S;
+      const size_t r = static_cast<size_t>(x_plane) * p.S + (live ? x_row : 0);
+      if (live) {
+        const uint4* o4 = reinterpret_cast<const uint4*>(p.O + r * D) + half * (D / 16);
+        const uint4* g4 = reinterpret_cast<const uint4*>(p.dO + r * D) + half * (D / 16);
+        uint4 a[D / 16], g[D / 16];
+#pragma unroll
+        for (int v = 0; v < D / 16; ++v) {
+          a[v] = __ldg(o4 + v);
+          g[v] = __ldg(g4 + v);
+        }
+        lse = p.LSE[r];
+#pragma unroll
+        for (int v = 0; v < D / 16; ++v) {
+          const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&a[v]);
+          const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&g[v]);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float2 af = __bfloat1622float2(a2[e]), gf = __bfloat1622float2(g2[e]);
+            part = fmaf(af.x, gf.x, part);
+            part = fmaf(af.y, gf.y, part);
+          }
+        }
+      }
+      stats[half * kBw2Rows + tid] = part;
+      asm volatile("bar.sync 2, 256;" ::: "memory");
+      const float delta = stats[tid] + stats[kBw2Rows + tid];
+      if (live && half == 0) p.delta[r] = delta;
+      row_ds = delta * p.scale;
+      row_l2 = lse * kLog2e;
+    }
+
+    // DKV: the per-column statistics of a step (LSE and delta of its 128 queries) are staged in shared memory:
+    // thread t of group 0 fetches LSE of query t, of group 1 delta of query t, one step ahead
+    // (the raw value: the factor is applied when the value is stored a step later -- a multiplication right
+    //  behind the load would hold the warp until the load has come back, which is what fetching ahead avoids)
+    auto fetch_stat = [&](int it) -> float {
+      const int q = y_tile_of(it) * kBw2Rows + tid;
+      const size_t r = static_cast<size_t>(y_plane_of(it)) * p.S + min(q, p.S - 1);
+      return (half == 0) ? p.LSE[r] : p.delta[r];
+    };
+    const float stat_factor = (half == 0) ? kLog2e : p.scale;
+    float stat_next = 0.f;
+    if (DKV && n_it > 0) stat_next = fetch_stat(0);
+    if (traced) WIR_TRACE_EVENT(p.trace, 1 + half, 91, 0);     // prologue done
+
+    for (int it = 0; it < n_it; ++it) {
+      const uint32_t ph = static_cast<uint32_t>(it) & 1u;
+      const int y_row0 = y_tile_of(it) * kBw2Rows;
+      if constexpr (DKV) {
+        // Group 0 publishes the step's LSE here: everybody has passed the previous step's second barrier, after
+        // which nobody reads LSE.  Delta, which is read until the end of the previous step, follows behind this
+        // step's first barrier (which every thread reaches only after its previous step).
+        if (half == 0) {
+          stats[tid] = stat_next * stat_factor;
+          if (it + 1 < n_it) stat_next = fetch_stat(it + 1);
+        }
+      }
+      if (traced) WIR_TRACE_EVENT(p.trace, 1 + half, 10, it);
+      // ---- P from T0
+      bool got = mbar_wait(t0_full, ph, ctx, kRoleSoftmax, 0, it);
+      if constexpr (DKV) {
+        // the compute warps meet at named barriers every step (they publish the statistics), so they must
+        // agree on going on
+        uint32_t all;
+        asm volatile(
+            "{\n\t.reg .pred a, q;\n\t"
+            "setp.ne.u32 q, %1, 0;\n\t"
+            "bar.red.and.pred a, 3, 256, q;\n\t"
+            "selp.u32 %0, 1, 0, a;\n\t}"
+            : "=r"(all)
+            : "r"(got ? 1u : 0u)
+            : "memory");
+        if (all == 0) { ok = false; break; }
+      } else if (!__all_sync(0xffffffffu, got)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      if constexpr (DKV) {
+        if (half == 1) {
+          stats[kBw2Rows + tid] = stat_next * stat_factor;       // published by the step's second barrier
+          if (it + 1 < n_it) stat_next = fetch_stat(it + 1);
+        }
+      }
+      if (traced) WIR_TRACE_EVENT(p.trace, 1 + half, 11, it);
+
+      // masks are only needed on tiles that touch the diagonal or the end of the sequence
+      const bool ragged = (y_row0 + kBw2Rows > p.S) || (x_row0 + kBw2Rows > p.S);
+      const bool diagonal = CAUSAL && (y_row0 == x_row0);
+      const bool masked = ragged || diagonal;
+
+      float pv[64];      // this thread's 64 values of P, kept for the dS phase
+      {
+        uint32_t t0[64];
+        tmem_ld32(lane_base + half * 64, t0);
+        tmem_ld32(lane_base + half * 64 + 32, t0 + 32);
+        tmem_wait_ld();
+        // in pairs (packed f32x2 arithmetic); one pair in kPolyEvery takes its exponentials on the FMA pipe
+        // (a cubic, relative error below 6e-4, far inside bf16's 4e-3): the exponential unit retires 16 results
+        // per clock per SM, which alone would take 1024 clocks per step
+        const float2 c2 = make_float2(c, c);
+#pragma unroll
+        for (int k = 0; k < 32; ++k) {
+          const int col = half * 64 + 2 * k;
+          const float la = DKV ? stats[col] : row_l2, lb = DKV ? stats[col + 1] : row_l2;
+          const float2 x = __ffma2_rn(make_float2(__uint_as_float(t0[2 * k]), __uint_as_float(t0[2 * k + 1])), c2,
+                                      make_float2(-la, -lb));
+          float2 e;
+          if (kPolyEvery > 0 && (k % (kPolyEvery > 0 ? kPolyEvery : 1)) == 0) {
+            e = ex2_fma2(x);
+          } else {
+            e.x = ex2_approx(x.x);
+            e.y = ex2_approx(x.y);
+          }
+          if (masked) {
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              const int y = y_row0 + col + h;             // index along the streamed tile
+              const int qi = DKV ? y : x_row;             // query index
+              const int ki = DKV ? x_row : y;             // key index
+              if (qi >= p.S || ki >= p.S || (CAUSAL && ki > qi)) (h == 0 ? e.x : e.y) = 0.f;
+            }
+          }
+          pv[2 * k] = e.x;
+          pv[2 * k + 1] = e.y;
+        }
+        if constexpr (DKV) {
+          uint32_t pk[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) pk[i] = pack_bf16(pv[2 * i], pv[2 * i + 1]);
+          tmem_st16(lane_base + kPackCol + half * 32, pk);
+          tmem_st16(lane_base + kPackCol + half * 32 + 16, pk + 16);
+          tmem_wait_st();
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(p_ready);
+      if (traced) WIR_TRACE_EVENT(p.trace, 1 + half, 12, it);
+
+      // ---- dS from T1 and P
+      got = mbar_wait(t1_full, ph, ctx, kRoleSoftmax, 1, it);
+      if constexpr (DKV) {
+        uint32_t all;
+        asm volatile(
+            "{\n\t.reg .pred a, q;\n\t"
+            "setp.ne.u32 q, %1, 0;\n\t"
+            "bar.red.and.pred a, 4, 256, q;\n\t"
+            "selp.u32 %0, 1, 0, a;\n\t}"
+            : "=r"(all)
+            : "r"(got ? 1u : 0u)
+            : "memory");
+        if (all == 0) { ok = false; break; }
+      } else if (!__all_sync(0xffffffffu, got)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      if (traced) WIR_TRACE_EVENT(p.trace, 1 + half, 13, it);
+      {
+        uint32_t t1[64];
+        tmem_ld32(lane_base + kT1Col + half * 64, t1);
+        tmem_ld32(lane_base + kT1Col + half * 64 + 32, t1 + 32);
+        tmem_wait_ld();
+        const float2 s2 = make_float2(p.scale, p.scale);
+        uint32_t dk[32];
+#pragma unroll
+        for (int k = 0; k < 32; ++k) {
+          const int col = half * 64 + 2 * k;
+          const float da = DKV ? stats[kBw2Rows + col] : row_ds, db = DKV ? stats[kBw2Rows + col + 1] : row_ds;
+          const float2 u = __ffma2_rn(make_float2(__uint_as_float(t1[2 * k]), __uint_as_float(t1[2 * k + 1])), s2,
+                                      make_float2(-da, -db));
+          const float2 d = __fmul2_rn(make_float2(pv[2 * k], pv[2 * k + 1]), u);
+          dk[k] = pack_bf16(d.x, d.y);
+        }
+        tmem_st16(lane_base + kT1Col + kPackCol + half * 32, dk);
+        tmem_st16(lane_base + kT1Col + kPackCol + half * 32 + 16, dk + 16);
+      }
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(ds_ready);
+      if (traced) WIR_TRACE_EVENT(p.trace, 1 + half, 14, it);
+    }
+
+    if (ok && n_it > 0) {
+      const bool got = mbar_wait(acc_done, 0, ctx, kRoleEpilogue, 0, n_it);
+      if (traced) WIR_TRACE_EVENT(p.trace, 1 + half, 92, 0);   // accumulators complete
+      if (__all_sync(0xffffffffu, got)) {
+        tc_fence_after();
+        // each warp turns its 32 x 32 blocks around in shared memory (XOR-swizzled; the ring is idle by now) and
+        // stores whole 128-byte rows, four rows per instruction
+        uint8_t* stage = smem + L::kRingOffset + (warp - 2) * 4096;
+        const int row0 = x_row0 + quarter * 32;
+        const int rows_valid = min(32, p.S - row0);
+        const size_t r0 = static_cast<size_t>(x_plane) * p.S + row0;
+#pragma unroll 1
+        for (int a = 0; a < (DKV ? 2 : 1); ++a) {
+          float* dst = (a == 0 ? p.out0 : p.out1) + r0 * D;
+#pragma unroll 1
+          for (int cidx = half * (D / 64); cidx < (half + 1) * (D / 64); ++cidx) {   // each group stores half the columns
+            uint32_t o[32];
+            tmem_ld32(lane_base + kAccCol + a * D + cidx * 32, o);
+            tmem_wait_ld();
+#pragma unroll
+            for (int v = 0; v < 8; ++v)
+              *reinterpret_cast<uint4*>(stage + lane * 128 + ((v ^ (lane & 7)) << 4)) =
+                  make_uint4(o[4 * v], o[4 * v + 1], o[4 * v + 2], o[4 * v + 3]);
+            __syncwarp();
+#pragma unroll
+            for (int rr = 0; rr < 8; ++rr) {
+              const int rl = rr * 4 + (lane >> 3);
+              const uint4 q = *reinterpret_cast<const uint4*>(stage + rl * 128 + (((lane & 7) ^ (rl & 7)) << 4));
+              if (rl < rows_valid)
+                *reinterpret_cast<uint4*>(dst + static_cast<size_t>(rl) * D + cidx * 32 + (lane & 7) * 4) = q;
+            }
+            __syncwarp();
+          }
+        }
+      }
+    } else if (ok && n_it == 0) {
+      // nothing attends here (only possible past the end of the sequence): gradients are zero
+      if (x_row < p.S && half == 0) {
+        const size_t r = static_cast<size_t>(x_plane) * p.S + x_row;
+        for (int a = 0; a < (DKV ? 2 : 1); ++a) {
+          float* dst = (a == 0 ? p.out0 : p.out1) + r * D;
+          for (int v = 0; v < D / 4; ++v) reinterpret_cast<uint4*>(dst)[v] = make_uint4(0, 0, 0, 0);
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+#ifdef WIR_TRACE
+  if (threadIdx.x == 64) {
+    WIR_TRACE_DECL;
+    WIR_TRACE_EVENT(p.trace, 3, 93, 0);   // epilogue done
+  }
+#endif
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+}  // namespace wir

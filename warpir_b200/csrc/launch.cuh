@@ -6,6 +6,7 @@
 
 #include "host_common.cuh"
 #include "attn_bwd_sm100.cuh"
+#include "attn_bwd_wide_sm100.cuh"
 #include "attn_fwd_sm100.cuh"
 #include "attn_fwd_wide_sm100.cuh"
 #include "gemm_sm100.cuh"
@@ -467,6 +468,29 @@ int launch_attn_bwd_cfg(const CUtensorMap& x0, const CUtensorMap& x1, const CUte
   return WARPIR_OK;
 }
 
+template <int D, bool CAUSAL, bool DKV>
+int launch_attn_bwd_wide_cfg(const CUtensorMap& x0, const CUtensorMap& x1, const CUtensorMap& y0, const CUtensorMap& y1,
+                             const wir::AttnBwdParams& p, cudaStream_t stream) {
+  auto kernel = wir::attn_bwd_wide_sm100<D, CAUSAL, DKV>;
+  constexpr int smem = wir::AttnBwdWideSmem<D, DKV>::kDynamicBytes;
+  static_assert(smem <= 232448, "shared memory limit per CTA");
+  static_assert(smem > 116 * 1024, "one CTA per SM is what keeps the tensor-memory allocation from blocking");
+  if (int rc = opt_in_smem(reinterpret_cast<const void*>(kernel), smem)) return rc;
+  dim3 grid((p.S + wir::kBw2Rows - 1) / wir::kBw2Rows, DKV ? p.Hkv : p.H, p.B);
+  kernel<<<grid, wir::kBwdThreads, smem, stream>>>(x0, x1, y0, y1, p);
+  WIR_CUDA(cudaGetLastError());
+  return WARPIR_OK;
+}
+
+// Tuning override for experiments: WARPIR_ATTN_BWD_ROWS=64|128 picks the backward kernel by the rows it streams per step.
+inline int env_attn_bwd_rows() {
+  static const int v = [] {
+    const char* e = getenv("WARPIR_ATTN_BWD_ROWS");
+    return e ? atoi(e) : 0;
+  }();
+  return v;
+}
+
 inline int attn_bwd_impl(const void* Q, const void* K, const void* V, const void* O, const void* dO, const float* LSE,
                          float* dQ, float* dK, float* dV, float* delta, int64_t B, int64_t Hq, int64_t Hkv, int64_t S,
                          int64_t D, float softmax_scale, int causal, int device, void* cuda_stream) {
@@ -518,6 +542,23 @@ inline int attn_bwd_impl(const void* Q, const void* K, const void* V, const void
   p.trace = g_trace;
   const bool c = causal != 0;
   int rc;
+  const bool wide = env_attn_bwd_rows() ? env_attn_bwd_rows() == 128 : true;
+  if (wide) {
+    // steps of 128 streamed rows: every operand is read as 128-row tiles, resident or streamed
+    p.out0 = dQ;
+    p.out1 = nullptr;
+    if (D == 128) rc = c ? launch_attn_bwd_wide_cfg<128, true, false>(q_x, g_x, k_x, v_x, p, stream) : launch_attn_bwd_wide_cfg<128, false, false>(q_x, g_x, k_x, v_x, p, stream);
+    else rc = c ? launch_attn_bwd_wide_cfg<64, true, false>(q_x, g_x, k_x, v_x, p, stream) : launch_attn_bwd_wide_cfg<64, false, false>(q_x, g_x, k_x, v_x, p, stream);
+    if (rc) return rc;
+#if defined(WIR_TRACE) || defined(WIR_BWD_ABLATE)
+    if (getenv("WARPIR_BWD_DQ_ONLY")) return rc;   // debug and measurement builds: the first launch alone
+#endif
+    p.out0 = dV;
+    p.out1 = dK;
+    if (D == 128) rc = c ? launch_attn_bwd_wide_cfg<128, true, true>(k_x, v_x, q_x, g_x, p, stream) : launch_attn_bwd_wide_cfg<128, false, true>(k_x, v_x, q_x, g_x, p, stream);
+    else rc = c ? launch_attn_bwd_wide_cfg<64, true, true>(k_x, v_x, q_x, g_x, p, stream) : launch_attn_bwd_wide_cfg<64, false, true>(k_x, v_x, q_x, g_x, p, stream);
+    return rc;
+  }
   // 1: dQ (and delta) per Q tile, streaming K and V
   p.out0 = dQ;
   p.out1 = nullptr;
