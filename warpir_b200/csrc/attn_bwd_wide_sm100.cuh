@@ -72,7 +72,7 @@ attn_bwd_wide_sm100(const __grid_constant__ CUtensorMap tmap_x0, const __grid_co
 #ifdef WIR_BWD_POLY_EVERY
   constexpr int kPolyEvery = WIR_BWD_POLY_EVERY;
 #else
-  constexpr int kPolyEvery = 4;        // one pair of exponentials in four on the FMA pipe (0: none)
+  constexpr int kPolyEvery = 0;        // one pair of exponentials in so many on the FMA pipe (0: none; 4, 2 and 1 measured 1, 5 and 12 % slower: the compute phases are short of issue slots, not of exponential throughput)
 #endif
 
   extern __shared__ uint8_t smem_raw[];
@@ -260,7 +260,13 @@ attn_bwd_wide_sm100(const __grid_constant__ CUtensorMap tmap_x0, const __grid_co
       const uint32_t acc = it > 0 ? 1u : 0u;
       // the next step's tiles were asked for long ago: look at their barriers before the waits that are true
       // dependencies, so that nothing but a fence stands between those and the MMAs
-      if (more && !wait_tile(nxt0, it + 1)) { ok = false; break; }
+      // (both tiles' barriers tested together: one vote, one branch; the full waits only if one is still open)
+      bool landed1 = !more;
+      if (more) {
+        const bool both = mbar_test_wait(y_full(nxt0.slot), nxt0.phase) & mbar_test_wait(y_full(nxt1.slot), nxt1.phase);
+        landed1 = __all_sync(0xffffffffu, both);
+        if (!landed1 && !wait_tile(nxt0, it + 1)) { ok = false; break; }
+      }
       if (lane == 0) WIR_TRACE_EVENT(p.trace, 0, 0, it);
       if (!mbar_wait_warp(p_ready, ph, ctx, kRoleMma, 20, it)) { ok = false; break; }
       tc_fence_after();
@@ -274,7 +280,7 @@ attn_bwd_wide_sm100(const __grid_constant__ CUtensorMap tmap_x0, const __grid_co
         mma_commit_elect(t0_full);
       }
       if (lane == 0) WIR_TRACE_EVENT(p.trace, 0, 2, it);
-      if (more && !wait_tile(nxt1, it + 1)) { ok = false; break; }
+      if (!landed1 && !wait_tile(nxt1, it + 1)) { ok = false; break; }
       if (!mbar_wait_warp(ds_ready, ph, ctx, kRoleMma, 30, it)) { ok = false; break; }
       tc_fence_after();
       if (lane == 0) WIR_TRACE_EVENT(p.trace, 0, 3, it);
@@ -412,35 +418,46 @@ attn_bwd_wide_sm100(const __grid_constant__ CUtensorMap tmap_x0, const __grid_co
         tmem_ld32(lane_base + half * 64, t0);
         tmem_ld32(lane_base + half * 64 + 32, t0 + 32);
         tmem_wait_ld();
+        if (traced) WIR_TRACE_EVENT(p.trace, 1 + half, 15, it);
         // in pairs (packed f32x2 arithmetic); one pair in kPolyEvery takes its exponentials on the FMA pipe
         // (a cubic, relative error below 6e-4, far inside bf16's 4e-3): the exponential unit retires 16 results
         // per clock per SM, which alone would take 1024 clocks per step
         const float2 c2 = make_float2(c, c);
+        const float4* l4 = reinterpret_cast<const float4*>(stats + half * 64);   // 16-byte loads: one per four columns
 #pragma unroll
-        for (int k = 0; k < 32; ++k) {
-          const int col = half * 64 + 2 * k;
-          const float la = DKV ? stats[col] : row_l2, lb = DKV ? stats[col + 1] : row_l2;
-          const float2 x = __ffma2_rn(make_float2(__uint_as_float(t0[2 * k]), __uint_as_float(t0[2 * k + 1])), c2,
-                                      make_float2(-la, -lb));
-          float2 e;
-          if (kPolyEvery > 0 && (k % (kPolyEvery > 0 ? kPolyEvery : 1)) == 0) {
-            e = ex2_fma2(x);
-          } else {
-            e.x = ex2_approx(x.x);
-            e.y = ex2_approx(x.y);
-          }
-          if (masked) {
+        for (int k4 = 0; k4 < 16; ++k4) {
+          float4 lq = make_float4(row_l2, row_l2, row_l2, row_l2);
+#if !(defined(WIR_BWD_ABLATE) && WIR_BWD_ABLATE == 6)     // measurement build 6: no per-column statistics from shared memory
+          if constexpr (DKV) lq = l4[k4];
+#endif
 #pragma unroll
-            for (int h = 0; h < 2; ++h) {
-              const int y = y_row0 + col + h;             // index along the streamed tile
-              const int qi = DKV ? y : x_row;             // query index
-              const int ki = DKV ? x_row : y;             // key index
-              if (qi >= p.S || ki >= p.S || (CAUSAL && ki > qi)) (h == 0 ? e.x : e.y) = 0.f;
+          for (int kk = 0; kk < 2; ++kk) {
+            const int k = 2 * k4 + kk;
+            const int col = half * 64 + 2 * k;
+            const float la = kk == 0 ? lq.x : lq.z, lb = kk == 0 ? lq.y : lq.w;
+            const float2 x = __ffma2_rn(make_float2(__uint_as_float(t0[2 * k]), __uint_as_float(t0[2 * k + 1])), c2,
+                                        make_float2(-la, -lb));
+            float2 e;
+            if (kPolyEvery > 0 && (k % (kPolyEvery > 0 ? kPolyEvery : 1)) == 0) {
+              e = ex2_fma2(x);
+            } else {
+              e.x = ex2_approx(x.x);
+              e.y = ex2_approx(x.y);
             }
+            if (masked) {
+#pragma unroll
+              for (int h = 0; h < 2; ++h) {
+                const int y = y_row0 + col + h;             // index along the streamed tile
+                const int qi = DKV ? y : x_row;             // query index
+                const int ki = DKV ? x_row : y;             // key index
+                if (qi >= p.S || ki >= p.S || (CAUSAL && ki > qi)) (h == 0 ? e.x : e.y) = 0.f;
+              }
+            }
+            pv[2 * k] = e.x;
+            pv[2 * k + 1] = e.y;
           }
-          pv[2 * k] = e.x;
-          pv[2 * k + 1] = e.y;
         }
+        if (traced) WIR_TRACE_EVENT(p.trace, 1 + half, 16, it);
         if constexpr (DKV) {
           uint32_t pk[32];
 #pragma unroll
@@ -478,16 +495,25 @@ attn_bwd_wide_sm100(const __grid_constant__ CUtensorMap tmap_x0, const __grid_co
         tmem_ld32(lane_base + kT1Col + half * 64, t1);
         tmem_ld32(lane_base + kT1Col + half * 64 + 32, t1 + 32);
         tmem_wait_ld();
+        if (traced) WIR_TRACE_EVENT(p.trace, 1 + half, 17, it);
         const float2 s2 = make_float2(p.scale, p.scale);
+        const float4* d4 = reinterpret_cast<const float4*>(stats + kBw2Rows + half * 64);
         uint32_t dk[32];
 #pragma unroll
-        for (int k = 0; k < 32; ++k) {
-          const int col = half * 64 + 2 * k;
-          const float da = DKV ? stats[kBw2Rows + col] : row_ds, db = DKV ? stats[kBw2Rows + col + 1] : row_ds;
-          const float2 u = __ffma2_rn(make_float2(__uint_as_float(t1[2 * k]), __uint_as_float(t1[2 * k + 1])), s2,
-                                      make_float2(-da, -db));
-          const float2 d = __fmul2_rn(make_float2(pv[2 * k], pv[2 * k + 1]), u);
-          dk[k] = pack_bf16(d.x, d.y);
+        for (int k4 = 0; k4 < 16; ++k4) {
+          float4 dq = make_float4(row_ds, row_ds, row_ds, row_ds);
+#if !(defined(WIR_BWD_ABLATE) && WIR_BWD_ABLATE == 6)
+          if constexpr (DKV) dq = d4[k4];
+#endif
+#pragma unroll
+          for (int kk = 0; kk < 2; ++kk) {
+            const int k = 2 * k4 + kk;
+            const float da = kk == 0 ? dq.x : dq.z, db = kk == 0 ? dq.y : dq.w;
+            const float2 u = __ffma2_rn(make_float2(__uint_as_float(t1[2 * k]), __uint_as_float(t1[2 * k + 1])), s2,
+                                        make_float2(-da, -db));
+            const float2 d = __fmul2_rn(make_float2(pv[2 * k], pv[2 * k + 1]), u);
+            dk[k] = pack_bf16(d.x, d.y);
+          }
         }
         tmem_st16(lane_base + kT1Col + kPackCol + half * 32, dk);
         tmem_st16(lane_base + kT1Col + kPackCol + half * 32 + 16, dk + 16);
