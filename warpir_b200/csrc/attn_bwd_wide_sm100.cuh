@@ -37,6 +37,8 @@
 // 64-127 and writes 64-95).  Every wait is bounded.
 #pragma once
 
+#include <type_traits>
+
 #include "attn_bwd_sm100.cuh"
 
 namespace wir {
@@ -69,10 +71,13 @@ attn_bwd_wide_sm100(const __grid_constant__ CUtensorMap tmap_x0, const __grid_co
   constexpr uint32_t kTmemCols = 512;
   constexpr uint32_t kT1Col = 128, kAccCol = 256;
   constexpr uint32_t kPackCol = 32;    // packed P / dS start here inside T0 / T1
-#ifdef WIR_BWD_POLY_EVERY
-  constexpr int kPolyEvery = WIR_BWD_POLY_EVERY;
+  // One pair of exponentials in so many takes the FMA pipe (a cubic) instead of the exponential unit; 0: none.
+  // Measured per launch (clocks per step): the dQ launch, whose compute phases have no other work, 2730 with one
+  // pair in four and 3410 with none; the dK / dV launch is faster with none.
+#if defined(WIR_BWD_POLY_DQ) && defined(WIR_BWD_POLY_DKV)
+  constexpr int kPolyEvery = DKV ? WIR_BWD_POLY_DKV : WIR_BWD_POLY_DQ;
 #else
-  constexpr int kPolyEvery = 0;        // one pair of exponentials in so many on the FMA pipe (0: none; 4, 2 and 1 measured 1, 5 and 12 % slower: the compute phases are short of issue slots, not of exponential throughput)
+  constexpr int kPolyEvery = DKV ? 0 : 4;
 #endif
 
   extern __shared__ uint8_t smem_raw[];
@@ -424,41 +429,53 @@ attn_bwd_wide_sm100(const __grid_constant__ CUtensorMap tmap_x0, const __grid_co
         // per clock per SM, which alone would take 1024 clocks per step
         const float2 c2 = make_float2(c, c);
         const float4* l4 = reinterpret_cast<const float4*>(stats + half * 64);   // 16-byte loads: one per four columns
+        // The loop exists twice, with and without the mask: a test of `masked` inside it, once per pair, is a
+        // branch per pair, across which the compiler does not move instructions -- every pair then runs through
+        // its chain of FMA, exponential and conversion alone, 55 clocks at a time (1800 clocks per step; the
+        // exponential unit needs 1024).
+        auto p_phase = [&](auto masked_c) {
+          constexpr bool kMasked = decltype(masked_c)::value;
 #pragma unroll
-        for (int k4 = 0; k4 < 16; ++k4) {
-          float4 lq = make_float4(row_l2, row_l2, row_l2, row_l2);
+          for (int k4 = 0; k4 < 16; ++k4) {
+            float4 lq = make_float4(row_l2, row_l2, row_l2, row_l2);
 #if !(defined(WIR_BWD_ABLATE) && WIR_BWD_ABLATE == 6)     // measurement build 6: no per-column statistics from shared memory
-          if constexpr (DKV) lq = l4[k4];
+            if constexpr (DKV) lq = l4[k4];
 #endif
 #pragma unroll
-          for (int kk = 0; kk < 2; ++kk) {
-            const int k = 2 * k4 + kk;
-            const int col = half * 64 + 2 * k;
-            const float la = kk == 0 ? lq.x : lq.z, lb = kk == 0 ? lq.y : lq.w;
-            const float2 x = __ffma2_rn(make_float2(__uint_as_float(t0[2 * k]), __uint_as_float(t0[2 * k + 1])), c2,
-                                        make_float2(-la, -lb));
-            float2 e;
-            if (kPolyEvery > 0 && (k % (kPolyEvery > 0 ? kPolyEvery : 1)) == 0) {
-              e = ex2_fma2(x);
-            } else {
-              e.x = ex2_approx(x.x);
-              e.y = ex2_approx(x.y);
-            }
-            if (masked) {
-#pragma unroll
-              for (int h = 0; h < 2; ++h) {
-                const int y = y_row0 + col + h;             // index along the streamed tile
-                const int qi = DKV ? y : x_row;             // query index
-                const int ki = DKV ? x_row : y;             // key index
-                if (qi >= p.S || ki >= p.S || (CAUSAL && ki > qi)) (h == 0 ? e.x : e.y) = 0.f;
+            for (int kk = 0; kk < 2; ++kk) {
+              const int k = 2 * k4 + kk;
+              const int col = half * 64 + 2 * k;
+              const float la = kk == 0 ? lq.x : lq.z, lb = kk == 0 ? lq.y : lq.w;
+              const float2 x = __ffma2_rn(make_float2(__uint_as_float(t0[2 * k]), __uint_as_float(t0[2 * k + 1])), c2,
+                                          make_float2(-la, -lb));
+              float2 e;
+              if (kPolyEvery > 0 && (k % (kPolyEvery > 0 ? kPolyEvery : 1)) == 0) {
+                e = ex2_fma2(x);
+              } else {
+                e.x = ex2_approx(x.x);
+                e.y = ex2_approx(x.y);
               }
+              if constexpr (kMasked) {
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                  const int y = y_row0 + col + h;             // index along the streamed tile
+                  const int qi = DKV ? y : x_row;             // query index
+                  const int ki = DKV ? x_row : y;             // key index
+                  if (qi >= p.S || ki >= p.S || (CAUSAL && ki > qi)) (h == 0 ? e.x : e.y) = 0.f;
+                }
+              }
+              pv[2 * k] = e.x;
+              pv[2 * k + 1] = e.y;
             }
-            pv[2 * k] = e.x;
-            pv[2 * k + 1] = e.y;
           }
-        }
+        };
+        if (masked) p_phase(std::true_type{});
+        else p_phase(std::false_type{});
         if (traced) WIR_TRACE_EVENT(p.trace, 1 + half, 16, it);
         if constexpr (DKV) {
+          // (packing with integer instructions instead of the conversion instruction measured 3-8 % slower, a
+          //  polynomial share of the exponentials in this launch 1-12 %: more instructions cost more than the
+          //  quarter-rate unit they would relieve)
           uint32_t pk[32];
 #pragma unroll
           for (int i = 0; i < 32; ++i) pk[i] = pack_bf16(pv[2 * i], pv[2 * i + 1]);
