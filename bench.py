@@ -677,7 +677,7 @@ def run_gpu_arm(args, w, name):
     roof["algorithmic_bytes_per_launch"] = bytes_of(w)
     roof["kernel"] = {"gemm": "gemm_pair_sm100" if (w["kind"] == "gemm" and min(w["M"], w["N"]) >= 2048) else "gemm_bf16_sm100",
                       "attn": "attn_fwd_sm100" if (w.get("causal") and w.get("D") == 128) else "attn_fwd_wide_sm100",
-                      "attn_bwd": "attn_bwd_sm100"}[w["kind"]]
+                      "attn_bwd": "attn_bwd_wide_sm100"}[w["kind"]]
     roof["algorithmic_per_launch"] = flops_of(w) if tensor_bound else bytes_of(w)
 
     others = []

@@ -80,3 +80,29 @@ def test_backward_rejections(lib):
     with pytest.raises(runtime.WarpirError):
         runtime.launch_attention_backward(Q96, Q96, Q96, Q96, Q96, L, z(1, 2, 64, 96, dt=torch.float32),
                                           z(1, 2, 64, 96, dt=torch.float32), z(1, 2, 64, 96, dt=torch.float32))
+
+
+def test_the_64_row_kernel_stays_correct():
+    """The library runs the backward in steps of 128 streamed rows; the kernel that streams 64 rows per step
+    remains selectable (WARPIR_ATTN_BWD_ROWS=64, read once per process, hence the child process) and must keep
+    passing the same comparison."""
+    import os
+    import subprocess
+    import sys
+    import textwrap
+    from pathlib import Path
+    root = Path(__file__).resolve().parent.parent
+    script = textwrap.dedent("""
+        import sys
+        sys.path.insert(0, %r)
+        sys.path.insert(0, %r)
+        import test_attention_backward_gpu as t
+        from oracle import reference_ops as R
+        for (B, H, Hkv, S, D, causal) in [(1, 2, 2, 200, 128, True), (2, 4, 2, 320, 128, False), (1, 8, 1, 192, 64, True)]:
+            err, _ = t.run_case(B, H, Hkv, S, D, causal, seed=S + D)
+            assert max(err.values()) <= R.ATTN_GRAD_REL_TOL, err
+        print("OK")
+    """ % (str(root), str(root / "tests")))
+    env = dict(os.environ, WARPIR_ATTN_BWD_ROWS="64")
+    proc = subprocess.run([sys.executable, "-c", script], capture_output=True, text=True, timeout=600, env=env)
+    assert proc.returncode == 0 and proc.stdout.strip().endswith("OK"), proc.stdout + proc.stderr
