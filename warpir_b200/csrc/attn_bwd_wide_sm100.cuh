@@ -2,7 +2,7 @@
 // attn_bwd_sm100.cuh remains as the other variant).  Same mathematics and the same two launches of one template:
 //
 //   DKV = false (grid over 128-row Q tiles):  X0 = Q, X1 = dO resident; streams K, V tiles; accumulates dQ.
-//     Its prologue also computes delta = rowsum(dO * O) and stores it for the second launch.
+//   (delta = rowsum(dO * O), which both need, comes from a third, small kernel that runs first: attn_bwd_delta.)
 //   DKV = true  (grid over 128-key K/V tiles): X0 = K, X1 = V resident; streams the Q, dO tiles of every query
 //     head of the group; accumulates dV and dK.
 //
@@ -320,41 +320,16 @@ attn_bwd_wide_sm100(const __grid_constant__ CUtensorMap tmap_x0, const __grid_co
     const bool traced = (quarter == 0 && lane == 0);
     if (traced) WIR_TRACE_EVENT(p.trace, 1 + half, 90, 0);     // set-up done, prologue starts
 
-    // per-row statistics (DKV = false): L2 = LSE log2 e, ds = delta * scale; delta is computed here, each
-    // group over half of the columns (all loads of a batch in flight at once), the halves meet in shared memory
+    // per-row statistics (DKV = false): L2 = LSE log2 e, ds = delta * scale.  delta = rowsum(dO * O) comes from a
+    // small kernel of its own that runs before this launch (attn_bwd_delta below): computed here, per thread from
+    // its own row, it was a chain of round trips to memory of 13000 clocks per CTA, an eighth of the launch.
     float row_l2 = 0.f, row_ds = 0.f;
     if constexpr (!DKV) {
-      float part = 0.f, lse = 0.f;
-      const bool live = x_row < p.S;
-      const size_t r = static_cast<size_t>(x_plane) * p.S + (live ? x_row : 0);
-      if (live) {
-        const uint4* o4 = reinterpret_cast<const uint4*>(p.O + r * D) + half * (D / 16);
-        const uint4* g4 = reinterpret_cast<const uint4*>(p.dO + r * D) + half * (D / 16);
-        uint4 a[D / 16], g[D / 16];
-#pragma unroll
-        for (int v = 0; v < D / 16; ++v) {
-          a[v] = __ldg(o4 + v);
-          g[v] = __ldg(g4 + v);
-        }
-        lse = p.LSE[r];
-#pragma unroll
-        for (int v = 0; v < D / 16; ++v) {
-          const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&a[v]);
-          const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&g[v]);
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const float2 af = __bfloat1622float2(a2[e]), gf = __bfloat1622float2(g2[e]);
-            part = fmaf(af.x, gf.x, part);
-            part = fmaf(af.y, gf.y, part);
-          }
-        }
+      if (x_row < p.S) {
+        const size_t r = static_cast<size_t>(x_plane) * p.S + x_row;
+        row_ds = p.delta[r] * p.scale;
+        row_l2 = p.LSE[r] * kLog2e;
       }
-      stats[half * kBw2Rows + tid] = part;
-      asm volatile("bar.sync 2, 256;" ::: "memory");
-      const float delta = stats[tid] + stats[kBw2Rows + tid];
-      if (live && half == 0) p.delta[r] = delta;
-      row_ds = delta * p.scale;
-      row_l2 = lse * kLog2e;
     }
 
     // DKV: the per-column statistics of a step (LSE and delta of its 128 queries) are staged in shared memory:
@@ -599,6 +574,39 @@ attn_bwd_wide_sm100(const __grid_constant__ CUtensorMap tmap_x0, const __grid_co
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// delta[r] = sum over the head dimension of dO[r][:] * O[r][:] for every row r of [B, H, S, D] (bf16, D = 64 or 128).
+// Sixteen bytes per lane: D / 8 lanes share a row, a warp takes 256 / D ... rows per step; memory-bound, one pass
+// over O and dO.
+template <int D>
+__global__ void __launch_bounds__(256) attn_bwd_delta(const __nv_bfloat16* __restrict__ O, const __nv_bfloat16* __restrict__ dO,
+                                                      float* __restrict__ delta, long long rows) {
+  constexpr int kLanesPerRow = D / 8;                 // 16 (D = 128) or 8 (D = 64)
+  constexpr int kRowsPerWarp = 32 / kLanesPerRow;
+  const int lane = threadIdx.x & 31;
+  const long long warp_global = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const long long n_warps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+  const int sub = lane / kLanesPerRow, piece = lane % kLanesPerRow;
+  for (long long r0 = warp_global * kRowsPerWarp; r0 < rows; r0 += n_warps * kRowsPerWarp) {
+    const long long r = r0 + sub;
+    float acc = 0.f;
+    if (r < rows) {
+      const uint4 a = __ldg(reinterpret_cast<const uint4*>(O + r * D) + piece);
+      const uint4 g = __ldg(reinterpret_cast<const uint4*>(dO + r * D) + piece);
+      const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&a);
+      const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&g);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 af = __bfloat1622float2(a2[e]), gf = __bfloat1622float2(g2[e]);
+        acc = fmaf(af.x, gf.x, acc);
+        acc = fmaf(af.y, gf.y, acc);
+      }
+    }
+#pragma unroll
+    for (int off = kLanesPerRow / 2; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+    if (r < rows && piece == 0) delta[r] = acc;
   }
 }
 

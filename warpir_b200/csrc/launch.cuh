@@ -545,6 +545,16 @@ inline int attn_bwd_impl(const void* Q, const void* K, const void* V, const void
   const bool wide = env_attn_bwd_rows() ? env_attn_bwd_rows() == 128 : true;
   if (wide) {
     // steps of 128 streamed rows: every operand is read as 128-row tiles, resident or streamed
+    {
+      // delta = rowsum(dO * O) first, in a small kernel of its own (one pass over O and dO)
+      const long long rows = static_cast<long long>(B) * Hq * S;
+      const int rows_per_block = 8 * (32 / static_cast<int>(D / 8));
+      long long blocks = (rows + rows_per_block - 1) / rows_per_block;
+      if (blocks > static_cast<long long>(dev->sm_count) * 16) blocks = static_cast<long long>(dev->sm_count) * 16;
+      if (D == 128) wir::attn_bwd_delta<128><<<static_cast<int>(blocks), 256, 0, stream>>>(p.O, p.dO, delta, rows);
+      else wir::attn_bwd_delta<64><<<static_cast<int>(blocks), 256, 0, stream>>>(p.O, p.dO, delta, rows);
+      WIR_CUDA(cudaGetLastError());
+    }
     p.out0 = dQ;
     p.out1 = nullptr;
     if (D == 128) rc = c ? launch_attn_bwd_wide_cfg<128, true, false>(q_x, g_x, k_x, v_x, p, stream) : launch_attn_bwd_wide_cfg<128, false, false>(q_x, g_x, k_x, v_x, p, stream);
