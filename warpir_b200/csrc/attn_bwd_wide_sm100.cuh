@@ -12,6 +12,11 @@
 //   P  = 2^(c T0 - LSE log2e)    dS = P (T1 - delta) scale               (compute warps, packed to bf16 in place)
 //   DKV:  B1: acc0 += P Y1 (dV)  B2: acc1 += dS Y0 (dK)       else  B: acc0 += dS Y0 (dQ)     (A from tensor memory)
 //
+// In the dQ launch LSE and delta belong to the thread's row and sit in two registers.  In the dK / dV launch they
+// belong to the COLUMN (the streamed query), 128 of each per step; there the tensor core subtracts them: one more
+// k-step per score tile multiplies rows of ones with rows that hold -LSE / scale (for A1) and -delta (for A2) in
+// three bf16 pieces, so that T0 = S - LSE / scale and T1 = dP - delta arrive ready (AttnBwdWideSmem::kExtraOffset).
+//
 // Why 128 rows per step: the warp that issues the MMAs is the kernel's clock.  It gets through its own dependent
 // instructions at 6-12 clocks each and pays 75-150 for every look at a barrier, and the tensor core's queue is
 // only about four MMAs deep; with 64-row steps (16 MMAs of 128 x 64 x 16, which from shared memory take 48 clocks
@@ -47,14 +52,21 @@ constexpr int kBw2Rows = 128;   // rows of the resident AND of the streamed tile
 
 template <int D, bool DKV>
 struct AttnBwdWideSmem {
-  static constexpr int kSlots = (D == 128) ? 5 : 10;                 // ring of streamed tiles
+  // ring of streamed tiles; the dK / dV launch gives one 32 KB slot up for the chunk of extra operands below
+  static constexpr int kSlots = (D == 128) ? (DKV ? 4 : 5) : 10;
   static constexpr int kChunkBytes = kBw2Rows * 128;                 // 128 rows x 64 bf16
   static constexpr int kTileBytes = (D / 64) * kChunkBytes;
   static constexpr int kRingOffset = 2 * kTileBytes;
-  static constexpr int kStatsOffset = kRingOffset + kSlots * kTileBytes;   // [2 vectors][128] floats
-  static constexpr int kBarOffset = kStatsOffset + 2 * kBw2Rows * 4;
-  // x_full, y_full[S], y_empty[S], t0_full, t1_full, p_ready, ds_ready, acc_done, drain
-  static constexpr int kNumBars = 2 * kSlots + 7;
+  // dK / dV launch: one K-major chunk (128 rows x 64 columns, 128-byte swizzle) whose k-steps 0, 1, 2 are three
+  // operands of their own: rows of (1, 1, 1, 0 ...); rows of -LSE / scale of the step's queries in three bf16
+  // pieces; rows of -delta likewise.  One more MMA per score tile adds ones x (-LSE / scale)^T to Q K^T and
+  // ones x (-delta)^T to dO V^T, so the compute warps get c S - LSE log2e and dP - delta without reading a
+  // statistic per column from shared memory (which cost the launch a sixth of its step).
+  static constexpr int kExtraOffset = kRingOffset + kSlots * kTileBytes;
+  static constexpr int kExtraBytes = DKV ? kChunkBytes : 0;
+  static constexpr int kBarOffset = kExtraOffset + kExtraBytes;
+  // x_full, y_full[S], y_empty[S], t0_full, t1_full, p_ready, ds_ready, acc_done, drain, e_ready
+  static constexpr int kNumBars = 2 * kSlots + 8;
   static constexpr int kTmemPtrOffset = kBarOffset + kNumBars * 8;
   static constexpr int kAbortOffset = kTmemPtrOffset + 4;
   static constexpr int kBytes = kAbortOffset + 4;
@@ -72,12 +84,13 @@ attn_bwd_wide_sm100(const __grid_constant__ CUtensorMap tmap_x0, const __grid_co
   constexpr uint32_t kT1Col = 128, kAccCol = 256;
   constexpr uint32_t kPackCol = 32;    // packed P / dS start here inside T0 / T1
   // One pair of exponentials in so many takes the FMA pipe (a cubic) instead of the exponential unit; 0: none.
-  // Measured per launch (clocks per step): the dQ launch, whose compute phases have no other work, 2730 with one
-  // pair in four and 3410 with none; the dK / dV launch is faster with none.
+  // Measured in clocks per step: the dQ launch 2730 with one pair in four, 3410 with none.  The dK / dV launch
+  // gains 0.4 % from the same share now that its loop holds nothing else but a multiplication; while it still
+  // read its statistics from shared memory there, any share made it slower.
 #if defined(WIR_BWD_POLY_DQ) && defined(WIR_BWD_POLY_DKV)
   constexpr int kPolyEvery = DKV ? WIR_BWD_POLY_DKV : WIR_BWD_POLY_DQ;
 #else
-  constexpr int kPolyEvery = DKV ? 0 : 4;
+  constexpr int kPolyEvery = 4;
 #endif
 
   extern __shared__ uint8_t smem_raw[];
@@ -93,9 +106,9 @@ attn_bwd_wide_sm100(const __grid_constant__ CUtensorMap tmap_x0, const __grid_co
   const uint32_t ds_ready = bar_base + 8u * (4 + 2 * SLOTS);
   const uint32_t acc_done = bar_base + 8u * (5 + 2 * SLOTS);
   const uint32_t drain_bar = bar_base + 8u * (6 + 2 * SLOTS);
+  const uint32_t e_ready = bar_base + 8u * (7 + 2 * SLOTS);     // dK / dV launch: the first step's extra operands are written
   volatile uint32_t* tmem_ptr_slot = reinterpret_cast<volatile uint32_t*>(smem + L::kTmemPtrOffset);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kAbortOffset);
-  float* stats = reinterpret_cast<float*>(smem + L::kStatsOffset);
   const AbortCtx ctx{abort_flag, p.status};
 
   const int warp = threadIdx.x >> 5;
@@ -159,6 +172,7 @@ attn_bwd_wide_sm100(const __grid_constant__ CUtensorMap tmap_x0, const __grid_co
     mbar_init(ds_ready, kBwdComputeThreads);
     mbar_init(acc_done, 1);
     mbar_init(drain_bar, 1);
+    mbar_init(e_ready, kBwdComputeThreads);
     fence_mbar_init();
     fence_proxy_async_smem();
     if (n_it > 0) {
@@ -240,20 +254,29 @@ attn_bwd_wide_sm100(const __grid_constant__ CUtensorMap tmap_x0, const __grid_co
                         (accumulate != 0u || m > 0) ? 1u : 0u);
       }
     };
+    // dK / dV launch: one more k-step per score tile, ones x (statistic)^T (see AttnBwdWideSmem::kExtraOffset);
+    // which = 1: -LSE / scale into T0, 2: -delta into T1
+    const uint32_t extra_lo = smem_desc_lo(smem_base + L::kExtraOffset, 16);
+    auto issue_extra = [&](uint32_t t_col, uint32_t which) {
+      if constexpr (DKV) mma_ss_elect(tmem_base + t_col, extra_lo, desc_hi, extra_lo + 2u * which, desc_hi, idesc_t, 1u);
+    };
     bool ok = true;
     WIR_TRACE_DECL;
     RingPos pos0{0u, 0u}, pos1{1u, 0u};     // Y0(j), Y1(j) of the current step; the next step's are two tiles on
 
     if (n_it > 0) ok = mbar_wait_warp(x_full, 0, ctx, kRoleMma, 1, 0);
+    if (DKV && ok && n_it > 0) ok = mbar_wait_warp(e_ready, 0, ctx, kRoleMma, 2, 0);
     if (ok && n_it > 0) ok = wait_tile(pos0, 0);
     if (ok && n_it > 0) {
       tc_fence_after();
       issue_a(0, x0d, pos0);
+      issue_extra(0, 1);
       mma_commit_elect(t0_full);
       ok = wait_tile(pos1, 0);
       if (ok) {
         tc_fence_after();
         issue_a(kT1Col, x1d, pos1);
+        issue_extra(kT1Col, 2);
         mma_commit_elect(t1_full);
         if (!DKV) mma_commit_elect(y_empty(pos1.slot));      // dQ launch: A2 is the last reader of V(j)
       }
@@ -270,7 +293,8 @@ attn_bwd_wide_sm100(const __grid_constant__ CUtensorMap tmap_x0, const __grid_co
       if (more) {
         const bool both = mbar_test_wait(y_full(nxt0.slot), nxt0.phase) & mbar_test_wait(y_full(nxt1.slot), nxt1.phase);
         landed1 = __all_sync(0xffffffffu, both);
-        if (!landed1 && !wait_tile(nxt0, it + 1)) { ok = false; break; }
+        // (dK / dV launch: if the next Q tile is still on its way, B1 goes out first; the ring there is two steps deep)
+        if (!DKV && !landed1 && !wait_tile(nxt0, it + 1)) { ok = false; break; }
       }
       if (lane == 0) WIR_TRACE_EVENT(p.trace, 0, 0, it);
       if (!mbar_wait_warp(p_ready, ph, ctx, kRoleMma, 20, it)) { ok = false; break; }
@@ -279,9 +303,14 @@ attn_bwd_wide_sm100(const __grid_constant__ CUtensorMap tmap_x0, const __grid_co
       if constexpr (DKV) {
         issue_b(kAccCol, kPackCol, pos1, acc);                 // dV += P^T dO
         mma_commit_elect(y_empty(pos1.slot));
+        if (!landed1) {
+          if (!wait_tile(nxt0, it + 1)) { ok = false; break; }
+          tc_fence_after();
+        }
       }
       if (more) {
         issue_a(0, x0d, nxt0);                                  // next scores, behind the MMAs that read P
+        issue_extra(0, 1);
         mma_commit_elect(t0_full);
       }
       if (lane == 0) WIR_TRACE_EVENT(p.trace, 0, 2, it);
@@ -294,6 +323,7 @@ attn_bwd_wide_sm100(const __grid_constant__ CUtensorMap tmap_x0, const __grid_co
       if (!more) mma_commit_elect(acc_done);
       if (more) {
         issue_a(kT1Col, x1d, nxt1);                             // next dP, behind the MMAs that read dS
+        issue_extra(kT1Col, 2);
         mma_commit_elect(t1_full);
         if (!DKV) mma_commit_elect(y_empty(nxt1.slot));
       }
@@ -332,57 +362,59 @@ attn_bwd_wide_sm100(const __grid_constant__ CUtensorMap tmap_x0, const __grid_co
       }
     }
 
-    // DKV: the per-column statistics of a step (LSE and delta of its 128 queries) are staged in shared memory:
-    // thread t of group 0 fetches LSE of query t, of group 1 delta of query t, one step ahead
-    // (the raw value: the factor is applied when the value is stored a step later -- a multiplication right
-    //  behind the load would hold the warp until the load has come back, which is what fetching ahead avoids)
+    // DKV: the statistics of a step's 128 queries (LSE, delta) reach the scores through one more MMA per score
+    // tile (see AttnBwdWideSmem::kExtraOffset): thread t of group 0 writes -LSE / scale of query t, thread t of
+    // group 1 -delta of query t, as three bf16 pieces into row t of its k-step of the extra chunk, for the NEXT
+    // step, once the MMA that read the current step's values has completed.  The values are fetched from global
+    // memory a step before that.
     auto fetch_stat = [&](int it) -> float {
       const int q = y_tile_of(it) * kBw2Rows + tid;
       const size_t r = static_cast<size_t>(y_plane_of(it)) * p.S + min(q, p.S - 1);
       return (half == 0) ? p.LSE[r] : p.delta[r];
     };
-    const float stat_factor = (half == 0) ? kLog2e : p.scale;
+    const float stat_factor = (half == 0) ? -1.0f / p.scale : -1.0f;
+    // k-step `slot` of row `row` of the extra chunk: 16 bf16 = two 16-byte units, swizzled like every K-major tile
+    // here (unit u of row r at r / 8 * 1024 + r % 8 * 128 + (u ^ r % 8) * 16)
+    auto write_extra = [&](int slot, int row, uint32_t w0, uint32_t w1) {
+      uint8_t* base = smem + L::kExtraOffset + (row >> 3) * 1024 + (row & 7) * 128;
+      *reinterpret_cast<uint4*>(base + (((2 * slot) ^ (row & 7)) << 4)) = make_uint4(w0, w1, 0u, 0u);
+      *reinterpret_cast<uint4*>(base + (((2 * slot + 1) ^ (row & 7)) << 4)) = make_uint4(0u, 0u, 0u, 0u);
+    };
+    auto write_stat = [&](float raw) {         // three bf16 pieces whose sum is raw * stat_factor to 24 bits
+      const float v = raw * stat_factor;
+      const __nv_bfloat16 h = __float2bfloat16_rn(v);
+      const float r1 = v - __bfloat162float(h);
+      const __nv_bfloat16 m = __float2bfloat16_rn(r1);
+      const __nv_bfloat16 l = __float2bfloat16_rn(r1 - __bfloat162float(m));
+      const uint32_t w0 = static_cast<uint32_t>(__bfloat16_as_ushort(h)) | (static_cast<uint32_t>(__bfloat16_as_ushort(m)) << 16);
+      write_extra(1 + half, tid, w0, static_cast<uint32_t>(__bfloat16_as_ushort(l)));
+    };
     float stat_next = 0.f;
-    if (DKV && n_it > 0) stat_next = fetch_stat(0);
+    if constexpr (DKV) {
+      if (n_it > 0) {
+        if (half == 0) write_extra(0, tid, 0x3f803f80u, 0x00003f80u);      // (1, 1, 1, 0 ...)
+        write_stat(fetch_stat(0));
+        if (n_it > 1) stat_next = fetch_stat(1);
+        fence_proxy_async_smem();
+        mbar_arrive(e_ready);
+      }
+    }
     if (traced) WIR_TRACE_EVENT(p.trace, 1 + half, 91, 0);     // prologue done
 
     for (int it = 0; it < n_it; ++it) {
       const uint32_t ph = static_cast<uint32_t>(it) & 1u;
       const int y_row0 = y_tile_of(it) * kBw2Rows;
-      if constexpr (DKV) {
-        // Group 0 publishes the step's LSE here: everybody has passed the previous step's second barrier, after
-        // which nobody reads LSE.  Delta, which is read until the end of the previous step, follows behind this
-        // step's first barrier (which every thread reaches only after its previous step).
-        if (half == 0) {
-          stats[tid] = stat_next * stat_factor;
-          if (it + 1 < n_it) stat_next = fetch_stat(it + 1);
-        }
-      }
       if (traced) WIR_TRACE_EVENT(p.trace, 1 + half, 10, it);
       // ---- P from T0
       bool got = mbar_wait(t0_full, ph, ctx, kRoleSoftmax, 0, it);
-      if constexpr (DKV) {
-        // the compute warps meet at named barriers every step (they publish the statistics), so they must
-        // agree on going on
-        uint32_t all;
-        asm volatile(
-            "{\n\t.reg .pred a, q;\n\t"
-            "setp.ne.u32 q, %1, 0;\n\t"
-            "bar.red.and.pred a, 3, 256, q;\n\t"
-            "selp.u32 %0, 1, 0, a;\n\t}"
-            : "=r"(all)
-            : "r"(got ? 1u : 0u)
-            : "memory");
-        if (all == 0) { ok = false; break; }
-      } else if (!__all_sync(0xffffffffu, got)) {
-        ok = false;
-        break;
-      }
+      if (!__all_sync(0xffffffffu, got)) { ok = false; break; }
       tc_fence_after();
       if constexpr (DKV) {
-        if (half == 1) {
-          stats[kBw2Rows + tid] = stat_next * stat_factor;       // published by the step's second barrier
-          if (it + 1 < n_it) stat_next = fetch_stat(it + 1);
+        // the MMA that read this step's -LSE / scale is done: the next step's may take its place
+        if (half == 0 && it + 1 < n_it) {
+          write_stat(stat_next);
+          if (it + 2 < n_it) stat_next = fetch_stat(it + 2);
+          fence_proxy_async_smem();
         }
       }
       if (traced) WIR_TRACE_EVENT(p.trace, 1 + half, 11, it);
@@ -400,57 +432,42 @@ attn_bwd_wide_sm100(const __grid_constant__ CUtensorMap tmap_x0, const __grid_co
         tmem_wait_ld();
         if (traced) WIR_TRACE_EVENT(p.trace, 1 + half, 15, it);
         // in pairs (packed f32x2 arithmetic); one pair in kPolyEvery takes its exponentials on the FMA pipe
-        // (a cubic, relative error below 6e-4, far inside bf16's 4e-3): the exponential unit retires 16 results
-        // per clock per SM, which alone would take 1024 clocks per step
+        // (a cubic, relative error below 6e-4, far inside bf16's 4e-3)
         const float2 c2 = make_float2(c, c);
-        const float4* l4 = reinterpret_cast<const float4*>(stats + half * 64);   // 16-byte loads: one per four columns
+        const float2 l2 = make_float2(-row_l2, -row_l2);       // (dK / dV launch: zero, the tensor core subtracted it)
         // The loop exists twice, with and without the mask: a test of `masked` inside it, once per pair, is a
-        // branch per pair, across which the compiler does not move instructions -- every pair then runs through
-        // its chain of FMA, exponential and conversion alone, 55 clocks at a time (1800 clocks per step; the
-        // exponential unit needs 1024).
+        // branch per pair, across which the compiler does not move instructions.
         auto p_phase = [&](auto masked_c) {
           constexpr bool kMasked = decltype(masked_c)::value;
 #pragma unroll
-          for (int k4 = 0; k4 < 16; ++k4) {
-            float4 lq = make_float4(row_l2, row_l2, row_l2, row_l2);
-#if !(defined(WIR_BWD_ABLATE) && WIR_BWD_ABLATE == 6)     // measurement build 6: no per-column statistics from shared memory
-            if constexpr (DKV) lq = l4[k4];
-#endif
-#pragma unroll
-            for (int kk = 0; kk < 2; ++kk) {
-              const int k = 2 * k4 + kk;
-              const int col = half * 64 + 2 * k;
-              const float la = kk == 0 ? lq.x : lq.z, lb = kk == 0 ? lq.y : lq.w;
-              const float2 x = __ffma2_rn(make_float2(__uint_as_float(t0[2 * k]), __uint_as_float(t0[2 * k + 1])), c2,
-                                          make_float2(-la, -lb));
-              float2 e;
-              if (kPolyEvery > 0 && (k % (kPolyEvery > 0 ? kPolyEvery : 1)) == 0) {
-                e = ex2_fma2(x);
-              } else {
-                e.x = ex2_approx(x.x);
-                e.y = ex2_approx(x.y);
-              }
-              if constexpr (kMasked) {
-#pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                  const int y = y_row0 + col + h;             // index along the streamed tile
-                  const int qi = DKV ? y : x_row;             // query index
-                  const int ki = DKV ? x_row : y;             // key index
-                  if (qi >= p.S || ki >= p.S || (CAUSAL && ki > qi)) (h == 0 ? e.x : e.y) = 0.f;
-                }
-              }
-              pv[2 * k] = e.x;
-              pv[2 * k + 1] = e.y;
+          for (int k = 0; k < 32; ++k) {
+            const int col = half * 64 + 2 * k;
+            const float2 t = make_float2(__uint_as_float(t0[2 * k]), __uint_as_float(t0[2 * k + 1]));
+            const float2 x = DKV ? __fmul2_rn(t, c2) : __ffma2_rn(t, c2, l2);
+            float2 e;
+            if (kPolyEvery > 0 && (k % (kPolyEvery > 0 ? kPolyEvery : 1)) == 0) {
+              e = ex2_fma2(x);
+            } else {
+              e.x = ex2_approx(x.x);
+              e.y = ex2_approx(x.y);
             }
+            if constexpr (kMasked) {
+#pragma unroll
+              for (int h = 0; h < 2; ++h) {
+                const int y = y_row0 + col + h;             // index along the streamed tile
+                const int qi = DKV ? y : x_row;             // query index
+                const int ki = DKV ? x_row : y;             // key index
+                if (qi >= p.S || ki >= p.S || (CAUSAL && ki > qi)) (h == 0 ? e.x : e.y) = 0.f;
+              }
+            }
+            pv[2 * k] = e.x;
+            pv[2 * k + 1] = e.y;
           }
         };
         if (masked) p_phase(std::true_type{});
         else p_phase(std::false_type{});
         if (traced) WIR_TRACE_EVENT(p.trace, 1 + half, 16, it);
         if constexpr (DKV) {
-          // (packing with integer instructions instead of the conversion instruction measured 3-8 % slower, a
-          //  polynomial share of the exponentials in this launch 1-12 %: more instructions cost more than the
-          //  quarter-rate unit they would relieve)
           uint32_t pk[32];
 #pragma unroll
           for (int i = 0; i < 32; ++i) pk[i] = pack_bf16(pv[2 * i], pv[2 * i + 1]);
@@ -465,22 +482,15 @@ attn_bwd_wide_sm100(const __grid_constant__ CUtensorMap tmap_x0, const __grid_co
 
       // ---- dS from T1 and P
       got = mbar_wait(t1_full, ph, ctx, kRoleSoftmax, 1, it);
-      if constexpr (DKV) {
-        uint32_t all;
-        asm volatile(
-            "{\n\t.reg .pred a, q;\n\t"
-            "setp.ne.u32 q, %1, 0;\n\t"
-            "bar.red.and.pred a, 4, 256, q;\n\t"
-            "selp.u32 %0, 1, 0, a;\n\t}"
-            : "=r"(all)
-            : "r"(got ? 1u : 0u)
-            : "memory");
-        if (all == 0) { ok = false; break; }
-      } else if (!__all_sync(0xffffffffu, got)) {
-        ok = false;
-        break;
-      }
+      if (!__all_sync(0xffffffffu, got)) { ok = false; break; }
       tc_fence_after();
+      if constexpr (DKV) {
+        if (half == 1 && it + 1 < n_it) {      // as above, for -delta
+          write_stat(stat_next);
+          if (it + 2 < n_it) stat_next = fetch_stat(it + 2);
+          fence_proxy_async_smem();
+        }
+      }
       if (traced) WIR_TRACE_EVENT(p.trace, 1 + half, 13, it);
       {
         uint32_t t1[64];
@@ -489,28 +499,19 @@ attn_bwd_wide_sm100(const __grid_constant__ CUtensorMap tmap_x0, const __grid_co
         tmem_wait_ld();
         if (traced) WIR_TRACE_EVENT(p.trace, 1 + half, 17, it);
         const float2 s2 = make_float2(p.scale, p.scale);
-        const float4* d4 = reinterpret_cast<const float4*>(stats + kBw2Rows + half * 64);
+        const float2 d2 = make_float2(-row_ds, -row_ds);
         uint32_t dk[32];
 #pragma unroll
-        for (int k4 = 0; k4 < 16; ++k4) {
-          float4 dq = make_float4(row_ds, row_ds, row_ds, row_ds);
-#if !(defined(WIR_BWD_ABLATE) && WIR_BWD_ABLATE == 6)
-          if constexpr (DKV) dq = d4[k4];
-#endif
-#pragma unroll
-          for (int kk = 0; kk < 2; ++kk) {
-            const int k = 2 * k4 + kk;
-            const float da = kk == 0 ? dq.x : dq.z, db = kk == 0 ? dq.y : dq.w;
-            const float2 u = __ffma2_rn(make_float2(__uint_as_float(t1[2 * k]), __uint_as_float(t1[2 * k + 1])), s2,
-                                        make_float2(-da, -db));
-            const float2 d = __fmul2_rn(make_float2(pv[2 * k], pv[2 * k + 1]), u);
-            dk[k] = pack_bf16(d.x, d.y);
-          }
+        for (int k = 0; k < 32; ++k) {
+          const float2 t = make_float2(__uint_as_float(t1[2 * k]), __uint_as_float(t1[2 * k + 1]));
+          const float2 u = DKV ? __fmul2_rn(t, s2) : __ffma2_rn(t, s2, d2);
+          const float2 d = __fmul2_rn(make_float2(pv[2 * k], pv[2 * k + 1]), u);
+          dk[k] = pack_bf16(d.x, d.y);
         }
         tmem_st16(lane_base + kT1Col + kPackCol + half * 32, dk);
         tmem_st16(lane_base + kT1Col + kPackCol + half * 32 + 16, dk + 16);
+        tmem_wait_st();
       }
-      tmem_wait_st();
       tc_fence_before();
       mbar_arrive(ds_ready);
       if (traced) WIR_TRACE_EVENT(p.trace, 1 + half, 14, it);
