@@ -430,6 +430,11 @@ attn_bwd_wide_sm100(const __grid_constant__ CUtensorMap tmap_x0, const __grid_co
         tmem_ld32(lane_base + half * 64, t0);
         tmem_ld32(lane_base + half * 64 + 32, t0 + 32);
         tmem_wait_ld();
+        if constexpr (!DKV) {
+          // dQ launch: P stays in registers, so T0 is free as soon as it has been read: the next scores start now
+          tc_fence_before();
+          mbar_arrive(p_ready);
+        }
         if (traced) WIR_TRACE_EVENT(p.trace, 1 + half, 15, it);
         // in pairs (packed f32x2 arithmetic); one pair in kPolyEvery takes its exponentials on the FMA pipe
         // (a cubic, relative error below 6e-4, far inside bf16's 4e-3)
@@ -476,8 +481,10 @@ attn_bwd_wide_sm100(const __grid_constant__ CUtensorMap tmap_x0, const __grid_co
           tmem_wait_st();
         }
       }
-      tc_fence_before();
-      mbar_arrive(p_ready);
+      if constexpr (DKV) {
+        tc_fence_before();
+        mbar_arrive(p_ready);
+      }
       if (traced) WIR_TRACE_EVENT(p.trace, 1 + half, 12, it);
 
       // ---- dS from T1 and P
