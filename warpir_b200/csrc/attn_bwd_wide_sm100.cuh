@@ -24,22 +24,25 @@
 // is 24 or 32 MMAs of 128 x 128 x 16 at the full rate, with the same number of hand-offs as a 64-row step had.
 //
 // Tensor memory has no room to double-buffer 128-column score tiles next to the accumulators (T0 128 + T1 128 +
-// acc0 D + acc1 D = 512 at D = 128), so the overlap comes from the order of issue instead:
+// acc0 D + acc1 D = 512 at D = 128), so the overlap comes from the order of issue and from where the packed values
+// go.
 //
-//   B1(j)  A1(j+1)  B2(j)  A2(j+1)        (dQ launch:  A1(j+1)  B(j)  A2(j+1))
-//
-// P of step j is produced from T0 while A2(j) and B2(j-1) execute, dS from T1 (and the P values, which the
-// threads keep in registers) while B1(j) and A1(j+1) execute: each compute phase runs under two of the four MMA
-// groups.  MMAs execute in issue order, which makes the aliasing safe: A1(j+1) overwrites T0 (and P inside it)
-// behind B1(j), which reads P; A2(j+1) overwrites T1 behind B2(j) / B(j), which reads dS.
+// dQ launch:   A1(j+1)  B(j)  A2(j+1).  P stays in registers, so T0 is released as soon as it has been read and the
+//   next scores are computed under the whole of step j; dS (packed bf16) goes over T1 columns 32-95, which B(j)
+//   reads before A2(j+1) overwrites them (MMAs execute in issue order).
+// dK / dV launch:   A1(j+1) | B1(j) | B2(j)  A2(j+1).  Both packed tiles go into T1, which is dead once both groups
+//   have read it: P over columns 32-95, dS over the outer columns (0-31 and 96-127).  T0 is released as soon as it
+//   has been read, as in the dQ launch, so the exponentials of step j+1 never wait for an MMA of step j; what is
+//   left in line is dS(j) -> B2(j), A2(j+1) -> dS(j+1), with the exponentials of step j+1 running under those MMAs.
+//   (Before, P went back into T0: the next scores then had to follow B1(j), and the compute warps waited 1000 of
+//   3500 clocks per step for them.)
 //
 // Shared memory: X0, X1, then a ring of STREAMED TILES (not steps): Y0(0), Y1(0), Y0(1), ...; a tile goes back to
 // the producer behind the last MMA group that reads it (Y1(j) after B1(j), or after A2(j) in the dQ launch; Y0(j)
 // after B2(j) / B(j)).  Warp 0 is the TMA producer, warp 1 issues every MMA (whole warp, one elected lane, four
 // MMAs per instruction block), warps 2-9 are two compute warpgroups: thread = one tensor-memory lane (row), group
-// g takes columns 64 g ... of T0 / T1.  Packed P sits at columns 32-95 of T0 and packed dS at 32-95 of T1, so that
-// each group overwrites only columns it has loaded itself (group 0 loads 0-63 and writes 32-63, group 1 loads
-// 64-127 and writes 64-95).  Every wait is bounded.
+// g takes columns 64 g ... of T0 / T1 and overwrites only columns of T1 that it has read itself (group 0 reads
+// 0-63 and writes 0-63, group 1 reads 64-127 and writes 64-127).  Every wait is bounded.
 #pragma once
 
 #include <type_traits>
@@ -65,8 +68,8 @@ struct AttnBwdWideSmem {
   static constexpr int kExtraOffset = kRingOffset + kSlots * kTileBytes;
   static constexpr int kExtraBytes = DKV ? kChunkBytes : 0;
   static constexpr int kBarOffset = kExtraOffset + kExtraBytes;
-  // x_full, y_full[S], y_empty[S], t0_full, t1_full, p_ready, ds_ready, acc_done, drain, e_ready
-  static constexpr int kNumBars = 2 * kSlots + 8;
+  // x_full, y_full[S], y_empty[S], t0_full, t1_full, p_ready, ds_ready, acc_done, drain, e_ready, t0_free
+  static constexpr int kNumBars = 2 * kSlots + 9;
   static constexpr int kTmemPtrOffset = kBarOffset + kNumBars * 8;
   static constexpr int kAbortOffset = kTmemPtrOffset + 4;
   static constexpr int kBytes = kAbortOffset + 4;
@@ -82,7 +85,7 @@ attn_bwd_wide_sm100(const __grid_constant__ CUtensorMap tmap_x0, const __grid_co
   constexpr int SLOTS = L::kSlots;
   constexpr uint32_t kTmemCols = 512;
   constexpr uint32_t kT1Col = 128, kAccCol = 256;
-  constexpr uint32_t kPackCol = 32;    // packed P / dS start here inside T0 / T1
+  constexpr uint32_t kPackCol = 32;    // packed dS (dQ launch) / packed P (dK / dV launch) start here inside T1
   // One pair of exponentials in so many takes the FMA pipe (a cubic) instead of the exponential unit; 0: none.
   // Measured in clocks per step: the dQ launch 2730 with one pair in four, 3410 with none.  The dK / dV launch
   // gains 0.4 % from the same share now that its loop holds nothing else but a multiplication; while it still
@@ -107,6 +110,7 @@ attn_bwd_wide_sm100(const __grid_constant__ CUtensorMap tmap_x0, const __grid_co
   const uint32_t acc_done = bar_base + 8u * (5 + 2 * SLOTS);
   const uint32_t drain_bar = bar_base + 8u * (6 + 2 * SLOTS);
   const uint32_t e_ready = bar_base + 8u * (7 + 2 * SLOTS);     // dK / dV launch: the first step's extra operands are written
+  const uint32_t t0_free = bar_base + 8u * (8 + 2 * SLOTS);     // dK / dV launch: every compute thread has read T0
   volatile uint32_t* tmem_ptr_slot = reinterpret_cast<volatile uint32_t*>(smem + L::kTmemPtrOffset);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kAbortOffset);
   const AbortCtx ctx{abort_flag, p.status};
@@ -143,6 +147,21 @@ attn_bwd_wide_sm100(const __grid_constant__ CUtensorMap tmap_x0, const __grid_co
     return r;
   };
   auto tile_addr = [&](RingPos r) { return smem_base + L::kRingOffset + r.slot * L::kTileBytes; };
+  // Where tile `which` (0: Y0, 1: Y1) of step `it` sits.  Normally the ring is a FIFO of tiles in the order they are
+  // loaded (tile k = 2 it + which in slot k % SLOTS).  A ring of four slots (dK / dV launch at D = 128) is only two
+  // steps deep, and a FIFO would give Y0(it), the tile that is needed FIRST (its scores start as soon as the previous
+  // ones have been read), the slot that is released LAST (Y0(it-2), after B2).  There the two tiles of a step trade
+  // places every other step: Y0(it) takes the slot of Y1(it-2), which B1 releases a third of a step earlier.
+  constexpr bool kCross = DKV && SLOTS == 4;
+  auto pos_of = [](int it, int which) {
+    if constexpr (kCross) {
+      const uint32_t turn = (static_cast<uint32_t>(it) >> 1) & 1u;
+      return RingPos{2u * (static_cast<uint32_t>(it) & 1u) + (static_cast<uint32_t>(which) ^ turn), turn};
+    } else {
+      const uint32_t k = 2u * static_cast<uint32_t>(it) + static_cast<uint32_t>(which);
+      return RingPos{k % SLOTS, (k / SLOTS) & 1u};
+    }
+  };
 
   // Producer (thread 0, which also initialises the barriers): streamed tile `which` (0: Y0, 1: Y1) of step `it`
   // into the ring at `pos`.  The resident tiles and the first step go out before the CTA-wide barrier below.
@@ -173,6 +192,7 @@ attn_bwd_wide_sm100(const __grid_constant__ CUtensorMap tmap_x0, const __grid_co
     mbar_init(acc_done, 1);
     mbar_init(drain_bar, 1);
     mbar_init(e_ready, kBwdComputeThreads);
+    mbar_init(t0_free, kBwdComputeThreads);
     fence_mbar_init();
     fence_proxy_async_smem();
     if (n_it > 0) {
@@ -182,7 +202,7 @@ attn_bwd_wide_sm100(const __grid_constant__ CUtensorMap tmap_x0, const __grid_co
         tma_load_3d(smem_base + c * L::kChunkBytes, &tmap_x0, x_full, c * 64, x_row0, x_plane);
         tma_load_3d(smem_base + L::kTileBytes + c * L::kChunkBytes, &tmap_x1, x_full, c * 64, x_row0, x_plane);
       }
-      p_ok = load_tile(0, 0, p_pos);
+      p_ok = load_tile(0, 0, p_pos);        // (step 0 sits in slots 0 and 1 either way)
       p_pos = ring_next(p_pos, 1);
       if (p_ok) {
         p_ok = load_tile(0, 1, p_pos);
@@ -208,7 +228,7 @@ attn_bwd_wide_sm100(const __grid_constant__ CUtensorMap tmap_x0, const __grid_co
 #pragma unroll
         for (int which = 0; which < 2; ++which) {
           if (!ok) break;
-          ok = load_tile(it, which, p_pos);
+          ok = load_tile(it, which, kCross ? pos_of(it, which) : p_pos);
           if (ok) {
             p_pos = ring_next(p_pos, 1);
             ++issued;
@@ -216,12 +236,13 @@ attn_bwd_wide_sm100(const __grid_constant__ CUtensorMap tmap_x0, const __grid_co
         }
       }
       if (!ok || *abort_flag) {
-        // every copy in flight must have landed before the CTA may exit: tile k completes phase k / SLOTS of barrier k % SLOTS
+        // every copy in flight must have landed before the CTA may exit
         mbar_wait_quiet(x_full, 0);
         const int n = issued < SLOTS ? issued : SLOTS;
         for (int back = 1; back <= n; ++back) {
           const int k = issued - back;
-          mbar_wait_quiet(y_full(k % SLOTS), (k / SLOTS) & 1);
+          const RingPos r = pos_of(k >> 1, k & 1);
+          mbar_wait_quiet(y_full(r.slot), r.phase);
         }
       }
     }
@@ -245,13 +266,14 @@ attn_bwd_wide_sm100(const __grid_constant__ CUtensorMap tmap_x0, const __grid_co
     };
     // acc += (P | dS) Y: the 128 streamed rows are the K dimension, eight k-steps of 16 rows (2048 bytes of an
     // MN-major tile whose 64-column chunks are kChunkBytes apart), A = 8 packed columns of tensor memory per step
-    auto issue_b = [&](uint32_t acc_col, uint32_t a_col, RingPos r, uint32_t accumulate) {
+    // (a_col0 / a_col1: where the packed values of streamed rows 0-63 / 64-127 sit)
+    auto issue_b = [&](uint32_t acc_col, uint32_t a_col0, uint32_t a_col1, RingPos r, uint32_t accumulate) {
       const uint64_t yd = desc64(smem_desc_lo(tile_addr(r), L::kChunkBytes), desc_hi);
 #pragma unroll
       for (int m = 0; m < kBw2Rows / 64; ++m) {
         const uint64_t y = yd + static_cast<uint64_t>(512 * m);
-        mma_ts_elect_x4(tmem_base + acc_col, tmem_base + a_col + 32 * m, y, y + 128, y + 256, y + 384, idesc_acc,
-                        (accumulate != 0u || m > 0) ? 1u : 0u);
+        mma_ts_elect_x4(tmem_base + acc_col, tmem_base + (m == 0 ? a_col0 : a_col1), y, y + 128, y + 256, y + 384,
+                        idesc_acc, (accumulate != 0u || m > 0) ? 1u : 0u);
       }
     };
     // dK / dV launch: one more k-step per score tile, ones x (statistic)^T (see AttnBwdWideSmem::kExtraOffset);
@@ -284,48 +306,80 @@ attn_bwd_wide_sm100(const __grid_constant__ CUtensorMap tmap_x0, const __grid_co
     for (int it = 0; ok && it < n_it; ++it) {
       const uint32_t ph = static_cast<uint32_t>(it) & 1u;
       const bool more = it + 1 < n_it;
-      const RingPos nxt0 = ring_next(pos0, 2), nxt1 = ring_next(pos1, 2);
+      const RingPos nxt0 = kCross ? pos_of(it + 1, 0) : ring_next(pos0, 2);
+      const RingPos nxt1 = kCross ? pos_of(it + 1, 1) : ring_next(pos1, 2);
       const uint32_t acc = it > 0 ? 1u : 0u;
       // the next step's tiles were asked for long ago: look at their barriers before the waits that are true
       // dependencies, so that nothing but a fence stands between those and the MMAs
       // (both tiles' barriers tested together: one vote, one branch; the full waits only if one is still open)
       bool landed1 = !more;
-      if (more) {
+      if (!DKV && more) {
         const bool both = mbar_test_wait(y_full(nxt0.slot), nxt0.phase) & mbar_test_wait(y_full(nxt1.slot), nxt1.phase);
         landed1 = __all_sync(0xffffffffu, both);
-        // (dK / dV launch: if the next Q tile is still on its way, B1 goes out first; the ring there is two steps deep)
-        if (!DKV && !landed1 && !wait_tile(nxt0, it + 1)) { ok = false; break; }
       }
       if (lane == 0) WIR_TRACE_EVENT(p.trace, 0, 0, it);
-      if (!mbar_wait_warp(p_ready, ph, ctx, kRoleMma, 20, it)) { ok = false; break; }
-      tc_fence_after();
-      if (lane == 0) WIR_TRACE_EVENT(p.trace, 0, 1, it);
       if constexpr (DKV) {
-        issue_b(kAccCol, kPackCol, pos1, acc);                 // dV += P^T dO
-        mma_commit_elect(y_empty(pos1.slot));
-        if (!landed1) {
-          if (!wait_tile(nxt0, it + 1)) { ok = false; break; }
+        // the next scores as soon as every thread has read the current ones (P goes into T1, not back into T0) and
+        // their Q tile has landed; if it has not, B1 goes first
+        auto next_scores = [&]() {
           tc_fence_after();
+          issue_a(0, x0d, nxt0);
+          issue_extra(0, 1);
+          mma_commit_elect(t0_full);
+        };
+        bool scores_out = !more;
+        if (more) {
+          if (!mbar_wait_warp(t0_free, ph, ctx, kRoleMma, 15, it)) { ok = false; break; }
+          if (__all_sync(0xffffffffu, mbar_test_wait(y_full(nxt0.slot), nxt0.phase))) {
+            next_scores();
+            scores_out = true;
+          }
         }
-      }
-      if (more) {
-        issue_a(0, x0d, nxt0);                                  // next scores, behind the MMAs that read P
-        issue_extra(0, 1);
-        mma_commit_elect(t0_full);
-      }
-      if (lane == 0) WIR_TRACE_EVENT(p.trace, 0, 2, it);
-      if (!landed1 && !wait_tile(nxt1, it + 1)) { ok = false; break; }
-      if (!mbar_wait_warp(ds_ready, ph, ctx, kRoleMma, 30, it)) { ok = false; break; }
-      tc_fence_after();
-      if (lane == 0) WIR_TRACE_EVENT(p.trace, 0, 3, it);
-      issue_b(DKV ? kAccCol + D : kAccCol, kT1Col + kPackCol, pos0, acc);   // dK += dS^T Q   /   dQ += dS K
-      mma_commit_elect(y_empty(pos0.slot));
-      if (!more) mma_commit_elect(acc_done);
-      if (more) {
-        issue_a(kT1Col, x1d, nxt1);                             // next dP, behind the MMAs that read dS
-        issue_extra(kT1Col, 2);
-        mma_commit_elect(t1_full);
-        if (!DKV) mma_commit_elect(y_empty(nxt1.slot));
+        if (!mbar_wait_warp(p_ready, ph, ctx, kRoleMma, 20, it)) { ok = false; break; }
+        tc_fence_after();
+        if (lane == 0) WIR_TRACE_EVENT(p.trace, 0, 1, it);
+        issue_b(kAccCol, kT1Col + kPackCol, kT1Col + kPackCol + 32, pos1, acc);      // dV += P^T dO
+        mma_commit_elect(y_empty(pos1.slot));
+        if (!scores_out) {
+          if (!wait_tile(nxt0, it + 1)) { ok = false; break; }
+          next_scores();
+        }
+        if (lane == 0) WIR_TRACE_EVENT(p.trace, 0, 2, it);
+        if (!mbar_wait_warp(ds_ready, ph, ctx, kRoleMma, 30, it)) { ok = false; break; }
+        tc_fence_after();
+        if (lane == 0) WIR_TRACE_EVENT(p.trace, 0, 3, it);
+        issue_b(kAccCol + D, kT1Col, kT1Col + 96, pos0, acc);                         // dK += dS^T Q
+        mma_commit_elect(y_empty(pos0.slot));
+        if (!more) mma_commit_elect(acc_done);
+        if (more) {
+          if (!wait_tile(nxt1, it + 1)) { ok = false; break; }    // (B2 is executing meanwhile)
+          tc_fence_after();
+          issue_a(kT1Col, x1d, nxt1);                             // next dP, behind the MMAs that read P and dS
+          issue_extra(kT1Col, 2);
+          mma_commit_elect(t1_full);
+        }
+      } else {
+        if (!landed1 && !wait_tile(nxt0, it + 1)) { ok = false; break; }
+        if (!mbar_wait_warp(p_ready, ph, ctx, kRoleMma, 20, it)) { ok = false; break; }
+        tc_fence_after();
+        if (lane == 0) WIR_TRACE_EVENT(p.trace, 0, 1, it);
+        if (more) {
+          issue_a(0, x0d, nxt0);                                  // next scores (T0 has been read)
+          mma_commit_elect(t0_full);
+        }
+        if (lane == 0) WIR_TRACE_EVENT(p.trace, 0, 2, it);
+        if (!landed1 && !wait_tile(nxt1, it + 1)) { ok = false; break; }
+        if (!mbar_wait_warp(ds_ready, ph, ctx, kRoleMma, 30, it)) { ok = false; break; }
+        tc_fence_after();
+        if (lane == 0) WIR_TRACE_EVENT(p.trace, 0, 3, it);
+        issue_b(kAccCol, kT1Col + kPackCol, kT1Col + kPackCol + 32, pos0, acc);       // dQ += dS K
+        mma_commit_elect(y_empty(pos0.slot));
+        if (!more) mma_commit_elect(acc_done);
+        if (more) {
+          issue_a(kT1Col, x1d, nxt1);                             // next dP, behind the MMAs that read dS
+          mma_commit_elect(t1_full);
+          mma_commit_elect(y_empty(nxt1.slot));                   // A2 is the last reader of V(j+1)
+        }
       }
       if (lane == 0) WIR_TRACE_EVENT(p.trace, 0, 4, it);
       pos0 = nxt0;
@@ -389,14 +443,14 @@ attn_bwd_wide_sm100(const __grid_constant__ CUtensorMap tmap_x0, const __grid_co
       const uint32_t w0 = static_cast<uint32_t>(__bfloat16_as_ushort(h)) | (static_cast<uint32_t>(__bfloat16_as_ushort(m)) << 16);
       write_extra(1 + half, tid, w0, static_cast<uint32_t>(__bfloat16_as_ushort(l)));
     };
-    float stat_next = 0.f;
+    float stat_next = 0.f, stat_fetched = 0.f;
     if constexpr (DKV) {
       if (n_it > 0) {
         if (half == 0) write_extra(0, tid, 0x3f803f80u, 0x00003f80u);      // (1, 1, 1, 0 ...)
         write_stat(fetch_stat(0));
-        if (n_it > 1) stat_next = fetch_stat(1);
         fence_proxy_async_smem();
         mbar_arrive(e_ready);
+        if (n_it > 1) stat_next = fetch_stat(1);
       }
     }
     if (traced) WIR_TRACE_EVENT(p.trace, 1 + half, 91, 0);     // prologue done
@@ -413,7 +467,6 @@ attn_bwd_wide_sm100(const __grid_constant__ CUtensorMap tmap_x0, const __grid_co
         // the MMA that read this step's -LSE / scale is done: the next step's may take its place
         if (half == 0 && it + 1 < n_it) {
           write_stat(stat_next);
-          if (it + 2 < n_it) stat_next = fetch_stat(it + 2);
           fence_proxy_async_smem();
         }
       }
@@ -425,15 +478,21 @@ attn_bwd_wide_sm100(const __grid_constant__ CUtensorMap tmap_x0, const __grid_co
       const bool masked = ragged || diagonal;
 
       float pv[64];      // this thread's 64 values of P, kept for the dS phase
+      uint32_t pk[DKV ? 32 : 1];   // dK / dV launch: and packed to bf16, stored once T1 has been read
       {
         uint32_t t0[64];
         tmem_ld32(lane_base + half * 64, t0);
         tmem_ld32(lane_base + half * 64 + 32, t0 + 32);
         tmem_wait_ld();
-        if constexpr (!DKV) {
-          // dQ launch: P stays in registers, so T0 is free as soon as it has been read: the next scores start now
-          tc_fence_before();
-          mbar_arrive(p_ready);
+        // T0 is free as soon as it has been read, and the next scores start now: P stays in registers (dQ launch)
+        // or goes into T1 (dK / dV launch)
+        tc_fence_before();
+        mbar_arrive(DKV ? t0_free : p_ready);
+        if constexpr (DKV) {
+          // The statistic for the step after the next is fetched HERE, with the exponentials between the load and
+          // the next fence or arrival: both wait for every earlier access of the thread, a load from global memory
+          // included, and right behind the load they kept the thread waiting for it.
+          if (it + 2 < n_it) stat_fetched = fetch_stat(it + 2);
         }
         if (traced) WIR_TRACE_EVENT(p.trace, 1 + half, 15, it);
         // in pairs (packed f32x2 arithmetic); one pair in kPolyEvery takes its exponentials on the FMA pipe
@@ -467,25 +526,13 @@ attn_bwd_wide_sm100(const __grid_constant__ CUtensorMap tmap_x0, const __grid_co
             }
             pv[2 * k] = e.x;
             pv[2 * k + 1] = e.y;
+            if constexpr (DKV) pk[k] = pack_bf16(e.x, e.y);
           }
         };
         if (masked) p_phase(std::true_type{});
         else p_phase(std::false_type{});
         if (traced) WIR_TRACE_EVENT(p.trace, 1 + half, 16, it);
-        if constexpr (DKV) {
-          uint32_t pk[32];
-#pragma unroll
-          for (int i = 0; i < 32; ++i) pk[i] = pack_bf16(pv[2 * i], pv[2 * i + 1]);
-          tmem_st16(lane_base + kPackCol + half * 32, pk);
-          tmem_st16(lane_base + kPackCol + half * 32 + 16, pk + 16);
-          tmem_wait_st();
-        }
       }
-      if constexpr (DKV) {
-        tc_fence_before();
-        mbar_arrive(p_ready);
-      }
-      if (traced) WIR_TRACE_EVENT(p.trace, 1 + half, 12, it);
 
       // ---- dS from T1 and P
       got = mbar_wait(t1_full, ph, ctx, kRoleSoftmax, 1, it);
@@ -494,7 +541,6 @@ attn_bwd_wide_sm100(const __grid_constant__ CUtensorMap tmap_x0, const __grid_co
       if constexpr (DKV) {
         if (half == 1 && it + 1 < n_it) {      // as above, for -delta
           write_stat(stat_next);
-          if (it + 2 < n_it) stat_next = fetch_stat(it + 2);
           fence_proxy_async_smem();
         }
       }
@@ -505,6 +551,15 @@ attn_bwd_wide_sm100(const __grid_constant__ CUtensorMap tmap_x0, const __grid_co
         tmem_ld32(lane_base + kT1Col + half * 64 + 32, t1 + 32);
         tmem_wait_ld();
         if (traced) WIR_TRACE_EVENT(p.trace, 1 + half, 17, it);
+        if constexpr (DKV) {
+          // P, packed, over T1 columns 32-95 (each group over columns it has just read): B1 reads it from there
+          tmem_st16(lane_base + kT1Col + kPackCol + half * 32, pk);
+          tmem_st16(lane_base + kT1Col + kPackCol + half * 32 + 16, pk + 16);
+          tmem_wait_st();
+          tc_fence_before();
+          mbar_arrive(p_ready);
+          if (traced) WIR_TRACE_EVENT(p.trace, 1 + half, 12, it);
+        }
         const float2 s2 = make_float2(p.scale, p.scale);
         const float2 d2 = make_float2(-row_ds, -row_ds);
         uint32_t dk[32];
@@ -515,12 +570,16 @@ attn_bwd_wide_sm100(const __grid_constant__ CUtensorMap tmap_x0, const __grid_co
           const float2 d = __fmul2_rn(make_float2(pv[2 * k], pv[2 * k + 1]), u);
           dk[k] = pack_bf16(d.x, d.y);
         }
-        tmem_st16(lane_base + kT1Col + kPackCol + half * 32, dk);
-        tmem_st16(lane_base + kT1Col + kPackCol + half * 32 + 16, dk + 16);
+        // dS, packed: dQ launch over T1 columns 32-95; dK / dV launch, where P sits there, over the outer columns
+        // (group 0: 0-31, group 1: 96-127)
+        const uint32_t ds_col = kT1Col + (DKV ? half * 96 : kPackCol + half * 32);
+        tmem_st16(lane_base + ds_col, dk);
+        tmem_st16(lane_base + ds_col + 16, dk + 16);
         tmem_wait_st();
       }
       tc_fence_before();
       mbar_arrive(ds_ready);
+      stat_next = stat_fetched;
       if (traced) WIR_TRACE_EVENT(p.trace, 1 + half, 14, it);
     }
 
