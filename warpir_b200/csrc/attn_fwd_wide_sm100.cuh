@@ -17,6 +17,15 @@
 //   warps 9, 11        idle: they only complete the warpgroup whose registers move to the
 //                      softmax warps (setmaxnreg 168 -> 104 / 200)
 //
+// D = 64: the two accumulators need only 128 columns, which leaves room for a THIRD score tile.  The three rotate
+// between the two Q tiles (the k-th Q K^T of the CTA, in the order the issuer sends them, goes into score tile
+// k % 3; the issuer sends P V number m and then Q K^T number m + 3 into the tile that P V has just read), so a
+// Q tile finds its next scores waiting when its softmax ends and the two softmaxes run all the time: the
+// exponential unit, which bounds this head dimension (16384 exponentials per 128 x 128 block against 512 clocks
+// of MMAs), went from 63 % busy to what 750 TFLOP/s need (660 before; causal B4 H32 S8192).  A Q tile announces P
+// of block j only once P V of block j - 1 has completed: otherwise it could get two blocks ahead of a held-up
+// issuer and the parity of the "P ready" barrier would alias (seen once in a few hundred runs, as a timed-out wait).
+//
 // Why one issuer: with an issuer per tile the two batches interleaved in the tensor core's
 // queue, which pulled the tiles into lockstep (both softmaxes at once at half speed, then both
 // batches queued; 1049 TFLOP/s).  Alternating batches make the tiles settle half a period apart.
@@ -68,8 +77,8 @@ struct AttnWideSmem {
   static constexpr int kQOffset = 0;
   static constexpr int kKVOffset = 2 * kTileBytes;
   static constexpr int kBarOffset = kKVOffset + kStages * kTileBytes;
-  // q_full, kv_full[S], kv_empty[S], s_full[2], p_full[2], pv_done[2], drain
-  static constexpr int kNumBars = 1 + 2 * kStages + 7;
+  // q_full, kv_full[S], kv_empty[S], s_full[3], p_full[2], pv_done[2], drain
+  static constexpr int kNumBars = 1 + 2 * kStages + 8;
   static constexpr int kTmemPtrOffset = kBarOffset + kNumBars * 8;
   static constexpr int kAbortOffset = kTmemPtrOffset + 4;
   static constexpr int kBytes = kAbortOffset + 4;
@@ -83,7 +92,12 @@ attn_fwd_wide_sm100(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
   using L = AttnWideSmem<D>;
   constexpr int STAGES = L::kStages;
   constexpr uint32_t kTmemCols = 512;
-  constexpr uint32_t kOCol = 256;        // O_t at columns 256 + t*D; S_t at t*128
+  // Tensor memory.  D = 128: score tile S_t at columns 128 t, O_t at 256 + 128 t: all 512, one score tile per
+  // Q tile.  D = 64: the accumulators need only 128 columns, which leaves room for a THIRD score tile: the three
+  // rotate between the two Q tiles (the k-th Q K^T of the CTA, in the order the issuer sends them, goes into tile
+  // k % 3), so that a Q tile's next scores are already waiting when its softmax ends; O_t at 384 + 64 t.
+  constexpr bool kThird = (D == 64);
+  constexpr uint32_t kOCol = kThird ? 384 : 256;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -92,10 +106,10 @@ attn_fwd_wide_sm100(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
   const uint32_t q_full = bar_base;
   auto kv_full = [&](int s) { return bar_base + 8u * (1 + s); };
   auto kv_empty = [&](int s) { return bar_base + 8u * (1 + STAGES + s); };
-  auto s_full = [&](int t) { return bar_base + 8u * (1 + 2 * STAGES + t); };
-  auto p_full = [&](int t) { return bar_base + 8u * (3 + 2 * STAGES + t); };
-  auto pv_done = [&](int t) { return bar_base + 8u * (5 + 2 * STAGES + t); };
-  const uint32_t drain_bar = bar_base + 8u * (7 + 2 * STAGES);
+  auto s_full = [&](int b) { return bar_base + 8u * (1 + 2 * STAGES + b); };      // per score tile
+  auto p_full = [&](int t) { return bar_base + 8u * (4 + 2 * STAGES + t); };      // per Q tile
+  auto pv_done = [&](int t) { return bar_base + 8u * (6 + 2 * STAGES + t); };
+  const uint32_t drain_bar = bar_base + 8u * (8 + 2 * STAGES);
   volatile uint32_t* tmem_ptr_slot = reinterpret_cast<volatile uint32_t*>(smem + L::kTmemPtrOffset);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kAbortOffset);
   const AbortCtx ctx{abort_flag, p.status};
@@ -113,6 +127,10 @@ attn_fwd_wide_sm100(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
   const int n0 = (qt0 * kAttnBQ >= p.S) ? 0 : (CAUSAL ? min(nkv, qt0 + 1) : nkv);
   const int n1 = (qt1 * kAttnBQ >= p.S) ? 0 : (CAUSAL ? min(nkv, qt1 + 1) : nkv);
   const int n_max = max(n0, n1);
+  // Order of the CTA's Q K^T (and P V): the two Q tiles alternate while both have blocks left, then the one with
+  // more goes on alone.  Block j of tile t is number seq_of(t, j) in that order.
+  const int n_min = min(n0, n1);
+  auto seq_of = [&](int t, int j) { return j < n_min ? 2 * j + t : n_min + j; };
   // ring positions: K(j) at 2j, V(j) at 2j + 1
 
   // Producer state (one lane of the producer warp, which also initialises the barriers and issues
@@ -139,8 +157,8 @@ attn_fwd_wide_sm100(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       mbar_init(kv_full(s), 1);
       mbar_init(kv_empty(s), 1);
     }
+    for (int b = 0; b < 3; ++b) mbar_init(s_full(b), 1);
     for (int t = 0; t < 2; ++t) {
-      mbar_init(s_full(t), 1);
       mbar_init(p_full(t), 128);   // one arrival per row
       mbar_init(pv_done(t), 1);
     }
@@ -209,26 +227,26 @@ attn_fwd_wide_sm100(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
     auto last_user = [&](int j) { return j < n1 ? 1 : 0; };
     // S_t = Q_t K(j)^T: D/16 MMAs of 128 x 128 x 16, four (one 64-element chunk of the head dimension) per
     // instruction block.  K(j) must have landed (the caller made sure).
-    auto issue_qk = [&](int t, int j) {
+    auto issue_qk = [&](int t, int j, int buf) {
       const uint32_t idx = 2u * j;
       const uint64_t qd = desc64(smem_desc_lo(smem_base + L::kQOffset + t * L::kTileBytes, 16), desc_hi);
       const uint64_t kd = desc64(smem_desc_lo(kv_addr(idx), 16), desc_hi);
-      const uint32_t s_tmem = tmem_base + t * 128;
+      const uint32_t s_tmem = tmem_base + buf * 128;
 #pragma unroll
       for (int c = 0; c < D / 64; ++c) {
         const uint64_t o = static_cast<uint64_t>((c * L::kChunkBytes) >> 4);   // 32 bytes per k-step inside a chunk
         mma_ss_elect_x4(s_tmem, qd + o, qd + o + 2, qd + o + 4, qd + o + 6, kd + o, kd + o + 2, kd + o + 4, kd + o + 6,
                         idesc_qk, c > 0 ? 1u : 0u);
       }
-      mma_commit_elect(s_full(t));
+      mma_commit_elect(s_full(buf));
       if (t == last_user(j)) mma_commit_elect(kv_empty(idx % STAGES));
     };
     // O_t += P_t(j) V(j): 8 MMAs of 128 x D x 16, P from tensor memory (columns 0-63 of the score tile),
     // four per instruction block.  V(j) must have landed and P_t(j) be complete.
-    auto issue_pv = [&](int t, int j) {
+    auto issue_pv = [&](int t, int j, int buf) {
       const uint32_t idx = 2u * j + 1;
       const uint64_t vd = desc64(smem_desc_lo(kv_addr(idx), L::kChunkBytes), desc_hi);
-      const uint32_t s_tmem = tmem_base + t * 128;
+      const uint32_t s_tmem = tmem_base + buf * 128;
       const uint32_t o_tmem = tmem_base + kOCol + t * D;
 #pragma unroll
       for (int m = 0; m < kWideBKV / 64; ++m) {
@@ -244,8 +262,10 @@ attn_fwd_wide_sm100(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
     // every wait that can be had early is taken BEFORE the one wait that is a true dependency (P from the
     // softmax warps): the K and V tiles are loaded well ahead.  Between P becoming ready and the sixteen MMAs
     // there is then nothing but the fence.
-    auto issue_batch = [&](int t, int j, bool next_scores) -> bool {
-      const uint32_t vidx = 2u * j + 1, kidx = next_scores ? 2u * (j + 1) : vidx;
+    // (t2, j2): whose scores go into the score tile that this P V frees (D = 128: the same Q tile's next block;
+    // D = 64: the third Q K^T from here in the CTA's order)
+    auto issue_batch = [&](int t, int j, int buf, bool next_scores, int t2, int j2) -> bool {
+      const uint32_t vidx = 2u * j + 1, kidx = next_scores ? 2u * j2 : vidx;
       if (lane == 0) WIR_TRACE_EVENT(p.trace, 0, 1 + 10 * t, j);
       // the three barriers tested together (one vote, one branch); full waits only if one is still open
       const bool ready = mbar_test_wait(kv_full(vidx % STAGES), (vidx / STAGES) & 1) &
@@ -258,26 +278,46 @@ attn_fwd_wide_sm100(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       }
       tc_fence_after();
       if (lane == 0) WIR_TRACE_EVENT(p.trace, 0, 2 + 10 * t, j);
-      issue_pv(t, j);
+      issue_pv(t, j, buf);
       if (lane == 0) WIR_TRACE_EVENT(p.trace, 0, 3 + 10 * t, j);
-      // the next scores overwrite S_t (and P inside it): in issue order behind P V, which reads P
-      if (next_scores) issue_qk(t, j + 1);
+      // the next scores overwrite the score tile (and P inside it): in issue order behind P V, which reads P
+      if (next_scores) issue_qk(t2, j2, buf);
       if (lane == 0) WIR_TRACE_EVENT(p.trace, 0, 4 + 10 * t, j);
       return true;
     };
 
     if (n_max > 0) ok = mbar_wait_warp(q_full, 0, ctx, kRoleMma, 1, 0);
     if (ok && n_max > 0) ok = wait_kv(0, 10);
-    if (ok) {
-      tc_fence_after();
-      if (n0 > 0) issue_qk(0, 0);
-      if (n1 > 0) issue_qk(1, 0);
-    }
-    for (int j = 0; ok && j < n_max; ++j) {
+    if constexpr (kThird) {
+      const int total = n0 + n1, longer = (n1 > n0) ? 1 : 0;
+      auto tile_of = [&](int m) { return m < 2 * n_min ? (m & 1) : longer; };
+      auto block_of = [&](int m) { return m < 2 * n_min ? (m >> 1) : m - n_min; };
+      // three Q K^T ahead (K(0) has landed; the third needs K(1))
+      for (int m = 0; ok && m < min(3, total); ++m) {
+        if (block_of(m) > 0) ok = wait_kv(2u * block_of(m), 10);
+        if (ok) {
+          tc_fence_after();
+          issue_qk(tile_of(m), block_of(m), m);
+        }
+      }
+      int buf = 0;
+      for (int m = 0; ok && m < total; ++m) {
+        const bool more = m + 3 < total;
+        ok = issue_batch(tile_of(m), block_of(m), buf, more, more ? tile_of(m + 3) : 0, more ? block_of(m + 3) : 0);
+        buf = (buf == 2) ? 0 : buf + 1;
+      }
+    } else {
+      if (ok) {
+        tc_fence_after();
+        if (n0 > 0) issue_qk(0, 0, 0);
+        if (n1 > 0) issue_qk(1, 0, 1);
+      }
+      for (int j = 0; ok && j < n_max; ++j) {
 #pragma unroll
-      for (int t = 0; t < 2; ++t) {
-        const int n = (t == 0) ? n0 : n1;
-        if (ok && j < n) ok = issue_batch(t, j, j + 1 < n);
+        for (int t = 0; t < 2; ++t) {
+          const int n = (t == 0) ? n0 : n1;
+          if (ok && j < n) ok = issue_batch(t, j, t, j + 1 < n, t, j + 1);
+        }
       }
     }
     if (!ok || *abort_flag) {
@@ -294,7 +334,6 @@ attn_fwd_wide_sm100(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
     const int qt = 2 * pair + t;
     const int q_row = qt * kAttnBQ + quarter * 32 + lane;
     const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
-    const uint32_t s_addr = lane_base + t * 128;
     const uint32_t o_addr = lane_base + kOCol + t * D;
     const float c = p.scale_log2;
     const int n = (t == 0) ? n0 : n1;
@@ -307,7 +346,12 @@ attn_fwd_wide_sm100(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
 
     for (int j = 0; j < n; ++j) {
       if (quarter == 0 && lane == 0) WIR_TRACE_EVENT(p.trace, 1 + t, 100, j);
-      if (!mbar_wait_warp(s_full(t), j & 1, ctx, kRoleSoftmax, t, j)) { ok = false; break; }
+      // which score tile, and which of its completions (D = 128: the Q tile's own, one completion per block)
+      const int k_seq = kThird ? seq_of(t, j) : 0;
+      const int buf = kThird ? k_seq % 3 : t;
+      const uint32_t s_phase = kThird ? static_cast<uint32_t>(k_seq / 3) & 1u : static_cast<uint32_t>(j) & 1u;
+      const uint32_t s_addr = lane_base + buf * 128;
+      if (!mbar_wait_warp(s_full(buf), s_phase, ctx, kRoleSoftmax, t, j)) { ok = false; break; }
       tc_fence_after();
       if (quarter == 0 && lane == 0) WIR_TRACE_EVENT(p.trace, 1 + t, 101, j);
 
@@ -403,6 +447,13 @@ attn_fwd_wide_sm100(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       }
 #undef WIR_S
       l += (la.x + lb.x) + (la.y + lb.y);
+      if constexpr (kThird) {
+        // With its next scores computed ahead, a Q tile could finish block j + 1 before the issuing warp (held up by
+        // a K or V tile, say) has looked at "P ready" of block j, and the barrier's parity would then read as "not
+        // yet" for good.  So block j is only announced once P V of block j - 1 has completed, which the issuing warp
+        // sends after it has seen block j - 1: the barrier is never more than one completion ahead of its reader.
+        if (j > 0 && !mbar_wait_warp(pv_done(t), (j - 1) & 1, ctx, kRoleSoftmax, 8 + t, j)) { ok = false; break; }
+      }
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(p_full(t));
