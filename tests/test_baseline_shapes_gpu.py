@@ -111,3 +111,42 @@ def test_attention_noncausal_b16_h16_s4096_d128(lib):
 @pytest.mark.parametrize("D", [64, 128])
 def test_attention_causal_b4_h32_s8192(D, lib):
     _attention_case(4, 32, 8192, D, True, seed=D)
+
+
+def _backward_case(B, H, S, D, causal, seed, slices):
+    """Attention backward at a benchmark shape: exactly linear in dO over the whole grid (doubling dO is
+    exact in bf16 and in every fp32 accumulation), and whole batch x head slices against autograd of the
+    CPU oracle."""
+    Q, K, V = R.attention_inputs(B, H, S, D, seed=seed)
+    dO = R.randn_bf16((B, H, S, D), torch.Generator().manual_seed(seed + 1000))
+    Qd, Kd, Vd, dOd = (t.cuda() for t in (Q, K, V, dO))
+    O = torch.empty_like(Qd)
+    LSE = torch.empty(B, H, S, dtype=torch.float32, device="cuda")
+    runtime.launch_attention(Qd, Kd, Vd, O, LSE, None, causal)
+
+    def grads(g):
+        out = [torch.full(t.shape, float("nan"), dtype=torch.float32, device="cuda") for t in (Qd, Kd, Vd)]
+        runtime.launch_attention_backward(Qd, Kd, Vd, O, g, LSE, *out, causal=causal)
+        runtime.read_status()
+        return out
+
+    once = grads(dOd)
+    twice = grads(dOd * 2)
+    for name, a, b in zip(("dQ", "dK", "dV"), once, twice):
+        assert not torch.isnan(a).any(), name
+        assert torch.equal(a * 2, b), name
+    for b, h in slices:
+        ref = R.attention_backward_ref(Q[b:b + 1, h:h + 1], K[b:b + 1, h:h + 1], V[b:b + 1, h:h + 1],
+                                       dO[b:b + 1, h:h + 1], None, causal)
+        for name, got, want in zip(("dQ", "dK", "dV"), once, ref):
+            err = ((got[b, h].cpu() - want[0, 0]).abs().max() / want.abs().max()).item()
+            assert err <= R.ATTN_GRAD_REL_TOL, (name, b, h, err)
+
+
+def test_attention_backward_noncausal_b16_h16_s4096_d128(lib):
+    _backward_case(16, 16, 4096, 128, False, seed=3, slices=[(0, 0), (9, 7), (15, 15)])
+
+
+@pytest.mark.parametrize("D", [64, 128])
+def test_attention_backward_causal_b4_h32_s8192(D, lib):
+    _backward_case(4, 32, 8192, D, True, seed=4 + D, slices=[(0, 0), (3, 31)])
