@@ -9,7 +9,7 @@
 // With c = scale * log2(e), per step j (Y0, Y1 the streamed 128 x D tiles):
 //
 //   A1:  T0 = X0 Y0^T            A2:  T1 = X1 Y1^T                       (128 x 128 each, operands in shared memory)
-//   P  = 2^(c T0 - LSE log2e)    dS = P (T1 - delta) scale               (compute warps, packed to bf16 in place)
+//   P  = 2^(c T0 - LSE log2e)    dS = P (T1 - delta) scale               (compute warps; packed to bf16 into T1)
 //   DKV:  B1: acc0 += P Y1 (dV)  B2: acc1 += dS Y0 (dK)       else  B: acc0 += dS Y0 (dQ)     (A from tensor memory)
 //
 // In the dQ launch LSE and delta belong to the thread's row and sit in two registers.  In the dK / dV launch they
