@@ -13,11 +13,16 @@ softmax warps: 100 waits for the scores, 101 has them, 102 has loaded them from 
 2 has it, 3 has issued P V, 4 has issued the next Q K^T.
 
 ``--backward``: the two launches of the backward write the same regions, the second over the first, so
-the timeline shown is that of the dK/dV launch unless ``--dq-only`` stops after the dQ launch.  Region 0 =
-the MMA-issuing warp (0 waits for P / dS of a step, 1 has them, 2 has issued stage 2, 3 has issued stage 1
-of the step after next), 1 / 2 = one thread of each compute warpgroup (10 waits for the scores, 11 has
-them, 12 has loaded a pass of 32 columns, 13 has stored P / dS, 14 has signalled; 90 set-up done, 91
-prologue done, 92 accumulators complete), 3 = event 93, epilogue done.  ``--library`` names another
+the timeline shown is that of the dK/dV launch unless ``--dq-only`` stops after the dQ launch.  The 128-row
+kernel (the library's choice): region 0 = the MMA-issuing warp (0 a step begins, 1 has seen "P ready" (dQ launch:
+T0 read), 2 has issued B1 (and the next scores if they had to wait for their tile), 3 has seen "dS ready", 4 has
+issued B2 / B and the next dP), 1 / 2 = one thread of compute warpgroup 0 / 1 (10 a step begins, 11 T0 has
+arrived, 15 T0 is loaded and released, 16 exponentials done, 13 T1 has arrived, 17 T1 is loaded, 12 P stored and
+signalled (dK/dV launch), 14 dS stored and signalled; 90 set-up done, 91 prologue done, 92 accumulators complete),
+3 = event 93, epilogue done.  With ``WARPIR_ATTN_BWD_ROWS=64`` the 64-row kernel runs instead (region 0: 0 waits
+for P / dS of a step, 1 has them, 2 has issued stage 2, 3 has issued stage 1 of the step after next; compute:
+10 waits for the scores, 11 has them, 12 has loaded a pass of 32 columns, 13 has stored P / dS, 14 has signalled).
+``--library`` names another
 debug build (e.g. one that also has ``WIR_BWD_ABLATE`` set).  A measurement aid; the product library
 has no tracing in it."""
 from __future__ import annotations
