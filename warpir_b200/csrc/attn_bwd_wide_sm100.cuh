@@ -87,13 +87,14 @@ attn_bwd_wide_sm100(const __grid_constant__ CUtensorMap tmap_x0, const __grid_co
   constexpr uint32_t kT1Col = 128, kAccCol = 256;
   constexpr uint32_t kPackCol = 32;    // packed dS (dQ launch) / packed P (dK / dV launch) start here inside T1
   // One pair of exponentials in so many takes the FMA pipe (a cubic) instead of the exponential unit; 0: none.
-  // Measured in clocks per step: the dQ launch 2730 with one pair in four, 3410 with none.  The dK / dV launch
-  // gains 0.4 % from the same share now that its loop holds nothing else but a multiplication; while it still
-  // read its statistics from shared memory there, any share made it slower.
+  // Measured: the dQ launch takes 2730 clocks per step with one pair in four and 3410 with none (a third is level,
+  // a half slower).  The dK / dV launch, whose exponentials run under the chain of MMAs anyway, is 0.6-1.4 %
+  // faster with none at D = 128 (under the power cap fewer instructions buy clock) and 1 % faster with one in
+  // four at D = 64.
 #if defined(WIR_BWD_POLY_DQ) && defined(WIR_BWD_POLY_DKV)
   constexpr int kPolyEvery = DKV ? WIR_BWD_POLY_DKV : WIR_BWD_POLY_DQ;
 #else
-  constexpr int kPolyEvery = 4;
+  constexpr int kPolyEvery = (DKV && D == 128) ? 0 : 4;
 #endif
 
   extern __shared__ uint8_t smem_raw[];
